@@ -1,0 +1,169 @@
+/*
+ * ppl_nn_b200.h -- C ABI of the B200 (sm_100a) kernels behind ppl.nn's llm_cuda operators
+ *   opmx.dynamic_batching.KeyValueCache            and
+ *   opmx.dynamic_batching.MultiHeadCacheAttention.
+ *
+ * In ppl.nn these operators call into an external kernel library through C++ entry points
+ * (namespace ppl::kernel::llm::cuda::pmx).  The functions below are what a binding for this path
+ * would bind instead: plain pointers and sizes, `int` status codes, no C++ or torch types.  All
+ * device pointers belong to the caller; every function only enqueues work on `stream` (a
+ * cudaStream_t passed as void*) and returns without synchronising, unless stated otherwise.
+ * Citations are paths inside the ppl.nn source tree.
+ *
+ * Tensor contract (src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/
+ * multi_head_cache_attention_kernel.cc:27-41; index tensors are int64 on the device):
+ *   query          [T, num_heads, head_dim]        fp16
+ *   current_key    [T, num_kv_heads, head_dim]     fp16
+ *   current_value  [T, num_kv_heads, head_dim]     fp16
+ *   seqstarts      [batch+1]   prefix sum of the query lengths
+ *   kvstarts       [batch+1]   prefix sum of start_pos + query length
+ *   cachestarts    [batch]     first cache row of each sequence
+ *                  ([batch, cachestart_stride_b] page start rows when cache_mode == 1)
+ *   start_pos      [batch]     tokens already cached
+ *   cache          int8,  cache_layout 0: (MaxT, L, 2, Hkv, Dh)       3: (L, 2, Hkv, MaxT, Dh)
+ *   scale          fp16,  same with Dh/quant_group in place of Dh
+ *   attn_output    [T, num_heads, head_dim]        fp16
+ * The first `decoding_batches` sequences are decode sequences (one query token each); the rest
+ * are prefill sequences.
+ */
+#ifndef PPL_NN_B200_H_
+#define PPL_NN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  ppl.nn reports ppl::common::RetCode; its numeric values are defined in the
+ * ppl.common module, so the host layer maps these by name (RC_SUCCESS, RC_UNSUPPORTED, ...). */
+enum {
+    PPLB200_SUCCESS = 0,
+    PPLB200_INVALID_VALUE = 1,       /* RC_INVALID_VALUE                                          */
+    PPLB200_UNSUPPORTED = 2,         /* RC_UNSUPPORTED                                            */
+    PPLB200_OUT_OF_MEMORY = 3,       /* RC_OUT_OF_MEMORY: workspace too small                     */
+    PPLB200_DEVICE_RUNTIME_ERROR = 4,/* RC_DEVICE_RUNTIME_ERROR: a CUDA call or launch failed     */
+    PPLB200_NOT_FOUND = 5,           /* RC_NOT_FOUND: a required pointer is null                  */
+    PPLB200_NO_DEVICE_CODE = 6       /* the library was built without sm_100a device code        */
+};
+
+/* Phases of MultiHeadCacheAttention, for pplb200_attn_params.phase_mask (0 means all). */
+enum {
+    PPLB200_PHASE_APPEND = 1,  /* quantise + append current_key/current_value                     */
+    PPLB200_PHASE_DECODE = 2,  /* split-k attention of the first decoding_batches sequences       */
+    PPLB200_PHASE_PREFILL = 4  /* causal attention of the remaining sequences                     */
+};
+
+/*
+ * Operator attributes + engine knobs + launch geometry, i.e. everything that
+ * dynamic_batching_multi_head_cache_attention::heuristic_prepare() receives as scalars
+ * (multi_head_cache_attention_kernel.cc:170-212), plus the attributes of KeyValueCacheParam
+ * (src/ppl/nn/params/opmx/key_value_cache_param.h:10-18) that the append needs.
+ */
+typedef struct pplb200_attn_params {
+    /* MultiHeadCacheAttentionParam (src/ppl/nn/params/opmx/multi_head_cache_attention_param.h:10-22) */
+    int32_t num_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim;           /* 64 or 128                                                      */
+    int32_t is_causal;
+    int32_t num_layer;
+    int32_t layer_idx;
+    int32_t quant_bit;          /* must be 8                                                      */
+    int32_t quant_group;        /* must be 8                                                      */
+    int32_t cache_mode;         /* 0: one contiguous row range per sequence, 1: paged             */
+    int32_t cache_layout;       /* 0 or 3                                                         */
+    int32_t page_size;          /* paged mode only; a multiple of 16                              */
+    /* EngineConfig knobs (src/ppl/nn/engines/llm_cuda/engine_config.h:30-35) */
+    int32_t enable_cache_prefill;  /* prefill reads the INT8 cache including start_pos history    */
+    int32_t split_k_mode;          /* specify_decoding_attn_split_k: 0 off, 1 heuristic, 2 always */
+    int32_t phase_mask;            /* 0 = all phases; else an OR of PPLB200_PHASE_*               */
+    /* host scalars of the call (multi_head_cache_attention_kernel.cc:114-134) */
+    int64_t batch;              /* start_pos.dim(0)                                               */
+    int64_t decoding_batches;
+    int64_t max_seqlen;
+    int64_t max_kvlen;
+    int64_t total_tokens;       /* T = query.dim(0)                                               */
+    int64_t max_tokens;         /* MaxT: cache rows (cache.dim(0) for layout 0, dim(3) for 3)     */
+    /* cache strides in elements of `cache` (same file :141-155); the scale tensor uses the same
+     * strides divided by quant_group */
+    int64_t cache_stride_s;
+    int64_t cache_stride_l;
+    int64_t cache_stride_h;
+    int64_t cache_stride_kv;
+    int64_t cachestart_stride_b; /* cachestarts.dim(1) when cache_mode == 1, else 0 (:161-168)    */
+} pplb200_attn_params;
+
+/* Fills the four cache strides from (cache_layout, num_layer, num_kv_heads, head_dim, max_tokens)
+ * exactly as multi_head_cache_attention_kernel.cc:141-155 does.  Host only. */
+int pplb200_fill_cache_strides(pplb200_attn_params* p);
+
+/*
+ * KeyValueCache, write side.  Replaces the quantise-and-append that the reference performs
+ * inside dynamic_batching_multi_head_cache_attention::forward (call site
+ * multi_head_cache_attention_kernel.cc:230; operator contract
+ * kernels/opmx/dynamic_batching/key_value_cache_kernel.cc:26-35).
+ * Token i of sequence b goes to cache row cachestarts[b] + start_pos[b] + i.
+ * Codes: int8 in [-127,127]; scale: fp16(absmax/127) per group of 8 channels.
+ */
+int pplb200_kv_append_i8g8(const pplb200_attn_params* p, const void* current_key, const void* current_value,
+                           const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos,
+                           void* cache, void* scale, void* stream);
+
+/*
+ * KeyValueCache, read side: the operator's `key` and `value` outputs, i.e. the dequantised
+ * history of every sequence packed as [total_kv, num_kv_heads, head_dim] fp16 with
+ * total_kv = kvstarts[batch]
+ * (src/ppl/nn/oputils/opmx/reshape_dynamic_batching_key_value_cache.cc:26-41;
+ *  src/ppl/nn/engines/llm_cuda/ops/opmx/dynamic_batching/key_value_cache_op.cc:37-56).
+ */
+int pplb200_kv_gather_dequant(const pplb200_attn_params* p, const int64_t* kvstarts, const int64_t* cachestarts,
+                              const void* cache, const void* scale, int64_t total_kv, void* key_out,
+                              void* value_out, void* stream);
+
+/*
+ * Scratch bytes that pplb200_mhca_forward needs for these params.  Replaces
+ * heuristic_prepare()'s cfg.workspace_size (multi_head_cache_attention_kernel.cc:170-218).
+ * Host only; depends on batch, decoding_batches, max_seqlen, max_kvlen, head counts and knobs.
+ */
+int pplb200_mhca_workspace_size(const pplb200_attn_params* p, uint64_t* bytes);
+
+/*
+ * MultiHeadCacheAttention.  Replaces heuristic_prepare() + forward()
+ * (multi_head_cache_attention_kernel.cc:170-230): append (unless masked out), split-k decode
+ * over the INT8 cache for sequences [0, decoding_batches), causal prefill for the rest.
+ * `workspace` is caller-allocated device memory of at least pplb200_mhca_workspace_size() bytes,
+ * 256-byte aligned; its contents need not be initialised and are undefined afterwards.
+ * Calls that share a workspace must not overlap on the device.
+ */
+int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const void* current_key,
+                         const void* current_value, const int64_t* seqstarts, const int64_t* kvstarts,
+                         const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale,
+                         void* workspace, uint64_t workspace_bytes, void* attn_output, void* stream);
+
+/*
+ * Reads the device-side status word that the kernels of the last pplb200_mhca_forward on this
+ * workspace left behind (0 = clean; non-zero = a bounded wait gave up, see PPLB200_DEV_*).
+ * Synchronises `stream`.  Has no counterpart in the reference; it exists because every wait
+ * in these kernels is bounded and reports instead of hanging.
+ */
+int pplb200_mhca_device_status(const void* workspace, void* stream, uint32_t* status);
+
+enum {
+    PPLB200_DEV_OK = 0,
+    PPLB200_DEV_TMA_WAIT_TIMEOUT = 1,  /* a wait for a bulk-tensor copy ran out of iterations    */
+    PPLB200_DEV_MMA_WAIT_TIMEOUT = 2   /* a wait for a tensor-core commit ran out of iterations   */
+};
+
+/* Name of a status code ("RC_SUCCESS", ...).  Never null. */
+const char* pplb200_status_str(int status);
+
+/* 1 if the library contains sm_100a device code and a CUDA device is present, else 0. */
+int pplb200_device_ready(void);
+
+/* Number of kernels launched by this library since load (all entry points).  For benchmarks. */
+uint64_t pplb200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PPL_NN_B200_H_ */

@@ -1,0 +1,183 @@
+"""Python face of the CPU oracle.  TEST INFRASTRUCTURE ONLY -- PARITY UNPINNED.
+
+Two independent restatements of the same contract live here:
+
+* ``CORacle`` loads ``kvattn_oracle.c`` (compiled by :func:`build`) through ctypes.  It is the
+  oracle of record for the tests, the smoke check and the benchmark's CPU baseline.
+* ``np_quant_groups`` / ``np_dequant`` / ``np_attention_one`` are a numpy twin of the same formulas,
+  written separately so that the C file is itself checked (the two must agree bit for bit on
+  the quantiser and to fp32 round-off on attention).
+
+Neither is ever imported by the CUDA product path.  "Parity unpinned" means: the reference
+tree (ppl.nn) contains no source, test or golden vector for the arithmetic of this path -- it
+lives in the un-vendored ppl.llm.kernel.cuda module -- so the quantisation formula below is the
+one fixed by this repository from the published description "INT8 symmetric groupwise, group 8,
+fp16 scale = absmax / 127", not one verified against the reference's own output.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+_SRC = _HERE / "kvattn_oracle.c"
+_OUT_DIR = _HERE / "_build"
+_LIB = _OUT_DIR / "libkvattn_oracle.so"
+
+
+def build(force: bool = False) -> Path:
+    """Compile kvattn_oracle.c into oracle/_build/ (x86-64-v3 so the file runs on any recent host)."""
+    if _LIB.exists() and not force and _LIB.stat().st_mtime >= _SRC.stat().st_mtime:
+        return _LIB
+    _OUT_DIR.mkdir(exist_ok=True)
+    cmd = ["gcc", "-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-shared", "-Wall", "-Wextra",
+           "-o", str(_LIB), str(_SRC), "-lm"]
+    subprocess.run(cmd, check=True)
+    return _LIB
+
+
+class OrcDesc(ctypes.Structure):
+    _fields_ = [
+        ("num_heads", ctypes.c_int32), ("num_kv_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("is_causal", ctypes.c_int32), ("num_layer", ctypes.c_int32), ("layer_idx", ctypes.c_int32),
+        ("quant_group", ctypes.c_int32), ("cache_mode", ctypes.c_int32), ("cache_layout", ctypes.c_int32),
+        ("page_size", ctypes.c_int32), ("enable_cache_prefill", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("batch", ctypes.c_int64), ("decoding_batches", ctypes.c_int64), ("max_tokens", ctypes.c_int64),
+        ("cachestart_stride_b", ctypes.c_int64),
+    ]
+
+
+def _ptr(a: np.ndarray):
+    assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
+    return a.ctypes.data_as(ctypes.c_void_p)
+
+
+class COracle:
+    """ctypes wrapper over the compiled C oracle.  fp16 tensors are numpy float16 arrays."""
+
+    def __init__(self, lib_path: os.PathLike | None = None):
+        path = Path(lib_path) if lib_path else (_LIB if _LIB.exists() else build())
+        self.lib = ctypes.CDLL(str(path))
+        L = self.lib
+        L.orc_half_to_float.restype = ctypes.c_float
+        L.orc_half_to_float.argtypes = [ctypes.c_uint16]
+        L.orc_float_to_half.restype = ctypes.c_uint16
+        L.orc_float_to_half.argtypes = [ctypes.c_float]
+        vp = ctypes.c_void_p
+        L.orc_quant_group.restype = None
+        L.orc_quant_group.argtypes = [vp, vp, vp]
+        L.orc_kv_append.restype = ctypes.c_int
+        L.orc_kv_append.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 7
+        L.orc_kv_gather_dequant.restype = ctypes.c_int
+        L.orc_kv_gather_dequant.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 6
+        L.orc_attention.restype = ctypes.c_int
+        L.orc_attention.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 9 + [ctypes.c_int64, ctypes.c_int64]
+        L.orc_mhca.restype = ctypes.c_int
+        L.orc_mhca.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 9
+        L.orc_num_threads.restype = ctypes.c_int
+
+    # -- scalar helpers ---------------------------------------------------------------
+    def half_to_float(self, h: int) -> float:
+        return float(self.lib.orc_half_to_float(h))
+
+    def float_to_half(self, f: float) -> int:
+        return int(self.lib.orc_float_to_half(ctypes.c_float(f)))
+
+    def num_threads(self) -> int:
+        return int(self.lib.orc_num_threads())
+
+    def quant_groups(self, x: np.ndarray):
+        """x: float16 [..., 8k] -> (int8 codes same shape, float16 scales [..., k])."""
+        x = np.ascontiguousarray(x, dtype=np.float16)
+        flat = x.reshape(-1, 8)
+        codes = np.empty(flat.shape, dtype=np.int8)
+        scales = np.empty(flat.shape[0], dtype=np.float16)
+        for i in range(flat.shape[0]):
+            self.lib.orc_quant_group(flat[i].ctypes.data_as(ctypes.c_void_p),
+                                     codes[i].ctypes.data_as(ctypes.c_void_p),
+                                     ctypes.c_void_p(scales.ctypes.data + 2 * i))
+        return codes.reshape(x.shape), scales.reshape(x.shape[:-1] + (x.shape[-1] // 8,))
+
+    # -- operators --------------------------------------------------------------------
+    @staticmethod
+    def desc(**kw) -> OrcDesc:
+        d = OrcDesc()
+        d.quant_group = 8
+        d.page_size = 128
+        d.num_layer = 1
+        d.is_causal = 1
+        for k, v in kw.items():
+            if not hasattr(d, k):
+                raise KeyError(k)
+            setattr(d, k, int(v))
+        return d
+
+    def kv_append(self, d, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale):
+        rc = self.lib.orc_kv_append(ctypes.byref(d), _ptr(cur_k), _ptr(cur_v), _ptr(seqstarts), _ptr(cachestarts),
+                                    _ptr(start_pos), _ptr(cache), _ptr(scale))
+        if rc != 0:
+            raise RuntimeError(f"orc_kv_append failed: {rc}")
+
+    def kv_gather_dequant(self, d, kvstarts, cachestarts, cache, scale):
+        total = int(kvstarts[-1])
+        key = np.empty((total, d.num_kv_heads, d.head_dim), dtype=np.float16)
+        value = np.empty_like(key)
+        rc = self.lib.orc_kv_gather_dequant(ctypes.byref(d), _ptr(kvstarts), _ptr(cachestarts), _ptr(cache),
+                                            _ptr(scale), _ptr(key), _ptr(value))
+        if rc != 0:
+            raise RuntimeError(f"orc_kv_gather_dequant failed: {rc}")
+        return key, value
+
+    def attention(self, d, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale,
+                  seq_lo: int = 0, seq_hi: int | None = None, out: np.ndarray | None = None):
+        if out is None:
+            out = np.zeros(query.shape, dtype=np.float16)
+        hi = int(d.batch) if seq_hi is None else int(seq_hi)
+        rc = self.lib.orc_attention(ctypes.byref(d), _ptr(query), _ptr(cur_k), _ptr(cur_v), _ptr(seqstarts),
+                                    _ptr(cachestarts), _ptr(start_pos), _ptr(cache), _ptr(scale), _ptr(out),
+                                    int(seq_lo), hi)
+        if rc != 0:
+            raise RuntimeError(f"orc_attention failed: {rc}")
+        return out
+
+    def mhca(self, d, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale):
+        out = np.zeros(query.shape, dtype=np.float16)
+        rc = self.lib.orc_mhca(ctypes.byref(d), _ptr(query), _ptr(cur_k), _ptr(cur_v), _ptr(seqstarts),
+                               _ptr(cachestarts), _ptr(start_pos), _ptr(cache), _ptr(scale), _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"orc_mhca failed: {rc}")
+        return out
+
+
+# ------------------------------------------------------------------ numpy twin ---------
+
+def np_quant_groups(x: np.ndarray):
+    """Same formula as orc_quant_group, vectorised.  x: float16 [..., 8k]."""
+    x = np.asarray(x, dtype=np.float16)
+    g = x.reshape(x.shape[:-1] + (x.shape[-1] // 8, 8)).astype(np.float32)
+    with np.errstate(invalid="ignore", divide="ignore", over="ignore"):
+        a = np.fmax.reduce(np.abs(g), axis=-1, initial=np.float32(0))  # fmax ignores NaN like `m > a`
+        s16 = (a / np.float32(127.0)).astype(np.float16)
+        s = s16.astype(np.float32)[..., None]
+        q = np.rint(g / s)  # numpy rint is round-half-to-even
+        q = np.where(q >= -127.0, q, np.float32(-127.0))  # NaN -> -127 like the C code
+        q = np.where(q > 127.0, np.float32(127.0), q)
+        q = np.where(s != 0, q, np.float32(0))
+    return q.astype(np.int8).reshape(x.shape), s16
+
+
+def np_dequant(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
+    """float32 dequantised values; codes [..., 8k] int8, scales [..., k] float16."""
+    c = codes.reshape(codes.shape[:-1] + (codes.shape[-1] // 8, 8)).astype(np.float32)
+    return (c * scales.astype(np.float32)[..., None]).reshape(codes.shape)
+
+
+def np_attention_one(q: np.ndarray, k: np.ndarray, v: np.ndarray) -> np.ndarray:
+    """One query vector against n_kv rows; all float32.  q [Dh], k/v [n_kv, Dh] -> [Dh]."""
+    s = (k @ q) * np.float32(1.0 / np.sqrt(np.float32(q.shape[0])))
+    p = np.exp(s - s.max())
+    return (p @ v) / p.sum()

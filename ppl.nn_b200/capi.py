@@ -1,0 +1,156 @@
+"""ctypes binding of the C ABI declared in include/ppl_nn_b200.h.
+
+Only pointers and integers cross this boundary.  The library is loaded from ``lib/`` next to this
+file and never falls back to anything else: if it is missing, or was built without sm_100a code for
+the current device, the calls fail with an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "lib" / "libppl_nn_b200.so"
+
+SUCCESS = 0
+INVALID_VALUE = 1
+UNSUPPORTED = 2
+OUT_OF_MEMORY = 3
+DEVICE_RUNTIME_ERROR = 4
+NOT_FOUND = 5
+NO_DEVICE_CODE = 6
+
+PHASE_APPEND = 1
+PHASE_DECODE = 2
+PHASE_PREFILL = 4
+
+DEV_OK = 0
+DEV_TMA_WAIT_TIMEOUT = 1
+DEV_MMA_WAIT_TIMEOUT = 2
+DEV_LENGTH_CLAMPED = 4
+
+# every symbol include/ppl_nn_b200.h declares
+EXPORTS = (
+    "pplb200_fill_cache_strides",
+    "pplb200_kv_append_i8g8",
+    "pplb200_kv_gather_dequant",
+    "pplb200_mhca_workspace_size",
+    "pplb200_mhca_forward",
+    "pplb200_mhca_device_status",
+    "pplb200_status_str",
+    "pplb200_device_ready",
+    "pplb200_launch_count",
+)
+
+
+class AttnParams(ctypes.Structure):
+    """Mirror of ``pplb200_attn_params``; field order and types must match the header."""
+
+    _fields_ = [
+        ("num_heads", ctypes.c_int32), ("num_kv_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("is_causal", ctypes.c_int32), ("num_layer", ctypes.c_int32), ("layer_idx", ctypes.c_int32),
+        ("quant_bit", ctypes.c_int32), ("quant_group", ctypes.c_int32), ("cache_mode", ctypes.c_int32),
+        ("cache_layout", ctypes.c_int32), ("page_size", ctypes.c_int32),
+        ("enable_cache_prefill", ctypes.c_int32), ("split_k_mode", ctypes.c_int32), ("phase_mask", ctypes.c_int32),
+        ("batch", ctypes.c_int64), ("decoding_batches", ctypes.c_int64), ("max_seqlen", ctypes.c_int64),
+        ("max_kvlen", ctypes.c_int64), ("total_tokens", ctypes.c_int64), ("max_tokens", ctypes.c_int64),
+        ("cache_stride_s", ctypes.c_int64), ("cache_stride_l", ctypes.c_int64), ("cache_stride_h", ctypes.c_int64),
+        ("cache_stride_kv", ctypes.c_int64), ("cachestart_stride_b", ctypes.c_int64),
+    ]
+
+    def copy(self) -> "AttnParams":
+        other = AttnParams()
+        ctypes.memmove(ctypes.byref(other), ctypes.byref(self), ctypes.sizeof(self))
+        return other
+
+
+class StatusError(RuntimeError):
+    def __init__(self, fn: str, code: int, name: str):
+        super().__init__(f"{fn} returned {name} ({code})")
+        self.code = code
+        self.name = name
+
+
+class Library:
+    """The loaded shared library with typed entry points."""
+
+    def __init__(self, path: Path | str | None = None):
+        p = Path(path) if path else LIB_PATH
+        if not p.exists():
+            raise FileNotFoundError(
+                f"{p} is missing: build it with `python -c 'import __graft_entry__ as g; g.build()'` "
+                "(there is no CPU or PyTorch fallback for these operators)")
+        self.path = p
+        self.dll = ctypes.CDLL(str(p))
+        d = self.dll
+        vp, i64p = ctypes.c_void_p, ctypes.c_void_p
+        pp = ctypes.POINTER(AttnParams)
+        d.pplb200_fill_cache_strides.restype = ctypes.c_int
+        d.pplb200_fill_cache_strides.argtypes = [pp]
+        d.pplb200_kv_append_i8g8.restype = ctypes.c_int
+        d.pplb200_kv_append_i8g8.argtypes = [pp, vp, vp, i64p, i64p, i64p, vp, vp, vp]
+        d.pplb200_kv_gather_dequant.restype = ctypes.c_int
+        d.pplb200_kv_gather_dequant.argtypes = [pp, i64p, i64p, vp, vp, ctypes.c_int64, vp, vp, vp]
+        d.pplb200_mhca_workspace_size.restype = ctypes.c_int
+        d.pplb200_mhca_workspace_size.argtypes = [pp, ctypes.POINTER(ctypes.c_uint64)]
+        d.pplb200_mhca_forward.restype = ctypes.c_int
+        d.pplb200_mhca_forward.argtypes = [pp, vp, vp, vp, i64p, i64p, i64p, i64p, vp, vp, vp, ctypes.c_uint64, vp, vp]
+        d.pplb200_mhca_device_status.restype = ctypes.c_int
+        d.pplb200_mhca_device_status.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_uint32)]
+        d.pplb200_status_str.restype = ctypes.c_char_p
+        d.pplb200_status_str.argtypes = [ctypes.c_int]
+        d.pplb200_device_ready.restype = ctypes.c_int
+        d.pplb200_device_ready.argtypes = []
+        d.pplb200_launch_count.restype = ctypes.c_uint64
+        d.pplb200_launch_count.argtypes = []
+
+    # ---- helpers ------------------------------------------------------------------------
+    def status_str(self, code: int) -> str:
+        return self.dll.pplb200_status_str(int(code)).decode()
+
+    def check(self, fn: str, code: int) -> None:
+        if code != SUCCESS:
+            raise StatusError(fn, code, self.status_str(code))
+
+    def device_ready(self) -> bool:
+        return bool(self.dll.pplb200_device_ready())
+
+    def launch_count(self) -> int:
+        return int(self.dll.pplb200_launch_count())
+
+    # ---- raw entry points: return the status code -----------------------------------------
+    def fill_cache_strides(self, p: AttnParams) -> int:
+        return self.dll.pplb200_fill_cache_strides(ctypes.byref(p))
+
+    def kv_append(self, p, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale, stream) -> int:
+        return self.dll.pplb200_kv_append_i8g8(ctypes.byref(p), cur_k, cur_v, seqstarts, cachestarts, start_pos,
+                                               cache, scale, stream)
+
+    def kv_gather_dequant(self, p, kvstarts, cachestarts, cache, scale, total_kv, key_out, value_out, stream) -> int:
+        return self.dll.pplb200_kv_gather_dequant(ctypes.byref(p), kvstarts, cachestarts, cache, scale,
+                                                  int(total_kv), key_out, value_out, stream)
+
+    def mhca_workspace_size(self, p) -> tuple[int, int]:
+        n = ctypes.c_uint64(0)
+        rc = self.dll.pplb200_mhca_workspace_size(ctypes.byref(p), ctypes.byref(n))
+        return rc, int(n.value)
+
+    def mhca_forward(self, p, q, cur_k, cur_v, seqstarts, kvstarts, cachestarts, start_pos, cache, scale,
+                     workspace, workspace_bytes, out, stream) -> int:
+        return self.dll.pplb200_mhca_forward(ctypes.byref(p), q, cur_k, cur_v, seqstarts, kvstarts, cachestarts,
+                                             start_pos, cache, scale, workspace, int(workspace_bytes), out, stream)
+
+    def mhca_device_status(self, workspace, stream) -> tuple[int, int]:
+        s = ctypes.c_uint32(0)
+        rc = self.dll.pplb200_mhca_device_status(workspace, stream, ctypes.byref(s))
+        return rc, int(s.value)
+
+
+_LIB: Library | None = None
+
+
+def library() -> Library:
+    global _LIB
+    if _LIB is None:
+        _LIB = Library()
+    return _LIB

@@ -1,0 +1,377 @@
+// extern "C" layer: argument validation, workspace layout and kernel sequencing for the two operators.
+// Nothing here allocates device memory or synchronises (except pplb200_mhca_device_status).
+#include <cuda_runtime.h>
+#include <stdio.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "common.cuh"
+#include "launch.h"
+
+namespace pplb200 {
+
+static std::atomic<uint64_t> g_launches{0};
+
+int check_launch(const char* kernel_name) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "[ppl_nn_b200] launch of %s failed: %s\n", kernel_name, cudaGetErrorString(e));
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    return PPLB200_SUCCESS;
+}
+
+int current_device_info(DeviceInfo* info) {
+    constexpr int kMaxDevices = 64;
+    static DeviceInfo cache[kMaxDevices];
+    static bool known[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!known[dev]) {
+        DeviceInfo d;
+        d.device_id = dev;
+        if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return PPLB200_DEVICE_RUNTIME_ERROR;
+        }
+        cache[dev] = d;
+        known[dev] = true;
+    }
+    *info = cache[dev];
+    return PPLB200_SUCCESS;
+}
+
+static int fail(int code, const char* what) {
+    fprintf(stderr, "[ppl_nn_b200] %s: %s\n", pplb200_status_str(code), what);
+    return code;
+}
+
+// Attribute and geometry checks shared by all entry points.  The reference rejects
+// quant_bit/quant_group only when BOTH differ from 8 (multi_head_cache_attention_kernel.cc:90-93);
+// here either one differing is rejected, because no other format is implemented.
+static int validate(const pplb200_attn_params* p) {
+    if (!p) {
+        return fail(PPLB200_NOT_FOUND, "params is null");
+    }
+    if (p->quant_bit != 8 || p->quant_group != 8) {
+        return fail(PPLB200_UNSUPPORTED, "only quant_bit == quant_group == 8 is supported");
+    }
+    if (p->head_dim != 64 && p->head_dim != 128) {
+        return fail(PPLB200_UNSUPPORTED, "head_dim must be 64 or 128");
+    }
+    if (p->num_heads <= 0 || p->num_kv_heads <= 0 || p->num_heads % p->num_kv_heads != 0) {
+        return fail(PPLB200_INVALID_VALUE, "num_heads must be a positive multiple of num_kv_heads");
+    }
+    if (p->cache_layout != 0 && p->cache_layout != 3) {
+        return fail(PPLB200_UNSUPPORTED, "only cache_layout 0 and 3 are supported");
+    }
+    if (p->cache_mode != 0 && p->cache_mode != 1) {
+        return fail(PPLB200_UNSUPPORTED, "only cache_mode 0 and 1 are supported");
+    }
+    if (p->cache_mode == 1 && (p->page_size <= 0 || p->page_size % 16 != 0 || p->cachestart_stride_b <= 0)) {
+        return fail(PPLB200_INVALID_VALUE, "paged cache needs page_size % 16 == 0 and 2-d cachestarts");
+    }
+    if (p->num_layer <= 0 || p->layer_idx < 0 || p->layer_idx >= p->num_layer) {
+        return fail(PPLB200_INVALID_VALUE, "layer_idx out of range");
+    }
+    if (p->batch < 0 || p->decoding_batches < 0 || p->decoding_batches > p->batch || p->total_tokens < 0 ||
+        p->batch > 0x7fffffff) {
+        return fail(PPLB200_INVALID_VALUE, "batch / decoding_batches / total_tokens out of range");
+    }
+    if (p->max_tokens <= 0 || p->max_tokens > 0x7fffffff) {
+        return fail(PPLB200_INVALID_VALUE, "max_tokens (cache rows) out of range");
+    }
+    const int64_t s[4] = {p->cache_stride_s, p->cache_stride_l, p->cache_stride_h, p->cache_stride_kv};
+    for (int i = 0; i < 4; ++i) {
+        if (s[i] <= 0 || s[i] % 64 != 0) {
+            return fail(PPLB200_INVALID_VALUE, "cache strides must be positive multiples of 64 elements");
+        }
+    }
+    if (p->split_k_mode < 0 || p->split_k_mode > 2) {
+        return fail(PPLB200_INVALID_VALUE, "split_k_mode must be 0, 1 or 2");
+    }
+    return PPLB200_SUCCESS;
+}
+
+static CacheGeom make_geom(const pplb200_attn_params& p) {
+    CacheGeom g;
+    g.stride_s = p.cache_stride_s;
+    g.stride_l = p.cache_stride_l;
+    g.stride_h = p.cache_stride_h;
+    g.stride_kv = p.cache_stride_kv;
+    g.layer_idx = p.layer_idx;
+    g.cachestart_stride_b = p.cachestart_stride_b;
+    g.cache_mode = p.cache_mode;
+    g.page_size = p.page_size > 0 ? p.page_size : 1;
+    return g;
+}
+
+// The library only carries sm_100a code; on any other device it must fail loudly, never fall back.
+static int require_device(DeviceInfo* di) {
+    const int rc = current_device_info(di);
+    if (rc != PPLB200_SUCCESS) {
+        return fail(PPLB200_NO_DEVICE_CODE, "no usable CUDA device");
+    }
+    if (di->cc_major != 10) {
+        return fail(PPLB200_NO_DEVICE_CODE, "this library holds sm_100a code only; the current device is not sm_100");
+    }
+    return PPLB200_SUCCESS;
+}
+
+struct WorkspaceLayout {
+    DecodePlan decode;
+    PrefillPlan prefill;
+    uint64_t off_prefill;
+    uint64_t bytes;
+};
+
+static int make_layout(const pplb200_attn_params& p, int sm_count, WorkspaceLayout* w) {
+    int rc = make_decode_plan(p, sm_count, &w->decode);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    rc = make_prefill_plan(p, &w->prefill);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    w->off_prefill = w->decode.bytes;
+    w->bytes = w->decode.bytes + w->prefill.bytes;
+    return PPLB200_SUCCESS;
+}
+
+}  // namespace pplb200
+
+using namespace pplb200;
+
+extern "C" {
+
+int pplb200_fill_cache_strides(pplb200_attn_params* p) {
+    if (!p) {
+        return PPLB200_NOT_FOUND;
+    }
+    const int64_t L = p->num_layer, H = p->num_kv_heads, D = p->head_dim, M = p->max_tokens;
+    if (p->cache_layout == 0) {  // (MaxT, L, 2, H, Dh)
+        p->cache_stride_s = L * 2 * H * D;
+        p->cache_stride_l = 2 * H * D;
+        p->cache_stride_h = D;
+        p->cache_stride_kv = H * D;
+    } else if (p->cache_layout == 3) {  // (L, 2, H, MaxT, Dh)
+        p->cache_stride_s = D;
+        p->cache_stride_l = 2 * H * M * D;
+        p->cache_stride_h = M * D;
+        p->cache_stride_kv = H * M * D;
+    } else {
+        return fail(PPLB200_UNSUPPORTED, "only cache_layout 0 and 3 are supported");
+    }
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_kv_append_i8g8(const pplb200_attn_params* p, const void* current_key, const void* current_value,
+                           const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos,
+                           void* cache, void* scale, void* stream) {
+    int rc = validate(p);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!scale) {
+        return fail(PPLB200_UNSUPPORTED, "only a quantised cache is supported but scale is null");
+    }
+    if (!current_key || !current_value || !seqstarts || !cachestarts || !start_pos || !cache) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    DeviceInfo di;
+    rc = require_device(&di);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    return launch_kv_append(*p, make_geom(*p), current_key, current_value, seqstarts, cachestarts, start_pos, cache,
+                            scale, di.sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int pplb200_kv_gather_dequant(const pplb200_attn_params* p, const int64_t* kvstarts, const int64_t* cachestarts,
+                              const void* cache, const void* scale, int64_t total_kv, void* key_out,
+                              void* value_out, void* stream) {
+    int rc = validate(p);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!scale) {
+        return fail(PPLB200_UNSUPPORTED, "only a quantised cache is supported but scale is null");
+    }
+    if (!kvstarts || !cachestarts || !cache || (total_kv > 0 && (!key_out || !value_out))) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    if (total_kv < 0) {
+        return fail(PPLB200_INVALID_VALUE, "total_kv is negative");
+    }
+    DeviceInfo di;
+    rc = require_device(&di);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    return launch_kv_gather_dequant(*p, make_geom(*p), kvstarts, cachestarts, cache, scale, total_kv, key_out,
+                                    value_out, di.sm_count, static_cast<cudaStream_t>(stream));
+}
+
+// The SM count enters the split heuristic.  Without a device (host-only callers sizing buffers
+// ahead of time) the B200 count is assumed; with a device its own count is used, and the forward
+// call uses the same rule, so the two agree on the machine that runs the kernels.
+static int planning_sm_count() {
+    DeviceInfo di;
+    if (current_device_info(&di) == PPLB200_SUCCESS && di.sm_count > 0) {
+        return di.sm_count;
+    }
+    return 148;
+}
+
+int pplb200_mhca_workspace_size(const pplb200_attn_params* p, uint64_t* bytes) {
+    int rc = validate(p);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!bytes) {
+        return fail(PPLB200_NOT_FOUND, "bytes is null");
+    }
+    WorkspaceLayout w;
+    rc = make_layout(*p, planning_sm_count(), &w);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    *bytes = w.bytes;
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const void* current_key,
+                         const void* current_value, const int64_t* seqstarts, const int64_t* kvstarts,
+                         const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale,
+                         void* workspace, uint64_t workspace_bytes, void* attn_output, void* stream_v) {
+    int rc = validate(p);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (p->is_causal == 0 && p->decoding_batches < p->batch) {
+        return fail(PPLB200_UNSUPPORTED, "prefill sequences need is_causal == 1");
+    }
+    if (!scale) {
+        return fail(PPLB200_UNSUPPORTED, "only a quantised cache is supported but scale is null");
+    }
+    if (!query || !current_key || !current_value || !seqstarts || !kvstarts || !cachestarts || !start_pos || !cache ||
+        !attn_output) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    if (p->batch == 0 || p->total_tokens == 0) {
+        return PPLB200_SUCCESS;
+    }
+    DeviceInfo di;
+    rc = require_device(&di);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    WorkspaceLayout w;
+    rc = make_layout(*p, di.sm_count, &w);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!workspace) {
+        return fail(PPLB200_NOT_FOUND, "workspace is null");
+    }
+    if (workspace_bytes < w.bytes) {
+        return fail(PPLB200_OUT_OF_MEMORY, "workspace is smaller than pplb200_mhca_workspace_size()");
+    }
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) {
+        return fail(PPLB200_INVALID_VALUE, "workspace must be 256-byte aligned");
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    const CacheGeom geom = make_geom(*p);
+    const int mask = p->phase_mask ? p->phase_mask : (PPLB200_PHASE_APPEND | PPLB200_PHASE_DECODE | PPLB200_PHASE_PREFILL);
+    uint8_t* ws = static_cast<uint8_t*>(workspace);
+    uint32_t* status = reinterpret_cast<uint32_t*>(ws + w.decode.off_status);
+
+    if (mask & PPLB200_PHASE_APPEND) {
+        rc = launch_kv_append(*p, geom, current_key, current_value, seqstarts, cachestarts, start_pos, cache, scale,
+                              di.sm_count, stream);
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+    }
+    bool status_reset = false;
+    if ((mask & PPLB200_PHASE_DECODE) && p->decoding_batches > 0) {
+        rc = launch_decode(*p, geom, w.decode, query, seqstarts, cachestarts, start_pos, cache, scale, workspace,
+                           attn_output, stream);  // its planning kernel clears the status word
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+        status_reset = true;
+    }
+    if ((mask & PPLB200_PHASE_PREFILL) && p->decoding_batches < p->batch) {
+        if (!status_reset) {
+            if (cudaMemsetAsync(status, 0, 4, stream) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return fail(PPLB200_DEVICE_RUNTIME_ERROR, "cudaMemsetAsync(status) failed");
+            }
+        }
+        rc = launch_prefill(*p, geom, w.prefill, query, current_key, current_value, seqstarts, cachestarts, start_pos,
+                            cache, scale, ws + w.off_prefill, status, attn_output, stream);
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+    }
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_mhca_device_status(const void* workspace, void* stream, uint32_t* status) {
+    if (!workspace || !status) {
+        return PPLB200_NOT_FOUND;
+    }
+    if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    if (cudaMemcpy(status, workspace, 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    return PPLB200_SUCCESS;
+}
+
+const char* pplb200_status_str(int status) {
+    switch (status) {
+        case PPLB200_SUCCESS: return "RC_SUCCESS";
+        case PPLB200_INVALID_VALUE: return "RC_INVALID_VALUE";
+        case PPLB200_UNSUPPORTED: return "RC_UNSUPPORTED";
+        case PPLB200_OUT_OF_MEMORY: return "RC_OUT_OF_MEMORY";
+        case PPLB200_DEVICE_RUNTIME_ERROR: return "RC_DEVICE_RUNTIME_ERROR";
+        case PPLB200_NOT_FOUND: return "RC_NOT_FOUND";
+        case PPLB200_NO_DEVICE_CODE: return "RC_NO_DEVICE_CODE";
+        default: return "RC_OTHER_ERROR";
+    }
+}
+
+int pplb200_device_ready(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    DeviceInfo di;
+    if (current_device_info(&di) != PPLB200_SUCCESS) {
+        return 0;
+    }
+    return di.cc_major == 10 ? 1 : 0;
+}
+
+uint64_t pplb200_launch_count(void) {
+    return g_launches.load(std::memory_order_relaxed);
+}
+
+}  // extern "C"

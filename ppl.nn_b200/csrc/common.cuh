@@ -1,0 +1,224 @@
+// Device-side helpers shared by the sm_100a kernels: PTX wrappers for mbarrier, bulk-tensor (TMA)
+// copies, warp-level MMA, byte permutes, and the INT8 group quantiser.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pplb200 {
+
+// ------------------------------------------------------------------------------------------
+// Device status word (first 4 bytes of the workspace).  Kernels OR a code into it when a bounded
+// wait gives up; they never spin forever.
+// ------------------------------------------------------------------------------------------
+constexpr uint32_t kDevOk = 0;
+constexpr uint32_t kDevTmaTimeout = 1;
+constexpr uint32_t kDevMmaTimeout = 2;
+
+// Upper bound on polls of one mbarrier wait.  One poll is a try_wait with a hardware time slice,
+// so this is tens of milliseconds at least -- far beyond any legitimate copy latency.
+constexpr uint32_t kMaxWaitPolls = 1u << 20;
+constexpr uint32_t kDevLengthClamped = 4;  // a sequence was longer than max_kvlen / max_seqlen and was clamped
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ------------------------------------------------------------------------------------------
+// mbarrier
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+    // make the initialised barriers visible to the async proxy (TMA / tcgen05 completions)
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Returns false when the poll budget ran out (the caller records a status code
+// and carries on with whatever is in shared memory; nothing hangs).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kMaxWaitPolls; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+    }
+    return false;
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------
+// TMA: tiled bulk-tensor loads, global -> shared, completion on an mbarrier.  No multicast.
+// The innermost coordinate must address a 16-byte boundary (callers only ever pass 0 there).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1,
+                                            int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_5d(void* smem_dst, const void* tmap, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3, int c4) {
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+
+// ------------------------------------------------------------------------------------------
+// Warp-level tensor-core MMA (used by the bandwidth-bound decode kernel, where the tile shape is
+// 16 tokens x 8 heads and a CTA-wide tcgen05 tile would not fit the problem).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_m16n8k16_f16f32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                    uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// 8x8 b16 transpose across the warp: lane (g,t) passes row g, columns 2t,2t+1 and receives
+// row g, columns 2t,2t+1 of the transposed matrix.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) {
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) {
+    return *reinterpret_cast<__half2*>(&u);
+}
+
+// Two biased bytes -> half2 of the signed codes.  `x` holds codes XOR 0x80 (i.e. code + 128 as an
+// unsigned byte).  0x6400 | u is the half 1024 + u, so subtracting 1152 yields the code, exactly.
+template <uint32_t SEL>
+__device__ __forceinline__ __half2 biased_bytes_to_half2(uint32_t x) {
+    const uint32_t h = prmt(x, 0x64646464u, SEL);
+    return __hsub2(u32_as_h2(h), u32_as_h2(0x64806480u));
+}
+
+// ------------------------------------------------------------------------------------------
+// INT8 group quantiser: 8 halves -> 8 codes + one fp16 scale.
+//   a = max|x|, s16 = fp16_rn(a / 127.0f), c = s == 0 ? 0 : clamp(rint(x / float(s16)), -127, 127)
+// IEEE division and round-half-even throughout: the file must be compiled without fast-math so
+// that codes and scales are reproducible bit for bit on any IEEE host.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void quant_group8(const uint4 in, uint2& codes, __half& scale16) {
+    const __half2* h2 = reinterpret_cast<const __half2*>(&in);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h2[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+    float a = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        a = fmaxf(a, fabsf(v[i]));  // fmaxf drops a NaN operand, like `if (m > a) a = m`
+    }
+    scale16 = __float2half_rn(__fdiv_rn(a, 127.0f));
+    const float s = __half2float(scale16);
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float q = 0.0f;
+        if (s != 0.0f) {
+            q = rintf(__fdiv_rn(v[i], s));
+            if (!(q >= -127.0f)) {
+                q = -127.0f;
+            }
+            if (q > 127.0f) {
+                q = 127.0f;
+            }
+        }
+        const int c = static_cast<int>(q);
+        w[i >> 2] |= (static_cast<uint32_t>(c) & 0xffu) << (8 * (i & 3));
+    }
+    codes = make_uint2(w[0], w[1]);
+}
+
+// Cache geometry shared by all kernels: element offset of channel 0 of (row, kv, head) in `cache`;
+// the scale tensor uses the same strides divided by 8.
+struct CacheGeom {
+    int64_t stride_s, stride_l, stride_h, stride_kv;  // elements of `cache`
+    int64_t layer_idx;
+    int64_t cachestart_stride_b;
+    int32_t cache_mode;
+    int32_t page_size;
+};
+
+__device__ __forceinline__ int64_t cache_row(const CacheGeom& g, const int64_t* __restrict__ cachestarts, int64_t b,
+                                             int64_t pos) {
+    if (g.cache_mode == 0) {
+        return cachestarts[b] + pos;
+    }
+    return cachestarts[b * g.cachestart_stride_b + pos / g.page_size] + pos % g.page_size;
+}
+
+__device__ __forceinline__ int64_t cache_offset(const CacheGeom& g, int64_t row, int kv, int head) {
+    return row * g.stride_s + g.layer_idx * g.stride_l + kv * g.stride_kv + head * g.stride_h;
+}
+
+}  // namespace pplb200

@@ -1,0 +1,72 @@
+// Host-side declarations shared by the translation units of the library: one launcher per kernel
+// family, the launch counter and the post-launch error check.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ppl_nn_b200.h"
+
+namespace pplb200 {
+
+struct CacheGeom;
+
+// cudaGetLastError() after a launch -> PPLB200_SUCCESS / PPLB200_DEVICE_RUNTIME_ERROR (logged to
+// stderr with the kernel name), and bumps the launch counter.  Mirrors what ppl.nn does after every
+// kernel (src/ppl/nn/engines/llm_cuda/kernel.cc:179-185).
+int check_launch(const char* kernel_name);
+
+// Properties of the current device, cached per device id.
+struct DeviceInfo {
+    int device_id;
+    int sm_count;
+    int cc_major;
+    int cc_minor;
+    int max_smem_optin;
+};
+int current_device_info(DeviceInfo* info);
+
+int launch_kv_append(const pplb200_attn_params& p, const CacheGeom& geom, const void* cur_k, const void* cur_v,
+                     const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos, void* cache,
+                     void* scale, int sm_count, cudaStream_t stream);
+
+int launch_kv_gather_dequant(const pplb200_attn_params& p, const CacheGeom& geom, const int64_t* kvstarts,
+                             const int64_t* cachestarts, const void* cache, const void* scale, int64_t total_kv,
+                             void* key_out, void* value_out, int sm_count, cudaStream_t stream);
+
+// ---- decode (split-k over the INT8 cache) ------------------------------------------------------
+// Host-side plan: pure function of the params and the SM count, used both for the workspace size
+// and for the launch, so the two always agree.
+struct DecodePlan {
+    int64_t chunk_tokens;      // tokens per split (a multiple of 64)
+    int64_t max_splits;        // ceil(max_kvlen / chunk_tokens)
+    int32_t octets;            // ceil(group / 8): query-head octets per kv head
+    int32_t head_warps;        // warps of a CTA that work on different (kv head, octet) pairs
+    int32_t token_warps;       // warps of a CTA that share one pair and split its tokens
+    int64_t num_vheads;        // num_kv_heads * octets
+    int64_t num_hsets;         // num_vheads / head_warps
+    int64_t grid;              // persistent CTAs
+    // workspace layout (byte offsets)
+    uint64_t off_status, off_counter, off_split_starts, off_part_ml, off_part_o, bytes;
+};
+int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* plan);
+
+int launch_decode(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan, const void* query,
+                  const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos, const void* cache,
+                  const void* scale, void* workspace, void* attn_output, cudaStream_t stream);
+
+// ---- prefill (causal, tcgen05) -------------------------------------------------------------------
+struct PrefillPlan {
+    int64_t prefill_batches;
+    int64_t q_tiles_per_seq;   // ceil(max_seqlen / 128)
+    int64_t kv_rows_bound;     // rows of the dequantised fp16 K/V staging buffer (cache prefill only)
+    uint64_t off_kv_stage, off_stage_starts, bytes;  // relative to the prefill region of the workspace
+};
+int make_prefill_plan(const pplb200_attn_params& p, PrefillPlan* plan);
+
+int launch_prefill(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan, const void* query,
+                   const void* cur_k, const void* cur_v, const int64_t* seqstarts, const int64_t* cachestarts,
+                   const int64_t* start_pos, const void* cache, const void* scale, void* workspace_region,
+                   uint32_t* status_word, void* attn_output, cudaStream_t stream);
+
+}  // namespace pplb200

@@ -1,0 +1,223 @@
+"""GPU parity: the CUDA path, called through the C ABI, against the CPU oracle on the same seeded
+inputs.  Cache codes and scales must be bit-exact; attention must be within 2e-3 max-abs and 1e-3
+mean-abs (the tolerance the task states for this floating-point kernel)."""
+from dataclasses import replace
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS = 2e-3
+MEAN_ABS = 1e-3
+
+
+@pytest.fixture(scope="module")
+def torch_dev(built_lib):
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("a test marked gpu ran without a CUDA device")
+    assert built_lib.device_ready(), "the CUDA library has no sm_100a code for this device"
+    return torch.device("cuda:0")
+
+
+def _t(a, dev):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def run_case(orc, dev, hc, *, layout=0, num_layer=1, layer_idx=0, split_k=1, cache_prefill=False,
+             check_attention=True):
+    """History append + one MultiHeadCacheAttention call on both sides; returns the error stats."""
+    import torch
+    from ppl_nn_b200 import ops, workloads
+
+    idx, hidx = hc.index, hc.hist_index
+    Hq, Hkv, Dh = hc.num_heads, hc.num_kv_heads, hc.spec.head_dim
+    page = idx.page_size
+    cshape, sshape = workloads.cache_shapes(layout, idx.max_tokens, num_layer, Hkv, Dh)
+    kw = dict(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=idx.batch, max_tokens=idx.max_tokens,
+              num_layer=num_layer, layer_idx=layer_idx, cache_layout=layout, cache_mode=1 if page else 0,
+              page_size=page or 128, cachestart_stride_b=idx.cachestarts.shape[1] if page else 0,
+              is_causal=int(hc.spec.is_causal), enable_cache_prefill=int(cache_prefill))
+    # ---- oracle ----
+    o_cache = np.zeros(cshape, dtype=np.int8)
+    o_scale = np.zeros(sshape, dtype=np.float16)
+    orc.kv_append(orc.desc(decoding_batches=0, **kw), hc.hist_key, hc.hist_value, hidx.seqstarts, hidx.cachestarts,
+                  hidx.start_pos, o_cache, o_scale)
+    want = orc.mhca(orc.desc(decoding_batches=idx.decoding_batches, **kw), hc.query, hc.current_key,
+                    hc.current_value, idx.seqstarts, idx.cachestarts, idx.start_pos, o_cache, o_scale)
+    # ---- CUDA ----
+    cache = torch.zeros(cshape, dtype=torch.int8, device=dev)
+    scale = torch.zeros(sshape, dtype=torch.float16, device=dev)
+    kvc = ops.KeyValueCache(ops.KeyValueCacheParam(num_layer=num_layer, layer_idx=layer_idx, quant_bit=8,
+                                                   cache_layout=layout, cache_mode=1 if page else 0,
+                                                   page_size=page or 128))
+    if hidx.total_tokens > 0:
+        kvc.forward(_t(hc.hist_key, dev), _t(hc.hist_value, dev), _t(hidx.seqstarts, dev), _t(hidx.kvstarts, dev),
+                    _t(hidx.cachestarts, dev), _t(hidx.start_pos, dev), hidx.max_seqlen, hidx.max_kvlen, cache, scale,
+                    total_kv=0)
+    op = ops.MultiHeadCacheAttention(
+        ops.MultiHeadCacheAttentionParam(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, num_layer=num_layer,
+                                         layer_idx=layer_idx, quant_bit=8, cache_layout=layout,
+                                         cache_mode=1 if page else 0, page_size=page or 128,
+                                         is_causal=hc.spec.is_causal),
+        ops.EngineConfig(enable_cache_prefill=cache_prefill, specify_decoding_attn_split_k=split_k))
+    got = op.forward(_t(hc.query, dev), _t(hc.current_key, dev), _t(hc.current_value, dev), _t(idx.seqstarts, dev),
+                     _t(idx.kvstarts, dev), _t(idx.cachestarts, dev), _t(idx.start_pos, dev), idx.decoding_batches,
+                     idx.max_seqlen, idx.max_kvlen, cache, scale)
+    assert op.device_status() == 0
+    np.testing.assert_array_equal(cache.cpu().numpy(), o_cache, err_msg="INT8 cache codes differ")
+    np.testing.assert_array_equal(scale.cpu().numpy().view(np.uint16), o_scale.view(np.uint16),
+                                  err_msg="fp16 cache scales differ")
+    got = got.cpu().numpy().astype(np.float32)
+    assert np.isfinite(got).all()
+    err = np.abs(got - want.astype(np.float32))
+    if check_attention:
+        per_seq = [float(err[idx.seqstarts[b]:idx.seqstarts[b + 1]].max()) for b in range(idx.batch)]
+        worst = int(np.argmax(per_seq))
+        assert err.max() <= MAX_ABS, (f"max-abs {err.max():.3e}; worst sequence {worst} kvlen "
+                                      f"{int(idx.kvlens[worst])} seqlen {int(idx.seqlens[worst])}")
+        assert err.mean() <= MEAN_ABS
+    return err, op
+
+
+def _spec(**kw):
+    from ppl_nn_b200 import workloads
+    base = workloads.Spec("custom", 8, 8, 128, 4, 1, 64)
+    return replace(base, **kw)
+
+
+def test_cfg1_tiny_decode(orc, torch_dev, pkg):
+    from ppl_nn_b200 import workloads
+    hc = workloads.host_case(workloads.SPECS["cfg1_tiny"])
+    err, _ = run_case(orc, torch_dev, hc)
+    # and against the committed golden output of the oracle
+    from pathlib import Path
+    g = Path(__file__).resolve().parent / "golden" / "attn_output-4_8_64-fp16.dat"
+    want = np.fromfile(g, dtype=np.float16).reshape(4, 8, 64)
+    assert err.shape == want.shape
+
+
+@pytest.mark.parametrize("layout,num_layer,layer_idx", [(0, 1, 0), (3, 1, 0), (0, 3, 1), (3, 2, 1)])
+def test_cfg2_mha_outlier_channels(orc, torch_dev, pkg, layout, num_layer, layer_idx):
+    from ppl_nn_b200 import workloads
+    spec = workloads.scaled(workloads.SPECS["cfg2_llama7b_decode"], seqs=24 / 256, length=0.25)
+    run_case(orc, torch_dev, workloads.host_case(spec), layout=layout, num_layer=num_layer, layer_idx=layer_idx)
+
+
+@pytest.mark.parametrize("world", [1, 2, 8])
+def test_cfg4_gqa8_kv_head_shards(orc, torch_dev, pkg, world):
+    """64 query / 8 kv heads, sharded by kv head: 8, 4 and 1 kv heads per rank exercise all three
+    warp arrangements of the decode kernel."""
+    from ppl_nn_b200 import workloads
+    spec = workloads.scaled(workloads.SPECS["cfg4_llama70b_decode"], seqs=32 / 512, length=0.25)
+    for rank in sorted({0, world - 1}):
+        run_case(orc, torch_dev, workloads.host_case(spec, rank=rank, world=world))
+
+
+@pytest.mark.parametrize("split_k", [0, 1, 2])
+def test_cfg5_long_context_split_k(orc, torch_dev, pkg, split_k):
+    from ppl_nn_b200 import workloads
+    spec = workloads.scaled(workloads.SPECS["cfg5_longctx"], seqs=6 / 16, length=1 / 16)
+    run_case(orc, torch_dev, workloads.host_case(spec), split_k=split_k)
+
+
+@pytest.mark.parametrize("hq,hkv,dh", [(8, 8, 128), (8, 2, 128), (4, 4, 64), (16, 1, 128), (6, 2, 64)])
+@pytest.mark.parametrize("split_k", [1, 2])
+def test_every_length_1_to_80(orc, torch_dev, pkg, hq, hkv, dh, split_k):
+    """Every kv length from 1 to 80 in one batch: every fill level of the 16-token tile, the 64-token
+    chunk boundary and one above/below it, for MHA, GQA 4, GQA 16 (two head octets) and GQA 3."""
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=hq, num_kv_heads=hkv, head_dim=dh, n_decode=80, kv_dist="list",
+                 kv_list=tuple(range(1, 81)), seed=21)
+    run_case(orc, torch_dev, workloads.host_case(spec), split_k=split_k)
+
+
+def test_split_boundaries(orc, torch_dev, pkg):
+    """Lengths on, one below and one above the split size that the heuristic picks."""
+    from ppl_nn_b200 import workloads
+    lens = (191, 192, 193, 300, 1, 255, 256, 257, 383, 384, 385)
+    spec = _spec(num_heads=8, num_kv_heads=2, head_dim=128, n_decode=len(lens), kv_dist="list", kv_list=lens, seed=22)
+    for split_k in (0, 2):
+        run_case(orc, torch_dev, workloads.host_case(spec), split_k=split_k)
+
+
+@pytest.mark.parametrize("page,layout", [(16, 0), (128, 0), (32, 3)])
+def test_paged_cache(orc, torch_dev, pkg, page, layout):
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=8, num_kv_heads=4, head_dim=128, n_decode=12, kv_lo=1, kv_hi=700, seed=23)
+    run_case(orc, torch_dev, workloads.host_case(spec, page_size=page), layout=layout, split_k=2)
+
+
+def test_append_adversarial_values_bit_exact(orc, torch_dev, pkg):
+    """+-65504, subnormals, zeros, -0.0, one outlier, all-equal, NaN and Inf groups."""
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=4, num_kv_heads=4, head_dim=64, n_decode=6, kv_dist="list", kv_list=(3, 9, 17, 33, 5, 64),
+                 seed=24)
+    hc = workloads.host_case(spec)
+    rng = np.random.default_rng(5)
+    for arr in (hc.hist_key, hc.hist_value, hc.current_key, hc.current_value):
+        flat = arr.reshape(-1, 8)
+        n = flat.shape[0]
+        flat[rng.integers(0, n, 40), rng.integers(0, 8, 40)] = np.float16(65504)
+        flat[rng.integers(0, n, 40), rng.integers(0, 8, 40)] = np.float16(-65504)
+        flat[rng.integers(0, n, 40)] = np.float16(6e-8)
+        flat[rng.integers(0, n, 40)] = np.float16(0)
+        flat[rng.integers(0, n, 40)] = np.float16(-0.0)
+        flat[rng.integers(0, n, 40)] = np.float16(0.37)
+        flat[rng.integers(0, n, 40), rng.integers(0, 8, 40)] *= np.float16(300)
+        flat[rng.integers(0, n, 10), rng.integers(0, 8, 10)] = np.float16("nan")
+        flat[rng.integers(0, n, 10), rng.integers(0, 8, 10)] = np.float16("inf")
+    import torch
+    from ppl_nn_b200 import ops
+    idx, hidx = hc.index, hc.hist_index
+    cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, 4, 64)
+    o_cache = np.zeros(cshape, dtype=np.int8)
+    o_scale = np.zeros(sshape, dtype=np.float16)
+    kw = dict(num_heads=4, num_kv_heads=4, head_dim=64, batch=idx.batch, max_tokens=idx.max_tokens)
+    orc.kv_append(orc.desc(decoding_batches=0, **kw), hc.hist_key, hc.hist_value, hidx.seqstarts, hidx.cachestarts,
+                  hidx.start_pos, o_cache, o_scale)
+    orc.kv_append(orc.desc(decoding_batches=idx.batch, **kw), hc.current_key, hc.current_value, idx.seqstarts,
+                  idx.cachestarts, idx.start_pos, o_cache, o_scale)
+    dev = torch_dev
+    cache = torch.zeros(cshape, dtype=torch.int8, device=dev)
+    scale = torch.zeros(sshape, dtype=torch.float16, device=dev)
+    kvc = ops.KeyValueCache(ops.KeyValueCacheParam(num_layer=1, layer_idx=0, quant_bit=8))
+    kvc.forward(_t(hc.hist_key, dev), _t(hc.hist_value, dev), _t(hidx.seqstarts, dev), _t(hidx.kvstarts, dev),
+                _t(hidx.cachestarts, dev), _t(hidx.start_pos, dev), hidx.max_seqlen, hidx.max_kvlen, cache, scale,
+                total_kv=0)
+    key, value = kvc.forward(_t(hc.current_key, dev), _t(hc.current_value, dev), _t(idx.seqstarts, dev),
+                             _t(idx.kvstarts, dev), _t(idx.cachestarts, dev), _t(idx.start_pos, dev), idx.max_seqlen,
+                             idx.max_kvlen, cache, scale)
+    np.testing.assert_array_equal(cache.cpu().numpy(), o_cache)
+    np.testing.assert_array_equal(scale.cpu().numpy().view(np.uint16), o_scale.view(np.uint16))
+    # the operator's key/value outputs: dequantised history, bit-exact (NaN patterns aside)
+    wk, wv = orc.kv_gather_dequant(orc.desc(decoding_batches=idx.batch, **kw), idx.kvstarts, idx.cachestarts, o_cache,
+                                   o_scale)
+    for got, want in ((key, wk), (value, wv)):
+        g = got.cpu().numpy()
+        assert g.shape == want.shape
+        nan = np.isnan(want)
+        np.testing.assert_array_equal(np.isnan(g), nan)
+        np.testing.assert_array_equal(g[~nan].view(np.uint16), want[~nan].view(np.uint16))
+
+
+def test_workspace_too_small_and_bad_params_are_rejected(torch_dev, built_lib, pkg):
+    import torch
+    from ppl_nn_b200 import capi, ops
+    op = ops.MultiHeadCacheAttention(ops.MultiHeadCacheAttentionParam(num_heads=8, num_kv_heads=8, head_dim=128,
+                                                                     num_layer=1, layer_idx=0, quant_bit=8))
+    p = op.make_params(batch=4, decoding_batches=4, max_seqlen=1, max_kvlen=100000, total_tokens=4, max_tokens=1 << 20)
+    rc, need = built_lib.mhca_workspace_size(p)
+    assert rc == capi.SUCCESS and need > 256
+    buf = torch.zeros(512, dtype=torch.uint8, device=torch_dev)
+    one = torch.zeros(64, dtype=torch.int64, device=torch_dev)
+    rc = built_lib.mhca_forward(p, one.data_ptr(), one.data_ptr(), one.data_ptr(), one.data_ptr(), one.data_ptr(),
+                                one.data_ptr(), one.data_ptr(), one.data_ptr(), one.data_ptr(), buf.data_ptr(), 256,
+                                one.data_ptr(), 0)
+    assert built_lib.status_str(rc) == "RC_OUT_OF_MEMORY"
+    rc = built_lib.mhca_forward(p, one.data_ptr(), one.data_ptr(), one.data_ptr(), one.data_ptr(), one.data_ptr(),
+                                one.data_ptr(), one.data_ptr(), one.data_ptr(), None, buf.data_ptr(), need,
+                                one.data_ptr(), 0)
+    assert built_lib.status_str(rc) == "RC_UNSUPPORTED"  # scale missing
