@@ -151,7 +151,8 @@ int pplb200_mhca_device_status(const void* workspace, void* stream, uint32_t* st
 enum {
     PPLB200_DEV_OK = 0,
     PPLB200_DEV_TMA_WAIT_TIMEOUT = 1,  /* a wait for a bulk-tensor copy ran out of iterations    */
-    PPLB200_DEV_MMA_WAIT_TIMEOUT = 2   /* a wait for a tensor-core commit ran out of iterations   */
+    PPLB200_DEV_MMA_WAIT_TIMEOUT = 2,  /* a wait for a tensor-core commit ran out of iterations   */
+    PPLB200_DEV_LENGTH_CLAMPED = 4     /* a sequence exceeded max_kvlen / max_seqlen and was cut   */
 };
 
 /* Name of a status code ("RC_SUCCESS", ...).  Never null. */
@@ -162,6 +163,23 @@ int pplb200_device_ready(void);
 
 /* Number of kernels launched by this library since load (all entry points).  For benchmarks. */
 uint64_t pplb200_launch_count(void);
+
+/*
+ * Measurement aid, in the spirit of the reference's PPLNN_ENABLE_KERNEL_PROFILING event pairs
+ * (src/ppl/nn/engines/llm_cuda/kernel.cc:93-160), but per CUDA kernel instead of per operator:
+ * while enabled, each launch of the kernel families below is bracketed by a pair of CUDA events
+ * recorded on the launching stream.  pplb200_profile_read() synchronises those events, returns
+ * the summed device time and the launch count of one family since the last read, and clears them.
+ * Off by default; not thread-safe against concurrent launches.
+ */
+enum {
+    PPLB200_KERNEL_APPEND = 0,   /* kv_append_i8g8_kernel   */
+    PPLB200_KERNEL_DECODE = 1,   /* decode_splitk_kernel    */
+    PPLB200_KERNEL_PREFILL = 2,  /* prefill_tcgen05_kernel  */
+    PPLB200_KERNEL_FAMILIES = 3
+};
+int pplb200_profile_enable(int enable);
+int pplb200_profile_read(int kernel_family, double* total_ms, uint64_t* launches);
 
 #ifdef __cplusplus
 }

@@ -40,7 +40,13 @@ EXPORTS = (
     "pplb200_status_str",
     "pplb200_device_ready",
     "pplb200_launch_count",
+    "pplb200_profile_enable",
+    "pplb200_profile_read",
 )
+
+KERNEL_APPEND = 0
+KERNEL_DECODE = 1
+KERNEL_PREFILL = 2
 
 
 class AttnParams(ctypes.Structure):
@@ -103,6 +109,11 @@ class Library:
         d.pplb200_device_ready.argtypes = []
         d.pplb200_launch_count.restype = ctypes.c_uint64
         d.pplb200_launch_count.argtypes = []
+        d.pplb200_profile_enable.restype = ctypes.c_int
+        d.pplb200_profile_enable.argtypes = [ctypes.c_int]
+        d.pplb200_profile_read.restype = ctypes.c_int
+        d.pplb200_profile_read.argtypes = [ctypes.c_int, ctypes.POINTER(ctypes.c_double),
+                                           ctypes.POINTER(ctypes.c_uint64)]
 
     # ---- helpers ------------------------------------------------------------------------
     def status_str(self, code: int) -> str:
@@ -117,6 +128,15 @@ class Library:
 
     def launch_count(self) -> int:
         return int(self.dll.pplb200_launch_count())
+
+    def profile_enable(self, on: bool) -> None:
+        self.check("pplb200_profile_enable", self.dll.pplb200_profile_enable(1 if on else 0))
+
+    def profile_read(self, family: int) -> tuple[float, int]:
+        """(summed device milliseconds, launches) of one kernel family since the last read."""
+        ms, n = ctypes.c_double(0), ctypes.c_uint64(0)
+        self.check("pplb200_profile_read", self.dll.pplb200_profile_read(family, ctypes.byref(ms), ctypes.byref(n)))
+        return float(ms.value), int(n.value)
 
     # ---- raw entry points: return the status code -----------------------------------------
     def fill_cache_strides(self, p: AttnParams) -> int:

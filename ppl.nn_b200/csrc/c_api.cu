@@ -5,6 +5,8 @@
 
 #include <atomic>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "common.cuh"
 #include "launch.h"
@@ -21,6 +23,39 @@ int check_launch(const char* kernel_name) {
         return PPLB200_DEVICE_RUNTIME_ERROR;
     }
     return PPLB200_SUCCESS;
+}
+
+// ---- optional per-kernel event timing ------------------------------------------------------------
+struct ProfileState {
+    std::mutex mu;
+    bool enabled = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending[PPLB200_KERNEL_FAMILIES];
+};
+static ProfileState& profile_state() {
+    static ProfileState s;
+    return s;
+}
+
+KernelTimer::KernelTimer(int family, cudaStream_t stream) : stream_(stream), stop_(nullptr) {
+    ProfileState& ps = profile_state();
+    if (!ps.enabled) {
+        return;
+    }
+    cudaEvent_t start = nullptr;
+    if (cudaEventCreate(&start) != cudaSuccess || cudaEventCreate(&stop_) != cudaSuccess) {
+        (void)cudaGetLastError();
+        stop_ = nullptr;
+        return;
+    }
+    cudaEventRecord(start, stream_);
+    std::lock_guard<std::mutex> lock(ps.mu);
+    ps.pending[family].emplace_back(start, stop_);
+}
+
+KernelTimer::~KernelTimer() {
+    if (stop_) {
+        cudaEventRecord(stop_, stream_);
+    }
 }
 
 int current_device_info(DeviceInfo* info) {
@@ -372,6 +407,40 @@ int pplb200_device_ready(void) {
 
 uint64_t pplb200_launch_count(void) {
     return g_launches.load(std::memory_order_relaxed);
+}
+
+int pplb200_profile_enable(int enable) {
+    ProfileState& ps = profile_state();
+    std::lock_guard<std::mutex> lock(ps.mu);
+    ps.enabled = enable != 0;
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_profile_read(int kernel_family, double* total_ms, uint64_t* launches) {
+    if (kernel_family < 0 || kernel_family >= PPLB200_KERNEL_FAMILIES || !total_ms || !launches) {
+        return PPLB200_INVALID_VALUE;
+    }
+    ProfileState& ps = profile_state();
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> taken;
+    {
+        std::lock_guard<std::mutex> lock(ps.mu);
+        taken.swap(ps.pending[kernel_family]);
+    }
+    double sum = 0.0;
+    int rc = PPLB200_SUCCESS;
+    for (auto& pr : taken) {
+        float ms = 0.0f;
+        if (cudaEventSynchronize(pr.second) != cudaSuccess || cudaEventElapsedTime(&ms, pr.first, pr.second) != cudaSuccess) {
+            (void)cudaGetLastError();
+            rc = PPLB200_DEVICE_RUNTIME_ERROR;
+        }
+        sum += ms;
+        cudaEventDestroy(pr.first);
+        cudaEventDestroy(pr.second);
+    }
+    *total_ms = sum;
+    *launches = taken.size();
+    return rc;
 }
 
 }  // extern "C"

@@ -710,8 +710,11 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
         }
         attr_set = true;
     }
-    decode_splitk_kernel<DH><<<static_cast<unsigned>(plan.grid), kThreads, T::kSmemBytes, stream>>>(tm_codes, tm_scales,
-                                                                                                     a);
+    {
+        KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
+        decode_splitk_kernel<DH><<<static_cast<unsigned>(plan.grid), kThreads, T::kSmemBytes, stream>>>(
+            tm_codes, tm_scales, a);
+    }
     rc = check_launch("decode_splitk_kernel");
     if (rc != PPLB200_SUCCESS) {
         return rc;

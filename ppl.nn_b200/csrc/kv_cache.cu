@@ -111,6 +111,7 @@ int launch_kv_append(const pplb200_attn_params& p, const CacheGeom& geom, const 
     }
     const int64_t work = p.total_tokens * 2 * p.num_kv_heads * (p.head_dim / 8);
     const int grid = grid_for(work, 256, sm_count);
+    KernelTimer timer(PPLB200_KERNEL_APPEND, stream);
     kv_append_i8g8_kernel<<<grid, 256, 0, stream>>>(
         static_cast<const __half*>(cur_k), static_cast<const __half*>(cur_v), seqstarts, cachestarts, start_pos,
         static_cast<int8_t*>(cache), static_cast<__half*>(scale), geom, p.batch, p.total_tokens, p.num_kv_heads,

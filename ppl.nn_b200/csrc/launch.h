@@ -16,6 +16,18 @@ struct CacheGeom;
 // kernel (src/ppl/nn/engines/llm_cuda/kernel.cc:179-185).
 int check_launch(const char* kernel_name);
 
+// Event bracketing of one kernel launch for pplb200_profile_*: a no-op unless profiling is on.
+// Usage: { KernelTimer t(PPLB200_KERNEL_DECODE, stream); kernel<<<...>>>(...); }
+class KernelTimer {
+public:
+    KernelTimer(int family, cudaStream_t stream);
+    ~KernelTimer();
+
+private:
+    cudaStream_t stream_;
+    cudaEvent_t stop_;
+};
+
 // Properties of the current device, cached per device id.
 struct DeviceInfo {
     int device_id;

@@ -1,22 +1,689 @@
-// placeholder while the tcgen05 prefill kernel is being written
+// Causal prefill attention for the ragged batch tail (sequences [decoding_batches, batch)), as a
+// dense contraction on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators, operands
+// staged in shared memory by TMA (no multicast), fp16 inputs, fp32 accumulation.
+//
+// One CTA computes a 128-row query tile of one (sequence, query head):
+//   warp 0      TMA producer: the Q tile once, then K/V tiles of 128 rows through a 2-stage ring
+//   warp 1      allocates TMEM and issues the MMAs (one lane): S = Q K^T into one of two 128-column
+//               TMEM buffers, then O += P V into a third accumulator; completion is reported to
+//               mbarriers with tcgen05.commit
+//   warps 2..5  128 softmax threads, one query row each (TMEM lane = row): read S with tcgen05.ld,
+//               causal mask, running maximum in the exp2 domain (the O accumulator is rescaled in
+//               TMEM only when the maximum grew by more than 2^8), write P as fp16 into shared memory
+//               in the 128-byte-swizzled K-major layout the MMA expects, and finally normalise O and
+//               store fp16 rows.
+// K/V come from this call's fp16 current_key/current_value (the default), or, with
+// enable_cache_prefill, from an fp16 staging copy of the INT8 cache rows (history included) that a
+// dequantising gather writes into the workspace first.
+//
+// Every mbarrier wait is bounded.  When one gives up, the CTA sets an abort flag that all its other
+// waits observe, records a status code, drains its own outstanding copies (bounded as well), frees its
+// TMEM and returns.
+#include <cuda.h>
+
 #include "common.cuh"
 #include "launch.h"
+#include "tensor_map.h"
 
 namespace pplb200 {
 
+namespace {
+
+constexpr int kBlockM = 128;   // query rows per CTA
+constexpr int kBlockN = 128;   // kv rows per tile
+constexpr int kThreads = 192;  // 6 warps
+constexpr int kKvStages = 2;
+constexpr float kNegBig = -1.0e30f;
+constexpr float kRescaleSlack = 8.0f;
+
+template <int DH>
+struct PTraits {
+    static constexpr int kColBlocks = DH / 64;                  // 64-element (128-byte) swizzled column blocks
+    static constexpr int kBlockBytes = 128 * 128;               // one [128 rows][64 halves] block
+    static constexpr int kQBytes = kColBlocks * kBlockBytes;    // Q tile
+    static constexpr int kKVBytes = kColBlocks * kBlockBytes;   // one K (or V) tile
+    static constexpr int kPBytes = 2 * kBlockBytes;             // P tile: 128 x 128 halves
+    static constexpr int kSmemBytes = kQBytes + 2 * kKvStages * kKVBytes + kPBytes + 1024;
+    static constexpr uint32_t kTmemCols = 512;                  // S0 | S1 | O  (power of two >= 256 + DH)
+    static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+};
+
+struct PrefillArgs {
+    __half* out;
+    const int64_t* seqstarts;
+    const int64_t* start_pos;
+    const int64_t* stage_starts;  // cache prefill: first staging row of each prefill sequence
+    uint32_t* status;
+    int64_t max_seqlen;
+    int32_t decoding_batches;
+    int32_t num_heads;
+    int32_t group;
+    int32_t cache_prefill;
+    float scale_log2;
+};
+
+struct Barriers {
+    uint64_t q_full;
+    uint64_t k_full[kKvStages];
+    uint64_t v_full[kKvStages];
+    uint64_t kv_empty[kKvStages];
+    uint64_t s_full[2];
+    uint64_t p_full;
+    uint64_t o_done;
+};
+
+// ---- tcgen05 wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem], M = 128, K = 16, fp16 inputs, fp32 accumulate
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+        "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
+//   K-major operand ([rows][64 halves] blocks): lbo is unused (1), sbo = 1024 (8 rows of 128 bytes).
+//   MN-major operand (V as [kv rows][64 channels]): lbo = bytes between 64-channel blocks,
+//   sbo = 1024 (8 kv rows of 128 bytes).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor for kind::f16: fp16 A and B, fp32 D, M = 128.
+__host__ __device__ constexpr uint32_t instr_desc_f16(int n, bool b_mn_major) {
+    return (1u << 4) |                                 // D format: F32
+           (0u << 7) | (0u << 10) |                    // A, B format: F16
+           (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |  // A K-major; B K- or MN-major
+           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
+}
+
+// Bounded wait that also gives up as soon as another thread of the CTA has given up.
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              uint32_t* status, uint32_t code) {
+    for (uint32_t i = 0; i < kMaxWaitPolls; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        if ((i & 255u) == 255u && *abort_flag) {
+            return false;
+        }
+    }
+    *abort_flag = 1;
+    atomicOr(status, code);
+    return false;
+}
+
+template <int DH>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                       const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
+    using T = PTraits<DH>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = smem;
+    uint8_t* sK = sQ + T::kQBytes;
+    uint8_t* sV = sK + kKvStages * T::kKVBytes;
+    uint8_t* sP = sV + kKvStages * T::kKVBytes;
+    __shared__ Barriers bars;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // ---- which tile ----
+    const int pb = blockIdx.y;
+    const int b = a.decoding_batches + pb;
+    const int64_t seq0 = a.seqstarts[b];
+    int64_t seqlen = a.seqstarts[b + 1] - seq0;
+    if (seqlen > a.max_seqlen) {
+        seqlen = a.max_seqlen;
+        if (threadIdx.x == 0 && blockIdx.x == 0) {
+            atomicOr(a.status, kDevLengthClamped);
+        }
+    }
+    const int n_qt = static_cast<int>((seqlen + kBlockM - 1) / kBlockM);
+    const int qt_rev = blockIdx.x / a.num_heads;
+    if (qt_rev >= n_qt) {
+        return;  // uniform for the CTA, before any barrier or TMEM allocation
+    }
+    const int qt = n_qt - 1 - qt_rev;  // longest (latest) query tiles first
+    const int head = blockIdx.x - qt_rev * a.num_heads;
+    const int kvh = head / a.group;
+    const int64_t i0 = static_cast<int64_t>(qt) * kBlockM;
+    const int rows_valid = (seqlen - i0) < kBlockM ? static_cast<int>(seqlen - i0) : kBlockM;
+    const int64_t hist = a.cache_prefill ? a.start_pos[b] : 0;
+    const int64_t kv_visible = hist + i0 + rows_valid;  // kv positions the last valid row may see
+    const int n_kv = static_cast<int>((kv_visible + kBlockN - 1) / kBlockN);
+    const int64_t q_row0 = seq0 + i0;
+    const int64_t kv_row0 = a.cache_prefill ? a.stage_starts[pb] : seq0;
+
+    // ---- setup ----
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        mbar_init(&bars.q_full, 1);
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(&bars.k_full[s], 1);
+            mbar_init(&bars.v_full[s], 1);
+            mbar_init(&bars.kv_empty[s], 1);
+        }
+        mbar_init(&bars.s_full[0], 1);
+        mbar_init(&bars.s_full[1], 1);
+        mbar_init(&bars.p_full, 128);
+        mbar_init(&bars.o_done, 1);
+        mbar_fence_init();
+        tma_prefetch_desc(&tm_q);
+        tma_prefetch_desc(&tm_k);
+        tma_prefetch_desc(&tm_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_slot, T::kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        // =========================== TMA producer ===========================
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&bars.q_full, T::kQBytes);
+#pragma unroll
+            for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                tma_load_3d(sQ + cb * T::kBlockBytes, &tm_q, &bars.q_full, cb * 64, head, static_cast<int>(q_row0));
+            }
+            int issued = 0;
+            for (int j = 0; j < n_kv; ++j) {
+                const int s = j % kKvStages;
+                if (j >= kKvStages) {
+                    if (!wait_or_abort(&bars.kv_empty[s], ((j / kKvStages) - 1) & 1, abort_flag, a.status,
+                                       kDevMmaTimeout)) {
+                        break;
+                    }
+                }
+                const int row = static_cast<int>(kv_row0 + static_cast<int64_t>(j) * kBlockN);
+                mbar_arrive_expect_tx(&bars.k_full[s], T::kKVBytes);
+#pragma unroll
+                for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                    tma_load_3d(sK + s * T::kKVBytes + cb * T::kBlockBytes, &tm_k, &bars.k_full[s], cb * 64, kvh, row);
+                }
+                mbar_arrive_expect_tx(&bars.v_full[s], T::kKVBytes);
+#pragma unroll
+                for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                    tma_load_3d(sV + s * T::kKVBytes + cb * T::kBlockBytes, &tm_v, &bars.v_full[s], cb * 64, kvh, row);
+                }
+                issued = j + 1;
+            }
+            if (*abort_flag) {
+                // drain: every copy this thread issued must have landed before the CTA may exit
+                mbar_wait_bounded(&bars.q_full, 0);
+                for (int j = issued > kKvStages ? issued - kKvStages : 0; j < issued; ++j) {
+                    mbar_wait_bounded(&bars.k_full[j % kKvStages], (j / kKvStages) & 1);
+                    mbar_wait_bounded(&bars.v_full[j % kKvStages], (j / kKvStages) & 1);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // =========================== MMA issuer ===========================
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = instr_desc_f16(kBlockN, false);
+            constexpr uint32_t idesc_pv = instr_desc_f16(DH, true);
+            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            auto issue_qk = [&](int j) {
+                const int s = j % kKvStages;
+                const uint32_t k_addr = smem_u32(sK + s * T::kKVBytes);
+                const uint32_t d = tmem_base + ((j & 1) ? T::kColS1 : T::kColS0);
+#pragma unroll
+                for (int cb = 0; cb < T::kColBlocks; ++cb) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint32_t off = cb * T::kBlockBytes + k * 32;
+                        tc_mma_f16(d, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024),
+                                   idesc_qk, (cb | k) ? 1u : 0u);
+                    }
+                }
+                tc_commit(&bars.s_full[j & 1]);
+            };
+            bool ok = wait_or_abort(&bars.q_full, 0, abort_flag, a.status, kDevTmaTimeout) &&
+                      wait_or_abort(&bars.k_full[0], 0, abort_flag, a.status, kDevTmaTimeout);
+            if (ok) {
+                tc_fence_after();
+                issue_qk(0);
+            }
+            for (int j = 0; ok && j < n_kv; ++j) {
+                const int s = j % kKvStages;
+                if (j + 1 < n_kv) {
+                    ok = wait_or_abort(&bars.k_full[(j + 1) % kKvStages], ((j + 1) / kKvStages) & 1, abort_flag, a.status,
+                                       kDevTmaTimeout);
+                    if (!ok) {
+                        break;
+                    }
+                    tc_fence_after();
+                    issue_qk(j + 1);
+                }
+                ok = wait_or_abort(&bars.p_full, j & 1, abort_flag, a.status, kDevMmaTimeout) &&
+                     wait_or_abort(&bars.v_full[s], (j / kKvStages) & 1, abort_flag, a.status, kDevTmaTimeout);
+                if (!ok) {
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(sV + s * T::kKVBytes);
+                const uint32_t d = tmem_base + T::kColO;
+#pragma unroll
+                for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                    // P: K-major, kv index = 16 ks -> column block ks / 4, 32-byte step ks % 4
+                    const uint64_t pa = smem_desc_sw128(p_addr + (ks >> 2) * T::kBlockBytes + (ks & 3) * 32, 16, 1024);
+                    // V: MN-major, kv rows 16 ks .. 16 ks + 15 of every 64-channel block
+                    const uint64_t vb = smem_desc_sw128(v_addr + ks * 2048, T::kBlockBytes, 1024);
+                    tc_mma_f16(d, pa, vb, idesc_pv, (j | ks) ? 1u : 0u);
+                }
+                tc_commit(&bars.kv_empty[s]);
+                tc_commit(&bars.o_done);
+            }
+        }
+    } else {
+        // =========================== softmax / epilogue ===========================
+        const int lane_group = warp & 3;          // TMEM lanes this warp may touch: 32 * (warp % 4) ..
+        const int r = lane_group * 32 + lane;     // query row of this thread within the tile
+        const uint32_t t_lane = static_cast<uint32_t>(lane_group * 32) << 16;
+        float m_ref = kNegBig, l_sum = 0.0f;
+        bool ok = true;
+        for (int j = 0; ok && j < n_kv; ++j) {
+            ok = wait_or_abort(&bars.s_full[j & 1], (j >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+            if (!ok) {
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t_s = tmem_base + t_lane + ((j & 1) ? T::kColS1 : T::kColS0);
+            // columns of this tile that row r may see: col <= limit
+            const int64_t lim64 = hist + i0 + r - static_cast<int64_t>(j) * kBlockN;
+            const int limit = lim64 > kBlockN ? kBlockN : (lim64 < -1 ? -1 : static_cast<int>(lim64));
+            // pass 1: row maximum of the visible scores
+            float mx = kNegBig;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_s + c * 32, v);
+                tmem_wait_ld();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float s = __uint_as_float(v[e]);
+                    mx = (c * 32 + e <= limit) ? fmaxf(mx, s) : mx;
+                }
+            }
+            mx *= a.scale_log2;  // scale_log2 > 0, so the maximum commutes with the scaling
+            // P and O are free again once the previous P V has completed
+            if (j > 0) {
+                ok = wait_or_abort(&bars.o_done, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                if (!ok) {
+                    break;
+                }
+                tc_fence_after();
+            }
+            const bool grow = mx > m_ref + kRescaleSlack;
+            if (__any_sync(0xffffffffu, grow)) {
+                const float m_new = fmaxf(m_ref, mx);
+                const float f = ex2_approx(m_ref - m_new);
+                m_ref = m_new;
+                l_sum *= f;
+                if (j > 0) {
+                    const uint32_t t_o = tmem_base + t_lane + T::kColO;
+#pragma unroll
+                    for (int c = 0; c < DH / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(t_o + c * 32, v);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
+                        }
+                        tmem_st32(t_o + c * 32, v);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // pass 2: P = exp2(s * scale - m_ref), fp16, into the swizzled K-major P tile
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_s + c * 32, v);
+                tmem_wait_ld();
+                uint32_t packed[16];
+#pragma unroll
+                for (int e = 0; e < 32; e += 2) {
+                    float p0 = ex2_approx(__uint_as_float(v[e]) * a.scale_log2 - m_ref);
+                    float p1 = ex2_approx(__uint_as_float(v[e + 1]) * a.scale_log2 - m_ref);
+                    p0 = (c * 32 + e <= limit) ? p0 : 0.0f;
+                    p1 = (c * 32 + e + 1 <= limit) ? p1 : 0.0f;
+                    l_sum += p0 + p1;
+                    packed[e >> 1] = h2_as_u32(__floats2half2_rn(p0, p1));
+                }
+                // columns 32c .. 32c+31 = 16-byte chunks 4c .. 4c+3 of the row; column block (4c)/8
+                uint8_t* prow = sP + (c >> 1) * T::kBlockBytes + r * 128;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + chunk * 16) =
+                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                }
+            }
+            // S buffer fully read (TMEM) and P fully written (shared, generic proxy): publish both
+            tc_fence_before();
+            fence_proxy_async_smem();
+            mbar_arrive(&bars.p_full);
+        }
+        // ---- epilogue: O / l -> fp16 rows ----
+        if (ok) {
+            ok = wait_or_abort(&bars.o_done, (n_kv - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+        }
+        if (ok) {
+            tc_fence_after();
+            const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+            const uint32_t t_o = tmem_base + t_lane + T::kColO;
+            __half* dst = a.out + ((q_row0 + r) * a.num_heads + head) * DH;
+#pragma unroll
+            for (int c = 0; c < DH / 32; ++c) {
+                uint32_t v[32];
+                tmem_ld32(t_o + c * 32, v);
+                tmem_wait_ld();
+                if (r < rows_valid) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        uint4 o4;
+                        o4.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv));
+                        o4.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv));
+                        o4.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv));
+                        o4.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv));
+                        *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o4;
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- teardown ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, T::kTmemCols);
+    }
+}
+
+// Prefix sum of the (128-row padded) kv lengths of the prefill sequences: first staging row of each.
+__global__ void prefill_stage_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
+                                          int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen,
+                                          int64_t* __restrict__ stage_starts) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int64_t acc = 0;
+        for (int32_t i = 0; i < prefill_batches; ++i) {
+            const int32_t b = decoding_batches + i;
+            int64_t n = start_pos[b] + (seqstarts[b + 1] - seqstarts[b]);
+            n = n > max_kvlen ? max_kvlen : n;
+            stage_starts[i] = acc;
+            acc += (n + kBlockN - 1) / kBlockN * kBlockN;
+        }
+        stage_starts[prefill_batches] = acc;
+    }
+}
+
+// Dequantise the cache rows of the prefill sequences (history and this call's tokens) into fp16
+// staging tensors [rows, Hkv, Dh]; pad rows up to the next multiple of 128 are zeroed.
+__global__ void __launch_bounds__(256)
+prefill_stage_dequant_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
+                             const int64_t* __restrict__ cachestarts, const int64_t* __restrict__ stage_starts,
+                             const int8_t* __restrict__ cache, const __half* __restrict__ scale,
+                             __half* __restrict__ k_stage, __half* __restrict__ v_stage, CacheGeom geom,
+                             int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen, int num_kv_heads,
+                             int head_dim) {
+    const int groups_per_head = head_dim >> 3;
+    const int64_t groups_per_tensor_row = static_cast<int64_t>(num_kv_heads) * groups_per_head;
+    const int64_t groups_per_token = 2 * groups_per_tensor_row;
+    const int64_t total_rows = stage_starts[prefill_batches];
+    const int64_t total = total_rows * groups_per_token;
+    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t row = idx / groups_per_token;
+        const int64_t rr = idx - row * groups_per_token;
+        const int kv = rr >= groups_per_tensor_row ? 1 : 0;
+        const int64_t r2 = rr - kv * groups_per_tensor_row;
+        const int head = static_cast<int>(r2 / groups_per_head);
+        const int grp = static_cast<int>(r2 - static_cast<int64_t>(head) * groups_per_head);
+        // sequence that owns this staging row
+        int32_t lo = 0, hi = prefill_batches;
+        while (hi - lo > 1) {
+            const int32_t mid = (lo + hi) >> 1;
+            if (stage_starts[mid] <= row) {
+                lo = mid;
+            } else {
+                hi = mid;
+            }
+        }
+        const int32_t b = decoding_batches + lo;
+        const int64_t pos = row - stage_starts[lo];
+        int64_t kvlen = start_pos[b] + (seqstarts[b + 1] - seqstarts[b]);
+        kvlen = kvlen > max_kvlen ? max_kvlen : kvlen;
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (pos < kvlen) {
+            const int64_t crow = cache_row(geom, cachestarts, b, pos);
+            const int64_t off = cache_offset(geom, crow, kv, head);
+            const uint2 codes = *reinterpret_cast<const uint2*>(cache + off + grp * 8);
+            const float s = __half2float(scale[(off >> 3) + grp]);
+            __half2* o2 = reinterpret_cast<__half2*>(&out);
+            const uint32_t w[2] = {codes.x, codes.y};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c0 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1))) & 0xffu);
+                const int c1 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1) + 8)) & 0xffu);
+                o2[i] = __floats2half2_rn(static_cast<float>(c0) * s, static_cast<float>(c1) * s);
+            }
+        }
+        __half* dst = (kv ? v_stage : k_stage) + (row * num_kv_heads + head) * head_dim + grp * 8;
+        *reinterpret_cast<uint4*>(dst) = out;
+    }
+}
+
+uint64_t align256(uint64_t x) {
+    return (x + 255) / 256 * 256;
+}
+
+}  // namespace
+
 int make_prefill_plan(const pplb200_attn_params& p, PrefillPlan* plan) {
     plan->prefill_batches = p.batch - p.decoding_batches;
-    plan->q_tiles_per_seq = (p.max_seqlen + 127) / 128;
+    plan->q_tiles_per_seq = (p.max_seqlen + kBlockM - 1) / kBlockM;
     plan->kv_rows_bound = 0;
     plan->off_kv_stage = 0;
     plan->off_stage_starts = 0;
     plan->bytes = 0;
+    if (plan->prefill_batches > 0 && p.enable_cache_prefill) {
+        const int64_t per_seq = (p.max_kvlen + kBlockN - 1) / kBlockN * kBlockN;
+        plan->kv_rows_bound = plan->prefill_batches * per_seq;
+        plan->off_stage_starts = 0;
+        plan->off_kv_stage = align256(static_cast<uint64_t>(plan->prefill_batches + 1) * 8);
+        const uint64_t one = align256(static_cast<uint64_t>(plan->kv_rows_bound) * p.num_kv_heads * p.head_dim * 2);
+        plan->bytes = plan->off_kv_stage + 2 * one;
+    }
     return PPLB200_SUCCESS;
 }
 
-int launch_prefill(const pplb200_attn_params&, const CacheGeom&, const PrefillPlan&, const void*, const void*,
-                   const void*, const int64_t*, const int64_t*, const int64_t*, const void*, const void*, void*,
-                   uint32_t*, void*, cudaStream_t) {
+template <int DH>
+static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan,
+                             const void* query, const void* cur_k, const void* cur_v, const int64_t* seqstarts,
+                             const int64_t* cachestarts, const int64_t* start_pos, const void* cache, const void* scale,
+                             void* region, uint32_t* status, void* attn_output, cudaStream_t stream) {
+    using T = PTraits<DH>;
+    const void* k_src = cur_k;
+    const void* v_src = cur_v;
+    int64_t kv_rows = p.total_tokens;
+    const int64_t* stage_starts = nullptr;
+    int rc;
+    if (p.enable_cache_prefill) {
+        uint8_t* base = static_cast<uint8_t*>(region);
+        int64_t* ss = reinterpret_cast<int64_t*>(base + plan.off_stage_starts);
+        const uint64_t one = align256(static_cast<uint64_t>(plan.kv_rows_bound) * p.num_kv_heads * p.head_dim * 2);
+        __half* ks = reinterpret_cast<__half*>(base + plan.off_kv_stage);
+        __half* vs = reinterpret_cast<__half*>(base + plan.off_kv_stage + one);
+        prefill_stage_plan_kernel<<<1, 32, 0, stream>>>(seqstarts, start_pos, static_cast<int32_t>(p.decoding_batches),
+                                                        static_cast<int32_t>(plan.prefill_batches), p.max_kvlen, ss);
+        rc = check_launch("prefill_stage_plan_kernel");
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+        const int64_t work = plan.kv_rows_bound * 2 * p.num_kv_heads * (p.head_dim / 8);
+        int64_t blocks = (work + 255) / 256;
+        blocks = blocks > 148 * 16 ? 148 * 16 : (blocks < 1 ? 1 : blocks);
+        prefill_stage_dequant_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+            seqstarts, start_pos, cachestarts, ss, static_cast<const int8_t*>(cache), static_cast<const __half*>(scale),
+            ks, vs, geom, static_cast<int32_t>(p.decoding_batches), static_cast<int32_t>(plan.prefill_batches),
+            p.max_kvlen, p.num_kv_heads, p.head_dim);
+        rc = check_launch("prefill_stage_dequant_kernel");
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+        k_src = ks;
+        v_src = vs;
+        kv_rows = plan.kv_rows_bound;
+        stage_starts = ss;
+    }
+
+    // tensor maps: {Dh, heads, rows} with a box of one head's [128 rows][64 halves], 128-byte swizzle
+    CUtensorMap tm_q, tm_k, tm_v;
+    {
+        const uint64_t dq[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(p.num_heads),
+                                static_cast<uint64_t>(p.total_tokens)};
+        const uint64_t sq[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(p.num_heads) * DH * 2};
+        const uint32_t box[3] = {64, 1, kBlockM};
+        rc = encode_tensor_map(&tm_q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, query, dq, sq, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+        const uint64_t dk[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(p.num_kv_heads),
+                                static_cast<uint64_t>(kv_rows)};
+        const uint64_t sk[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(p.num_kv_heads) * DH * 2};
+        rc = encode_tensor_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, k_src, dk, sk, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+        rc = encode_tensor_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, v_src, dk, sk, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+    }
+
+    PrefillArgs a;
+    a.out = static_cast<__half*>(attn_output);
+    a.seqstarts = seqstarts;
+    a.start_pos = start_pos;
+    a.stage_starts = stage_starts;
+    a.status = status;
+    a.max_seqlen = p.max_seqlen;
+    a.decoding_batches = static_cast<int32_t>(p.decoding_batches);
+    a.num_heads = p.num_heads;
+    a.group = p.num_heads / p.num_kv_heads;
+    a.cache_prefill = p.enable_cache_prefill ? 1 : 0;
+    a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             T::kSmemBytes);
+        if (e != cudaSuccess) {
+            fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(prefill_tcgen05_kernel): %s\n", cudaGetErrorString(e));
+            return PPLB200_DEVICE_RUNTIME_ERROR;
+        }
+        attr_set = true;
+    }
+    const dim3 grid(static_cast<unsigned>(plan.q_tiles_per_seq * p.num_heads),
+                    static_cast<unsigned>(plan.prefill_batches));
+    {
+        KernelTimer timer(PPLB200_KERNEL_PREFILL, stream);
+        prefill_tcgen05_kernel<DH><<<grid, kThreads, T::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+    }
+    return check_launch("prefill_tcgen05_kernel");
+}
+
+int launch_prefill(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan, const void* query,
+                   const void* cur_k, const void* cur_v, const int64_t* seqstarts, const int64_t* cachestarts,
+                   const int64_t* start_pos, const void* cache, const void* scale, void* workspace_region,
+                   uint32_t* status_word, void* attn_output, cudaStream_t stream) {
+    if (plan.prefill_batches <= 0 || plan.q_tiles_per_seq <= 0) {
+        return PPLB200_SUCCESS;
+    }
+    if (plan.prefill_batches > 65535) {
+        return PPLB200_UNSUPPORTED;
+    }
+    if (p.head_dim == 128) {
+        return launch_prefill_dh<128>(p, geom, plan, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache,
+                                      scale, workspace_region, status_word, attn_output, stream);
+    }
+    if (p.head_dim == 64) {
+        return launch_prefill_dh<64>(p, geom, plan, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale,
+                                     workspace_region, status_word, attn_output, stream);
+    }
     return PPLB200_UNSUPPORTED;
 }
 
