@@ -4,23 +4,25 @@
 // scales for K and for V (320 B at head_dim 128) and does 4*group*head_dim flops on them.
 //
 // Shape of the computation
-//   * Work item = (sequence b, set of `head_warps` kv heads, split s of the sequence's tokens).
-//     A tiny planning kernel turns the device-side lengths into a prefix sum of split counts; a
-//     persistent grid (2 CTAs per SM) pulls items from an atomic counter, so ragged batches balance.
-//   * A CTA has 4 warps.  Warp w works on kv head (w % head_warps) of the set and on every
-//     token_warps-th 16-token tile of the split.  Each warp runs its own 4-stage TMA pipeline: one
-//     lane issues four bulk-tensor copies per tile (K codes, V codes, K scales, V scales; 5 KB) that
-//     complete on an mbarrier, so ~15 KB per warp are in flight while it computes.
-//   * Per tile the warp computes S^T[16 tokens x 8 heads] = K[16 x Dh] * Q^T with
-//     mma.m16n8k16 (tokens are the M dimension, the up-to-8 query heads of the group the N
-//     dimension), dequantising K in registers: a byte permute builds the half 1024+u from each
-//     code byte, a subtract gives the code exactly, a multiply applies the group scale.
-//     Softmax runs in fp32 in the exp2 domain with a lazily updated reference maximum; P^T is
-//     transposed between lanes with movmatrix and O^T[Dh x 8 heads] += V^T * P^T follows, with V
-//     dequantised the same way (two tokens are interleaved into one half2 by a permute).
-//   * At the end of an item the warps that shared a kv head merge their (max, sum, O) through
-//     shared memory; the CTA writes fp16 output directly when the sequence has one split, else an
-//     fp32 partial (O, max, sum) that the reduction kernel merges.
+//   * The unit of work is a TILE: 16 consecutive tokens of one (sequence, kv head [, octet of query
+//     heads]) pair, called a segment.  All tiles of the batch form one sequence ordered by (sequence,
+//     head, position).  A planning kernel turns the device-side lengths into a prefix sum of tile
+//     counts and cuts the sequence into ranges of equal size, one per resident warp ("stream-k"): every
+//     warp streams the same number of tiles no matter how ragged the batch is.  A range may start or
+//     end in the middle of a segment; such pieces go to the workspace as fp32 partials (at most two
+//     per range) and a second-pass kernel merges them.  Pieces that cover a whole segment are written
+//     as fp16 output directly.
+//   * Every warp is an independent worker with its own TMA pipeline: one lane issues four bulk-tensor
+//     copies per tile (K codes, V codes, K scales, V scales; 5 KB at head_dim 128) that complete on
+//     an mbarrier; the pipeline runs across segment boundaries without draining.  There is no
+//     block-level synchronisation after start-up.
+//   * Per tile the warp computes S^T[16 tokens x 8 heads] = K[16 x Dh] * Q^T with mma.m16n8k16
+//     (tokens are the M dimension, the up-to-8 query heads of the group the N dimension),
+//     dequantising K in registers: a byte permute builds the half 1024+u from each code byte, a
+//     subtract gives the code exactly, a multiply applies the group scale.  Softmax runs in fp32 in the
+//     exp2 domain with a lazily updated reference maximum; P^T is transposed between lanes with
+//     movmatrix and O^T[Dh x 8 heads] += V^T * P^T follows, with V dequantised the same way (two
+//     tokens are interleaved into one half2 by a permute).
 //
 // Every wait on an mbarrier is bounded; on a timeout the warp records a status code, stops
 // waiting and finishes (with wrong numbers, flagged) instead of hanging.

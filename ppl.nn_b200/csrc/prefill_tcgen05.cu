@@ -20,6 +20,7 @@
 // waits observe, records a status code, drains its own outstanding copies (bounded as well), frees its
 // TMEM and returns.
 #include <cuda.h>
+#include <stdio.h>
 
 #include "common.cuh"
 #include "launch.h"

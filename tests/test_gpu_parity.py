@@ -221,3 +221,72 @@ def test_workspace_too_small_and_bad_params_are_rejected(torch_dev, built_lib, p
                                 one.data_ptr(), one.data_ptr(), one.data_ptr(), None, buf.data_ptr(), need,
                                 one.data_ptr(), 0)
     assert built_lib.status_str(rc) == "RC_UNSUPPORTED"  # scale missing
+
+
+# ------------------------------------------------------------------------------------------------
+# prefill (tcgen05) and mixed batches
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("hq,hkv,dh,lens", [
+    (4, 4, 128, (128,)),                       # exactly one tile
+    (4, 2, 128, (1, 5, 127, 129, 200)),        # ragged tails around the 128-row tile
+    (8, 2, 64, (33, 256, 300)),                # head_dim 64
+    (32, 8, 128, (515, 700)),                  # the LLaMA-3-8B head geometry, several kv tiles
+])
+def test_prefill_only(orc, torch_dev, pkg, hq, hkv, dh, lens):
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=hq, num_kv_heads=hkv, head_dim=dh, n_decode=0, kv_dist="list", kv_list=(),
+                 n_prefill=len(lens), seed=31)
+    hc = workloads.host_case(spec)
+    # draw_lengths gives random prefill lengths; rebuild the case with the lengths we want
+    idx = workloads.make_index([], lens)
+    hc = _case_with_index(hc, idx, spec)
+    run_case(orc, torch_dev, hc)
+
+
+def _case_with_index(hc, idx, spec, prefill_hist=None):
+    """Re-draw the tensors of a HostCase for an explicit index."""
+    from ppl_nn_b200 import workloads
+    rng = np.random.default_rng([spec.seed, 77])
+    T = idx.total_tokens
+    hk, hq, dh = hc.num_kv_heads, hc.num_heads, spec.head_dim
+    hc.index = idx
+    hc.query = rng.standard_normal((T, hq, dh), dtype=np.float32).astype(np.float16)
+    hc.current_key = rng.standard_normal((T, hk, dh), dtype=np.float32).astype(np.float16)
+    hc.current_value = rng.standard_normal((T, hk, dh), dtype=np.float32).astype(np.float16)
+    rows = int(idx.start_pos.sum())
+    hc.hist_key = rng.standard_normal((rows, hk, dh), dtype=np.float32).astype(np.float16)
+    hc.hist_value = rng.standard_normal((rows, hk, dh), dtype=np.float32).astype(np.float16)
+    starts = np.concatenate([[0], np.cumsum(idx.start_pos)]).astype(np.int64)
+    hc.hist_index = workloads.Index(seqstarts=starts, kvstarts=starts.copy(), cachestarts=idx.cachestarts,
+                                    start_pos=np.zeros_like(idx.start_pos), seqlens=idx.start_pos.copy(),
+                                    decoding_batches=0, max_seqlen=int(idx.start_pos.max()) if idx.batch else 0,
+                                    max_kvlen=int(idx.start_pos.max()) if idx.batch else 0, total_tokens=rows,
+                                    max_tokens=idx.max_tokens, page_size=idx.page_size)
+    return hc
+
+
+def test_cfg3_mixed_decode_and_prefill(orc, torch_dev, pkg):
+    """248 decode + 8 prefill sequences in one ragged call, scaled down: GQA 32/8, causal."""
+    from ppl_nn_b200 import workloads
+    spec = workloads.scaled(workloads.SPECS["cfg3_llama8b_mixed"], seqs=24 / 256, length=0.125)
+    hc = workloads.host_case(spec)
+    assert hc.index.decoding_batches > 0 and hc.index.batch > hc.index.decoding_batches
+    run_case(orc, torch_dev, hc)
+
+
+@pytest.mark.parametrize("layout", [0, 3])
+def test_cache_prefill_with_history(orc, torch_dev, pkg, layout):
+    """enable_cache_prefill: prefill sequences with start_pos > 0 read the INT8 cache (chunked
+    prefill), next to decode sequences in the same call."""
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=8, num_kv_heads=2, head_dim=128, n_decode=3, kv_dist="list", kv_list=(40, 300, 17),
+                 n_prefill=3, seed=33)
+    hc = workloads.host_case(spec)
+    idx = workloads.make_index([40, 300, 17], [100, 64, 130], prefill_hist=[0, 200, 131])
+    hc = _case_with_index(hc, idx, spec)
+    run_case(orc, torch_dev, hc, layout=layout, cache_prefill=True)
+
+
+def test_smoke_entry_point(torch_dev):
+    import __graft_entry__ as entry
+    entry.smoke()
