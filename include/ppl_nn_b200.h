@@ -141,6 +141,32 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
                          void* workspace, uint64_t workspace_bytes, void* attn_output, void* stream);
 
 /*
+ * MultiHeadCacheAttention without a caller workspace.  This entry point has no counterpart in the
+ * reference: ppl.nn always borrows the scratch from its engine's tmp-buffer pool
+ * (multi_head_cache_attention_kernel.cc:218-228).  It is for callers that cannot allocate device
+ * memory at all -- an operator invoked outside an engine's device context has no pool to borrow
+ * from, and a server that gave every free byte to the KV cache, or that must not call cudaMalloc
+ * behind its own allocator's back, has nowhere to get a buffer.  Same arguments and results as
+ * pplb200_mhca_forward, minus `workspace`: the scratch is a fixed 32 MiB array inside the library's
+ * device image (pplb200_static_scratch_bytes(); every GPU that loads the library carries it until
+ * the process exits).  The call allocates and frees nothing.
+ *   - Calls whose pplb200_mhca_workspace_size() exceeds that capacity return PPLB200_OUT_OF_MEMORY
+ *     and enqueue nothing.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, which keeps whatever the previous call left in
+ *     it; the kernels re-initialise what they rely on, but two calls that overlap on the GPU
+ *     (different streams) race on it.  pplb200_mhca_device_status cannot be used with it.
+ */
+int pplb200_mhca_forward_noalloc(const pplb200_attn_params* p, const void* query, const void* current_key,
+                                 const void* current_value, const int64_t* seqstarts, const int64_t* kvstarts,
+                                 const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale,
+                                 void* attn_output, void* stream);
+
+/* Capacity in bytes of the built-in scratch used by pplb200_mhca_forward_noalloc. */
+uint64_t pplb200_static_scratch_bytes(void);
+
+/*
  * Reads the device-side status word that the kernels of the last pplb200_mhca_forward on this
  * workspace left behind (0 = clean; non-zero = a bounded wait gave up, see PPLB200_DEV_*).
  * Synchronises `stream`.  Has no counterpart in the reference; it exists because every wait

@@ -36,6 +36,8 @@ EXPORTS = (
     "pplb200_kv_gather_dequant",
     "pplb200_mhca_workspace_size",
     "pplb200_mhca_forward",
+    "pplb200_mhca_forward_noalloc",
+    "pplb200_static_scratch_bytes",
     "pplb200_mhca_device_status",
     "pplb200_status_str",
     "pplb200_device_ready",
@@ -101,6 +103,10 @@ class Library:
         d.pplb200_mhca_workspace_size.argtypes = [pp, ctypes.POINTER(ctypes.c_uint64)]
         d.pplb200_mhca_forward.restype = ctypes.c_int
         d.pplb200_mhca_forward.argtypes = [pp, vp, vp, vp, i64p, i64p, i64p, i64p, vp, vp, vp, ctypes.c_uint64, vp, vp]
+        d.pplb200_mhca_forward_noalloc.restype = ctypes.c_int
+        d.pplb200_mhca_forward_noalloc.argtypes = [pp, vp, vp, vp, i64p, i64p, i64p, i64p, vp, vp, vp, vp]
+        d.pplb200_static_scratch_bytes.restype = ctypes.c_uint64
+        d.pplb200_static_scratch_bytes.argtypes = []
         d.pplb200_mhca_device_status.restype = ctypes.c_int
         d.pplb200_mhca_device_status.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_uint32)]
         d.pplb200_status_str.restype = ctypes.c_char_p
@@ -159,6 +165,15 @@ class Library:
                      workspace, workspace_bytes, out, stream) -> int:
         return self.dll.pplb200_mhca_forward(ctypes.byref(p), q, cur_k, cur_v, seqstarts, kvstarts, cachestarts,
                                              start_pos, cache, scale, workspace, int(workspace_bytes), out, stream)
+
+    def mhca_forward_noalloc(self, p, q, cur_k, cur_v, seqstarts, kvstarts, cachestarts, start_pos, cache, scale,
+                             out, stream) -> int:
+        """Same as mhca_forward but with the library's built-in scratch: no workspace, no allocation."""
+        return self.dll.pplb200_mhca_forward_noalloc(ctypes.byref(p), q, cur_k, cur_v, seqstarts, kvstarts,
+                                                     cachestarts, start_pos, cache, scale, out, stream)
+
+    def static_scratch_bytes(self) -> int:
+        return int(self.dll.pplb200_static_scratch_bytes())
 
     def mhca_device_status(self, workspace, stream) -> tuple[int, int]:
         s = ctypes.c_uint32(0)
