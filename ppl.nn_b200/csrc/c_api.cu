@@ -330,7 +330,7 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     const CacheGeom geom = make_geom(*p);
     const int mask = p->phase_mask ? p->phase_mask : (PPLB200_PHASE_APPEND | PPLB200_PHASE_DECODE | PPLB200_PHASE_PREFILL);
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    uint32_t* status = reinterpret_cast<uint32_t*>(ws + w.decode.off_status);
+    uint32_t* status = reinterpret_cast<uint32_t*>(ws + w.decode.off_header);  // first word of the header
 
     if (mask & PPLB200_PHASE_APPEND) {
         rc = launch_kv_append(*p, geom, current_key, current_value, seqstarts, cachestarts, start_pos, cache, scale,

@@ -12,10 +12,14 @@
 //     end in the middle of a segment; such pieces go to the workspace as fp32 partials (at most two
 //     per range) and a second-pass kernel merges them.  Pieces that cover a whole segment are written
 //     as fp16 output directly.
+//   * The heads are dealt round-robin into `head_lanes` (4, 2 or 1) classes; the 4 warps of a CTA take
+//     the same range of different classes, i.e. adjacent heads of the same token rows, so that in the
+//     token-major cache layout the CTA streams 4 x 128 contiguous bytes per row (with fewer classes
+//     the remaining warps take the next range of the same class).
 //   * Every warp is an independent worker with its own TMA pipeline: one lane issues four bulk-tensor
 //     copies per tile (K codes, V codes, K scales, V scales; 5 KB at head_dim 128) that complete on
-//     an mbarrier; the pipeline runs across segment boundaries without draining.  There is no
-//     block-level synchronisation after start-up.
+//     an mbarrier; the pipeline runs across segment boundaries without draining.  The only
+//     block-level synchronisation is the hand-out of the next range.
 //   * Per tile the warp computes S^T[16 tokens x 8 heads] = K[16 x Dh] * Q^T with mma.m16n8k16
 //     (tokens are the M dimension, the up-to-8 query heads of the group the N dimension),
 //     dequantising K in registers: a byte permute builds the half 1024+u from each code byte, a
@@ -39,9 +43,11 @@ namespace pplb200 {
 namespace {
 
 constexpr int kTileTok = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
+constexpr int kCtasPerSm = 3;
+constexpr int kMinRangeTiles = 8;  // never cut the work finer than 128 tokens per range
 constexpr float kNegBig = -1.0e30f;
 constexpr float kRescaleSlack = 8.0f;  // the reference maximum may lag by up to 2^8 before a rescale
 
@@ -55,8 +61,17 @@ struct Traits {
     static constexpr int kKRegs = DH / 16;                         // 32-bit code words per thread per K row
     static constexpr int kVRegs = DH / 32;                         // 32-bit code words per thread per V row
     static constexpr int kMTiles = DH / 16;                        // 16-channel output tiles
-    static constexpr bool kSwizzle = (DH == 128);                  // 128-byte rows use the 128B TMA swizzle
-    static_assert(8 * DH * 4 + 64 <= kWarpBytes, "merge buffer must fit in the warp's stage buffers");
+};
+
+// Header of the decode region of the workspace, written by the planning kernel.
+struct PlanHeader {
+    uint32_t status;        // device status word (first word of the workspace)
+    int32_t counter;        // next range to hand out
+    int32_t range_tiles;    // R: tiles per range (uniform mode)
+    int32_t num_ranges;
+    int64_t total_tiles;    // tiles of one head class: (num_vheads / head_lanes) * sum_b tiles_b
+    int32_t per_segment;    // 1: ranges are whole segments (split-k off), 0: uniform ranges
+    int32_t reserved;
 };
 
 struct DecodeArgs {
@@ -65,22 +80,18 @@ struct DecodeArgs {
     const int64_t* seqstarts;
     const int64_t* cachestarts;
     const int64_t* start_pos;
-    uint32_t* status;
-    int32_t* counter;
-    const int32_t* split_starts;
-    float* part_ml;
-    float* part_o;
+    PlanHeader* hdr;
+    const int32_t* tile_prefix;  // [decoding_batches + 1] prefix sum of tiles per sequence
+    float* part_ml;              // [slots][8][2]
+    float* part_o;               // [slots][8][DH]
     CacheGeom geom;
-    int64_t chunk_tokens;
     int64_t max_kvlen;
     int32_t decoding_batches;
     int32_t num_heads;
-    int32_t num_kv_heads;
     int32_t group;
     int32_t octets;
-    int32_t head_warps;
-    int32_t token_warps;
-    int32_t num_hsets;
+    int32_t head_lanes;   // head classes = warps of a CTA that share a range
+    int32_t class_heads;  // virtual heads per class: num_vheads / head_lanes
     int32_t layer_idx;
     CacheMapOrder order;
     float scale_log2;
@@ -100,25 +111,25 @@ __device__ __forceinline__ void tma_load_cache_tile(void* dst, const CUtensorMap
 }
 
 // ------------------------------------------------------------------------------------------
-// Planning kernel: split counts per decode sequence -> exclusive prefix sum; resets the work
-// counter and the status word.  One CTA.
+// Planning kernel (one CTA): tiles per decode sequence -> exclusive prefix sum, the longest
+// sequence, and from them the range size; resets the work counter and the status word.
 // ------------------------------------------------------------------------------------------
 constexpr int kPlanThreads = 512;
 
 __global__ void __launch_bounds__(kPlanThreads)
 decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
-                   int32_t decoding_batches, int64_t chunk_tokens, int64_t max_kvlen,
-                   int32_t* __restrict__ split_starts, int32_t* __restrict__ counter, uint32_t* __restrict__ status,
-                   int reset_status) {
+                   int32_t decoding_batches, int32_t class_heads, int64_t max_kvlen, int32_t split_k_mode,
+                   int32_t workers, int32_t max_ranges, PlanHeader* __restrict__ hdr,
+                   int32_t* __restrict__ tile_prefix) {
     using Scan = cub::BlockScan<int32_t, kPlanThreads>;
     __shared__ typename Scan::TempStorage tmp;
     __shared__ int32_t carry;
+    __shared__ int32_t longest;
     if (threadIdx.x == 0) {
         carry = 0;
-        *counter = 0;
-        if (reset_status) {
-            *status = 0;
-        }
+        longest = 1;
+        hdr->status = 0;
+        hdr->counter = 0;
     }
     __syncthreads();
     for (int32_t base = 0; base < decoding_batches; base += kPlanThreads) {
@@ -128,18 +139,19 @@ decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restr
             int64_t kvlen = start_pos[b] + (seqstarts[b + 1] - seqstarts[b]);
             if (kvlen > max_kvlen) {
                 kvlen = max_kvlen;
-                atomicOr(status, kDevLengthClamped);
+                atomicOr(&hdr->status, kDevLengthClamped);
             }
             if (kvlen < 1) {
-                kvlen = 1;  // an empty sequence still owns one (empty) split so that its output is written
+                kvlen = 1;  // an empty sequence still owns one (fully masked) tile so that its output is written
             }
-            n = static_cast<int32_t>((kvlen + chunk_tokens - 1) / chunk_tokens);
+            n = static_cast<int32_t>((kvlen + kTileTok - 1) / kTileTok);
+            atomicMax(&longest, n);
         }
         int32_t excl, total;
         Scan(tmp).ExclusiveSum(n, excl, total);
         const int32_t c = carry;
         if (b < decoding_batches) {
-            split_starts[b] = c + excl;
+            tile_prefix[b] = c + excl;
         }
         __syncthreads();
         if (threadIdx.x == 0) {
@@ -148,7 +160,30 @@ decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restr
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        split_starts[decoding_batches] = carry;
+        tile_prefix[decoding_batches] = carry;
+        const int64_t total = static_cast<int64_t>(carry) * class_heads;
+        hdr->total_tiles = total;
+        if (split_k_mode == 0) {
+            hdr->per_segment = 1;
+            hdr->range_tiles = 0;
+            hdr->num_ranges = decoding_batches * class_heads;
+        } else {
+            int64_t r = (total + workers - 1) / workers;  // equal share per resident warp of the class
+            r = r < kMinRangeTiles ? kMinRangeTiles : r;
+            if (split_k_mode == 2) {
+                const int64_t half = (longest + 1) / 2;  // "always": the longest sequence is cut at least once
+                r = r < half ? r : half;
+                r = r < 1 ? 1 : r;
+            }
+            int64_t nr = (total + r - 1) / r;
+            if (nr > max_ranges) {  // cannot happen for lengths within max_kvlen; keep the partial slots in bounds
+                r = (total + max_ranges - 1) / max_ranges;
+                nr = (total + r - 1) / r;
+            }
+            hdr->per_segment = 0;
+            hdr->range_tiles = static_cast<int32_t>(r);
+            hdr->num_ranges = static_cast<int32_t>(nr);
+        }
     }
 }
 
@@ -176,15 +211,23 @@ __device__ __forceinline__ void dequant_v_pair(uint32_t wa, uint32_t wb, __half2
     h[3] = h2_as_u32(__hmul2(biased_bytes_to_half2<0x5342u>(y), s2));
 }
 
+// Position in the tile sequence of one head class: sequence b, class-local head index vc (the virtual
+// head, i.e. kv head x octet of query heads, is vc * head_lanes + class), tile index within the
+// segment, tiles per segment of this sequence, first cache row of the sequence.
+struct Cursor {
+    int32_t b, vc, tile, n;
+    int64_t row_base;
+};
+
 template <int DH>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_scales,
                      const DecodeArgs a) {
     using T = Traits<DH>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full_bar[kWarps * kStages];
-    __shared__ int32_t s_item;
+    __shared__ int32_t s_base;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -203,348 +246,378 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
 
     uint8_t* wsm = smem + warp * T::kWarpBytes;
     uint64_t* wbar = full_bar + warp * kStages;
-    uint32_t tiles_done = 0;  // tiles this warp has consumed so far: selects stage and barrier parity
-    bool wait_dead = false;   // set after the first timed-out wait: stop waiting, just finish
+    uint32_t c_stage = 0, c_phase = 0;  // consume position in the stage ring
+    uint32_t i_stage = 0;               // issue position in the stage ring
+    bool wait_dead = false;             // set after the first timed-out wait: stop waiting, just finish
 
-    const int HW = a.head_warps;
-    const int TW = a.token_warps;
-    const int head_sub = warp % HW;
-    const int tw = warp / HW;
+    const int nvc = a.class_heads;
+    const int cls = warp % a.head_lanes;             // head class of this warp
+    const int sub = warp / a.head_lanes;             // which of the CTA's consecutive ranges it takes
+    const int ranges_per_cta = kWarps / a.head_lanes;
+    const int32_t DB = a.decoding_batches;
+    const int32_t num_ranges = a.hdr->num_ranges;
+    const int32_t range_tiles = a.hdr->range_tiles;
+    const int32_t per_segment = a.hdr->per_segment;
+    const int64_t total_tiles = a.hdr->total_tiles;
 
-    const int32_t total_splits = a.split_starts[a.decoding_batches];
-    const int64_t total_items = static_cast<int64_t>(total_splits) * a.num_hsets;
+    auto seq_row_base = [&](int32_t b) -> int64_t { return a.geom.cache_mode == 0 ? a.cachestarts[b] : 0; };
+    auto advance = [&](Cursor& c, int32_t by) {
+        // moves within the segment or to the start of the next one (by never crosses two boundaries)
+        c.tile += by;
+        if (c.tile >= c.n) {
+            c.tile = 0;
+            if (++c.vc == nvc) {
+                c.vc = 0;
+                ++c.b;
+                if (c.b < DB) {
+                    c.n = a.tile_prefix[c.b + 1] - a.tile_prefix[c.b];
+                    c.row_base = seq_row_base(c.b);
+                }
+            }
+        }
+    };
 
     for (;;) {
+        __syncthreads();  // everyone has read the previous s_base
         if (threadIdx.x == 0) {
-            s_item = atomicAdd(a.counter, 1);
+            s_base = atomicAdd(&a.hdr->counter, ranges_per_cta);
         }
         __syncthreads();
-        const int64_t item = s_item;
-        if (item >= total_items) {
-            break;
+        const int32_t r = s_base + sub;
+        if (s_base >= num_ranges) {
+            break;  // uniform for the CTA
         }
-        const int hset = static_cast<int>(item % a.num_hsets);
-        const int32_t j = static_cast<int32_t>(item / a.num_hsets);
-        // sequence that owns global split j: largest b with split_starts[b] <= j
-        int32_t lo = 0, hi = a.decoding_batches;
-        while (hi - lo > 1) {
-            const int32_t mid = (lo + hi) >> 1;
-            if (a.split_starts[mid] <= j) {
-                lo = mid;
-            } else {
-                hi = mid;
-            }
+        if (r >= num_ranges) {
+            continue;
         }
-        const int32_t b = lo;
-        const int32_t first_split = a.split_starts[b];
-        const int32_t nsplits = a.split_starts[b + 1] - first_split;
-        const int32_t split = j - first_split;
-        const int64_t qtok = a.seqstarts[b];
-        int64_t kvlen = a.start_pos[b] + (a.seqstarts[b + 1] - qtok);
-        kvlen = kvlen > a.max_kvlen ? a.max_kvlen : kvlen;
-        const int64_t t0 = static_cast<int64_t>(split) * a.chunk_tokens;
-        int64_t t1 = t0 + a.chunk_tokens;
-        t1 = t1 > kvlen ? kvlen : t1;
-        const int32_t ntiles = t1 > t0 ? static_cast<int32_t>((t1 - t0 + kTileTok - 1) / kTileTok) : 0;
-        const int32_t my_n = ntiles > tw ? (ntiles - tw + TW - 1) / TW : 0;
-
-        const int vhead = hset * HW + head_sub;
-        const int kvh = vhead / a.octets;
-        const int oct = vhead - kvh * a.octets;
-
-        // ---- Q fragments (B operand: k = channel, n = query head of the group) ----
-        uint32_t qf[T::kKRegs][2];
-        {
-            const int hq_in_group = oct * 8 + g;
-            if (hq_in_group < a.group) {
-                const __half* qp =
-                    a.q + (qtok * a.num_heads + kvh * a.group + hq_in_group) * DH + t * (DH / 4);
-#pragma unroll
-                for (int i = 0; i < T::kKRegs / 2; ++i) {
-                    const uint4 v = *reinterpret_cast<const uint4*>(qp + 8 * i);
-                    qf[2 * i][0] = v.x;
-                    qf[2 * i][1] = v.y;
-                    qf[2 * i + 1][0] = v.z;
-                    qf[2 * i + 1][1] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < T::kKRegs; ++i) {
-                    qf[i][0] = 0u;
-                    qf[i][1] = 0u;
+        // ---- the range [lo, hi) of the global tile sequence and the segment it starts in ----
+        int64_t lo, hi;
+        Cursor cc;
+        if (per_segment) {
+            cc.b = r / nvc;
+            cc.vc = r - cc.b * nvc;
+            cc.tile = 0;
+            cc.n = a.tile_prefix[cc.b + 1] - a.tile_prefix[cc.b];
+            lo = static_cast<int64_t>(a.tile_prefix[cc.b]) * nvc + static_cast<int64_t>(cc.vc) * cc.n;
+            hi = lo + cc.n;
+        } else {
+            lo = static_cast<int64_t>(r) * range_tiles;
+            hi = lo + range_tiles;
+            hi = hi > total_tiles ? total_tiles : hi;
+            int32_t l = 0, h = DB;  // largest b with tile_prefix[b] * nvc <= lo
+            while (h - l > 1) {
+                const int32_t mid = (l + h) >> 1;
+                if (static_cast<int64_t>(a.tile_prefix[mid]) * nvc <= lo) {
+                    l = mid;
+                } else {
+                    h = mid;
                 }
             }
+            cc.b = l;
+            const int32_t base = a.tile_prefix[l];
+            cc.n = a.tile_prefix[l + 1] - base;
+            const int64_t rem = lo - static_cast<int64_t>(base) * nvc;
+            cc.vc = static_cast<int32_t>(rem / cc.n);
+            cc.tile = static_cast<int32_t>(rem - static_cast<int64_t>(cc.vc) * cc.n);
         }
+        cc.row_base = seq_row_base(cc.b);
+        Cursor ic = cc;      // issue cursor: runs up to kStages tiles ahead of the consume cursor
+        int64_t gi = lo;     // global index of the next tile to issue
 
-        float o[T::kMTiles][4];
-#pragma unroll
-        for (int i = 0; i < T::kMTiles; ++i) {
-            o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-        }
-        float m0 = kNegBig, m1 = kNegBig, l0 = 0.0f, l1 = 0.0f;
-
-        const uint32_t base_seq = tiles_done;
-        auto issue = [&](int32_t local_idx) {
-            const int64_t tok = t0 + static_cast<int64_t>(tw + local_idx * TW) * kTileTok;
-            const int row = static_cast<int>(cache_row(a.geom, a.cachestarts, b, tok));
-            const uint32_t stage = (base_seq + local_idx) % kStages;
-            uint8_t* st = wsm + stage * T::kStageBytes;
-            uint64_t* bar = &wbar[stage];
-            mbar_arrive_expect_tx(bar, T::kStageBytes);
-            tma_load_cache_tile(st, &tmap_codes, bar, a.order, row, kvh, 0, a.layer_idx);
-            tma_load_cache_tile(st + T::kCodeBytes, &tmap_codes, bar, a.order, row, kvh, 1, a.layer_idx);
-            tma_load_cache_tile(st + 2 * T::kCodeBytes, &tmap_scales, bar, a.order, row, kvh, 0, a.layer_idx);
-            tma_load_cache_tile(st + 2 * T::kCodeBytes + T::kScaleBytes, &tmap_scales, bar, a.order, row, kvh, 1,
-                                a.layer_idx);
+        auto issue_one = [&]() {
+            if (lane == 0) {
+                const int64_t tok = static_cast<int64_t>(ic.tile) * kTileTok;
+                const int row = static_cast<int>(a.geom.cache_mode == 0 ? ic.row_base + tok
+                                                                         : cache_row(a.geom, a.cachestarts, ic.b, tok));
+                const int kvh = (ic.vc * a.head_lanes + cls) / a.octets;
+                uint8_t* st = wsm + i_stage * T::kStageBytes;
+                uint64_t* bar = &wbar[i_stage];
+                mbar_arrive_expect_tx(bar, T::kStageBytes);
+                tma_load_cache_tile(st, &tmap_codes, bar, a.order, row, kvh, 0, a.layer_idx);
+                tma_load_cache_tile(st + T::kCodeBytes, &tmap_codes, bar, a.order, row, kvh, 1, a.layer_idx);
+                tma_load_cache_tile(st + 2 * T::kCodeBytes, &tmap_scales, bar, a.order, row, kvh, 0, a.layer_idx);
+                tma_load_cache_tile(st + 2 * T::kCodeBytes + T::kScaleBytes, &tmap_scales, bar, a.order, row, kvh, 1,
+                                    a.layer_idx);
+            }
+            i_stage = (i_stage + 1 == kStages) ? 0 : i_stage + 1;
+            advance(ic, 1);
+            ++gi;
         };
-
-        if (lane == 0) {
-            const int32_t npre = my_n < kStages ? my_n : kStages;
-            for (int32_t i = 0; i < npre; ++i) {
-                issue(i);
-            }
+        for (int i = 0; i < kStages && gi < hi; ++i) {
+            issue_one();
         }
 
-        for (int32_t i = 0; i < my_n; ++i) {
-            const uint32_t seq = base_seq + i;
-            const uint32_t stage = seq % kStages;
-            if (!wait_dead) {
-                if (!mbar_wait_bounded(&wbar[stage], (seq / kStages) & 1u)) {
-                    wait_dead = true;
-                    if (lane == 0) {
-                        atomicOr(a.status, kDevTmaTimeout);
-                    }
-                }
-            }
-            const uint8_t* st = wsm + stage * T::kStageBytes;
-            const uint8_t* kc = st;
-            const uint8_t* vc = st + T::kCodeBytes;
-            const uint8_t* ks = st + 2 * T::kCodeBytes;
-            const uint8_t* vs = ks + T::kScaleBytes;
-            const int64_t tok0 = t0 + static_cast<int64_t>(tw + i * TW) * kTileTok;
-            const int nvalid = (t1 - tok0) < kTileTok ? static_cast<int>(t1 - tok0) : kTileTok;
+        int64_t gc = lo;  // global index of the next tile to consume
+        while (gc < hi) {
+            // ---- one piece: the part of segment (cc.b, cc.vc) that lies inside the range ----
+            const int32_t t_first = cc.tile;
+            const int64_t left = hi - gc;
+            const int32_t t_end = (cc.n - t_first) <= left ? cc.n : t_first + static_cast<int32_t>(left);
+            const int32_t b = cc.b;
+            const int vh = cc.vc * a.head_lanes + cls;
+            const int kvh = vh / a.octets;
+            const int oct = vh - kvh * a.octets;
+            const int64_t qtok = a.seqstarts[b];
+            int64_t kvlen = a.start_pos[b] + (a.seqstarts[b + 1] - qtok);
+            kvlen = kvlen > a.max_kvlen ? a.max_kvlen : kvlen;
 
-            // ---------------- S^T = K * Q^T ----------------
-            float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            // Q fragments (B operand: k = channel, n = query head of the group)
+            uint32_t qf[T::kKRegs][2];
             {
-                uint32_t wa[T::kKRegs], wb[T::kKRegs];  // rows g and g+8, this thread's channel slab
-                uint32_t sa[T::kKRegs / 4], sb[T::kKRegs / 4];  // packed group scales (2 halves per word)
-                if constexpr (DH == 128) {
-                    const uint4 a0 = lds128(kc + g * 128 + (((2 * t) ^ g) << 4));
-                    const uint4 a1 = lds128(kc + g * 128 + (((2 * t + 1) ^ g) << 4));
-                    const uint4 b0 = lds128(kc + (g + 8) * 128 + (((2 * t) ^ g) << 4));
-                    const uint4 b1 = lds128(kc + (g + 8) * 128 + (((2 * t + 1) ^ g) << 4));
-                    wa[0] = a0.x; wa[1] = a0.y; wa[2] = a0.z; wa[3] = a0.w;
-                    wa[4] = a1.x; wa[5] = a1.y; wa[6] = a1.z; wa[7] = a1.w;
-                    wb[0] = b0.x; wb[1] = b0.y; wb[2] = b0.z; wb[3] = b0.w;
-                    wb[4] = b1.x; wb[5] = b1.y; wb[6] = b1.z; wb[7] = b1.w;
-                    const uint2 s_a = *reinterpret_cast<const uint2*>(ks + g * 32 + t * 8);
-                    const uint2 s_b = *reinterpret_cast<const uint2*>(ks + (g + 8) * 32 + t * 8);
-                    sa[0] = s_a.x; sa[1] = s_a.y;
-                    sb[0] = s_b.x; sb[1] = s_b.y;
+                const int hq_in_group = oct * 8 + g;
+                if (hq_in_group < a.group) {
+                    const __half* qp = a.q + (qtok * a.num_heads + kvh * a.group + hq_in_group) * DH + t * (DH / 4);
+#pragma unroll
+                    for (int i = 0; i < T::kKRegs / 2; ++i) {
+                        const uint4 v = *reinterpret_cast<const uint4*>(qp + 8 * i);
+                        qf[2 * i][0] = v.x;
+                        qf[2 * i][1] = v.y;
+                        qf[2 * i + 1][0] = v.z;
+                        qf[2 * i + 1][1] = v.w;
+                    }
                 } else {
-                    const uint4 a0 = lds128(kc + g * 64 + t * 16);
-                    const uint4 b0 = lds128(kc + (g + 8) * 64 + t * 16);
-                    wa[0] = a0.x; wa[1] = a0.y; wa[2] = a0.z; wa[3] = a0.w;
-                    wb[0] = b0.x; wb[1] = b0.y; wb[2] = b0.z; wb[3] = b0.w;
-                    sa[0] = *reinterpret_cast<const uint32_t*>(ks + g * 16 + t * 4);
-                    sb[0] = *reinterpret_cast<const uint32_t*>(ks + (g + 8) * 16 + t * 4);
-                }
 #pragma unroll
-                for (int r = 0; r < T::kKRegs; ++r) {
-                    // word r holds channels 4r..4r+3 of the slab: quantisation group r/2 of the slab
-                    const uint32_t sel = (r & 2) ? 0x3232u : 0x1010u;
-                    const __half2 s2a = u32_as_h2(prmt(sa[r >> 2], 0u, sel));
-                    const __half2 s2b = u32_as_h2(prmt(sb[r >> 2], 0u, sel));
-                    uint32_t a0, a1, a2, a3;
-                    dequant_k_word(wa[r], s2a, a0, a2);
-                    dequant_k_word(wb[r], s2b, a1, a3);
-                    mma_m16n8k16_f16f32(sacc, a0, a1, a2, a3, qf[r][0], qf[r][1]);
-                }
-            }
-
-            // ---------------- softmax (exp2 domain, lazy reference maximum) ----------------
-            float s0 = sacc[0] * a.scale_log2;  // token g,   head 2t
-            float s1 = sacc[1] * a.scale_log2;  // token g,   head 2t+1
-            float s2 = sacc[2] * a.scale_log2;  // token g+8, head 2t
-            float s3 = sacc[3] * a.scale_log2;  // token g+8, head 2t+1
-            if (g >= nvalid) {
-                s0 = kNegBig;
-                s1 = kNegBig;
-            }
-            if (g + 8 >= nvalid) {
-                s2 = kNegBig;
-                s3 = kNegBig;
-            }
-            {
-                float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
-                const bool need = (lm0 > m0 + kRescaleSlack) || (lm1 > m1 + kRescaleSlack);
-                if (__any_sync(0xffffffffu, need)) {
-#pragma unroll
-                    for (int off = 4; off <= 16; off <<= 1) {
-                        lm0 = fmaxf(lm0, __shfl_xor_sync(0xffffffffu, lm0, off));
-                        lm1 = fmaxf(lm1, __shfl_xor_sync(0xffffffffu, lm1, off));
-                    }
-                    const float n0 = fmaxf(m0, lm0), n1 = fmaxf(m1, lm1);
-                    const float r0 = ex2_approx(m0 - n0), r1 = ex2_approx(m1 - n1);
-                    m0 = n0;
-                    m1 = n1;
-                    l0 *= r0;
-                    l1 *= r1;
-#pragma unroll
-                    for (int i = 0; i < T::kMTiles; ++i) {
-                        o[i][0] *= r0;
-                        o[i][1] *= r1;
-                        o[i][2] *= r0;
-                        o[i][3] *= r1;
+                    for (int i = 0; i < T::kKRegs; ++i) {
+                        qf[i][0] = 0u;
+                        qf[i][1] = 0u;
                     }
                 }
             }
-            const float p0 = ex2_approx(s0 - m0), p1 = ex2_approx(s1 - m1);
-            const float p2 = ex2_approx(s2 - m0), p3 = ex2_approx(s3 - m1);
-            l0 += p0 + p2;
-            l1 += p1 + p3;
-            // P^T as the B operand of the second MMA: k = token, n = head
-            const uint32_t pb0 = movmatrix_trans(h2_as_u32(__floats2half2_rn(p0, p1)));
-            const uint32_t pb1 = movmatrix_trans(h2_as_u32(__floats2half2_rn(p2, p3)));
-
-            // ---------------- O^T += V^T * P^T ----------------
-            {
-                const int ta = 2 * t, tb = 2 * t + 1, tc = 2 * t + 8, td = 2 * t + 9;
-                uint32_t va[T::kVRegs], vb[T::kVRegs], vcw[T::kVRegs], vd[T::kVRegs];
-                uint32_t sca, scb, scc, scd;  // scales of the thread's channel groups, per token
-                if constexpr (DH == 128) {
-                    const uint4 xa = lds128(vc + ta * 128 + ((g ^ (ta & 7)) << 4));
-                    const uint4 xb = lds128(vc + tb * 128 + ((g ^ (tb & 7)) << 4));
-                    const uint4 xc = lds128(vc + tc * 128 + ((g ^ (tc & 7)) << 4));
-                    const uint4 xd = lds128(vc + td * 128 + ((g ^ (td & 7)) << 4));
-                    va[0] = xa.x; va[1] = xa.y; va[2] = xa.z; va[3] = xa.w;
-                    vb[0] = xb.x; vb[1] = xb.y; vb[2] = xb.z; vb[3] = xb.w;
-                    vcw[0] = xc.x; vcw[1] = xc.y; vcw[2] = xc.z; vcw[3] = xc.w;
-                    vd[0] = xd.x; vd[1] = xd.y; vd[2] = xd.z; vd[3] = xd.w;
-                    sca = *reinterpret_cast<const uint32_t*>(vs + ta * 32 + g * 4);
-                    scb = *reinterpret_cast<const uint32_t*>(vs + tb * 32 + g * 4);
-                    scc = *reinterpret_cast<const uint32_t*>(vs + tc * 32 + g * 4);
-                    scd = *reinterpret_cast<const uint32_t*>(vs + td * 32 + g * 4);
-                } else {
-                    const uint2 xa = *reinterpret_cast<const uint2*>(vc + ta * 64 + g * 8);
-                    const uint2 xb = *reinterpret_cast<const uint2*>(vc + tb * 64 + g * 8);
-                    const uint2 xc = *reinterpret_cast<const uint2*>(vc + tc * 64 + g * 8);
-                    const uint2 xd = *reinterpret_cast<const uint2*>(vc + td * 64 + g * 8);
-                    va[0] = xa.x; va[1] = xa.y;
-                    vb[0] = xb.x; vb[1] = xb.y;
-                    vcw[0] = xc.x; vcw[1] = xc.y;
-                    vd[0] = xd.x; vd[1] = xd.y;
-                    sca = *reinterpret_cast<const uint16_t*>(vs + ta * 16 + g * 2);
-                    scb = *reinterpret_cast<const uint16_t*>(vs + tb * 16 + g * 2);
-                    scc = *reinterpret_cast<const uint16_t*>(vs + tc * 16 + g * 2);
-                    scd = *reinterpret_cast<const uint16_t*>(vs + td * 16 + g * 2);
-                }
-                if (nvalid < kTileTok) {
-                    // rows past the end of the split hold other data (or nothing): their scales may be
-                    // anything, and 0 * NaN would poison the accumulator even though P is exactly 0 there
-                    sca = ta < nvalid ? sca : 0u;
-                    scb = tb < nvalid ? scb : 0u;
-                    scc = tc < nvalid ? scc : 0u;
-                    scd = td < nvalid ? scd : 0u;
-                }
+            float o[T::kMTiles][4];
 #pragma unroll
-                for (int q = 0; q < T::kVRegs; ++q) {
-                    // word q holds channels 4q..4q+3 of the thread's slab: group q/2 of the slab
-                    const uint32_t sel = (q & 2) ? 0x7632u : 0x5410u;
-                    const __half2 s_ab = u32_as_h2(prmt(sca, scb, sel));
-                    const __half2 s_cd = u32_as_h2(prmt(scc, scd, sel));
-                    uint32_t hab[4], hcd[4];
-                    dequant_v_pair(va[q], vb[q], s_ab, hab);
-                    dequant_v_pair(vcw[q], vd[q], s_cd, hcd);
-                    mma_m16n8k16_f16f32(o[2 * q], hab[0], hab[1], hcd[0], hcd[1], pb0, pb1);
-                    mma_m16n8k16_f16f32(o[2 * q + 1], hab[2], hab[3], hcd[2], hcd[3], pb0, pb1);
+            for (int i = 0; i < T::kMTiles; ++i) {
+                o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+            }
+            float m0 = kNegBig, m1 = kNegBig, l0 = 0.0f, l1 = 0.0f;
+
+            for (int32_t tile = t_first; tile < t_end; ++tile) {
+                if (!wait_dead) {
+                    if (!mbar_wait_bounded(&wbar[c_stage], c_phase)) {
+                        wait_dead = true;
+                        if (lane == 0) {
+                            atomicOr(&a.hdr->status, kDevTmaTimeout);
+                        }
+                    }
+                }
+                const uint8_t* st = wsm + c_stage * T::kStageBytes;
+                const uint8_t* kc = st;
+                const uint8_t* vc = st + T::kCodeBytes;
+                const uint8_t* ks = st + 2 * T::kCodeBytes;
+                const uint8_t* vs = ks + T::kScaleBytes;
+                const int64_t tok0 = static_cast<int64_t>(tile) * kTileTok;
+                const int nvalid = (kvlen - tok0) < kTileTok ? static_cast<int>(kvlen - tok0) : kTileTok;
+
+                // ---------------- S^T = K * Q^T ----------------
+                float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                {
+                    uint32_t wa[T::kKRegs], wb[T::kKRegs];          // rows g and g+8, this thread's channel slab
+                    uint32_t sa[T::kKRegs / 4], sb[T::kKRegs / 4];  // packed group scales (2 halves per word)
+                    if constexpr (DH == 128) {
+                        const uint4 a0 = lds128(kc + g * 128 + (((2 * t) ^ g) << 4));
+                        const uint4 a1 = lds128(kc + g * 128 + (((2 * t + 1) ^ g) << 4));
+                        const uint4 b0 = lds128(kc + (g + 8) * 128 + (((2 * t) ^ g) << 4));
+                        const uint4 b1 = lds128(kc + (g + 8) * 128 + (((2 * t + 1) ^ g) << 4));
+                        wa[0] = a0.x; wa[1] = a0.y; wa[2] = a0.z; wa[3] = a0.w;
+                        wa[4] = a1.x; wa[5] = a1.y; wa[6] = a1.z; wa[7] = a1.w;
+                        wb[0] = b0.x; wb[1] = b0.y; wb[2] = b0.z; wb[3] = b0.w;
+                        wb[4] = b1.x; wb[5] = b1.y; wb[6] = b1.z; wb[7] = b1.w;
+                        const uint2 s_a = *reinterpret_cast<const uint2*>(ks + g * 32 + t * 8);
+                        const uint2 s_b = *reinterpret_cast<const uint2*>(ks + (g + 8) * 32 + t * 8);
+                        sa[0] = s_a.x; sa[1] = s_a.y;
+                        sb[0] = s_b.x; sb[1] = s_b.y;
+                    } else {
+                        const uint4 a0 = lds128(kc + g * 64 + t * 16);
+                        const uint4 b0 = lds128(kc + (g + 8) * 64 + t * 16);
+                        wa[0] = a0.x; wa[1] = a0.y; wa[2] = a0.z; wa[3] = a0.w;
+                        wb[0] = b0.x; wb[1] = b0.y; wb[2] = b0.z; wb[3] = b0.w;
+                        sa[0] = *reinterpret_cast<const uint32_t*>(ks + g * 16 + t * 4);
+                        sb[0] = *reinterpret_cast<const uint32_t*>(ks + (g + 8) * 16 + t * 4);
+                    }
+#pragma unroll
+                    for (int rr = 0; rr < T::kKRegs; ++rr) {
+                        // word rr holds channels 4rr..4rr+3 of the slab: quantisation group rr/2 of the slab
+                        const uint32_t sel = (rr & 2) ? 0x3232u : 0x1010u;
+                        const __half2 s2a = u32_as_h2(prmt(sa[rr >> 2], 0u, sel));
+                        const __half2 s2b = u32_as_h2(prmt(sb[rr >> 2], 0u, sel));
+                        uint32_t a0, a1, a2, a3;
+                        dequant_k_word(wa[rr], s2a, a0, a2);
+                        dequant_k_word(wb[rr], s2b, a1, a3);
+                        mma_m16n8k16_f16f32(sacc, a0, a1, a2, a3, qf[rr][0], qf[rr][1]);
+                    }
+                }
+
+                // ---------------- softmax (exp2 domain, lazy reference maximum) ----------------
+                float s0 = sacc[0] * a.scale_log2;  // token g,   head 2t
+                float s1 = sacc[1] * a.scale_log2;  // token g,   head 2t+1
+                float s2 = sacc[2] * a.scale_log2;  // token g+8, head 2t
+                float s3 = sacc[3] * a.scale_log2;  // token g+8, head 2t+1
+                if (g >= nvalid) {
+                    s0 = kNegBig;
+                    s1 = kNegBig;
+                }
+                if (g + 8 >= nvalid) {
+                    s2 = kNegBig;
+                    s3 = kNegBig;
+                }
+                {
+                    float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
+                    const bool need = (lm0 > m0 + kRescaleSlack) || (lm1 > m1 + kRescaleSlack);
+                    if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+                        for (int off = 4; off <= 16; off <<= 1) {
+                            lm0 = fmaxf(lm0, __shfl_xor_sync(0xffffffffu, lm0, off));
+                            lm1 = fmaxf(lm1, __shfl_xor_sync(0xffffffffu, lm1, off));
+                        }
+                        const float n0 = fmaxf(m0, lm0), n1 = fmaxf(m1, lm1);
+                        const float r0 = ex2_approx(m0 - n0), r1 = ex2_approx(m1 - n1);
+                        m0 = n0;
+                        m1 = n1;
+                        l0 *= r0;
+                        l1 *= r1;
+#pragma unroll
+                        for (int i = 0; i < T::kMTiles; ++i) {
+                            o[i][0] *= r0;
+                            o[i][1] *= r1;
+                            o[i][2] *= r0;
+                            o[i][3] *= r1;
+                        }
+                    }
+                }
+                const float p0 = ex2_approx(s0 - m0), p1 = ex2_approx(s1 - m1);
+                const float p2 = ex2_approx(s2 - m0), p3 = ex2_approx(s3 - m1);
+                l0 += p0 + p2;
+                l1 += p1 + p3;
+                // P^T as the B operand of the second MMA: k = token, n = head
+                const uint32_t pb0 = movmatrix_trans(h2_as_u32(__floats2half2_rn(p0, p1)));
+                const uint32_t pb1 = movmatrix_trans(h2_as_u32(__floats2half2_rn(p2, p3)));
+
+                // ---------------- O^T += V^T * P^T ----------------
+                {
+                    const int ta = 2 * t, tb = 2 * t + 1, tc = 2 * t + 8, td = 2 * t + 9;
+                    uint32_t va[T::kVRegs], vb[T::kVRegs], vcw[T::kVRegs], vd[T::kVRegs];
+                    uint32_t sca, scb, scc, scd;  // scales of the thread's channel groups, per token
+                    if constexpr (DH == 128) {
+                        const uint4 xa = lds128(vc + ta * 128 + ((g ^ (ta & 7)) << 4));
+                        const uint4 xb = lds128(vc + tb * 128 + ((g ^ (tb & 7)) << 4));
+                        const uint4 xc = lds128(vc + tc * 128 + ((g ^ (tc & 7)) << 4));
+                        const uint4 xd = lds128(vc + td * 128 + ((g ^ (td & 7)) << 4));
+                        va[0] = xa.x; va[1] = xa.y; va[2] = xa.z; va[3] = xa.w;
+                        vb[0] = xb.x; vb[1] = xb.y; vb[2] = xb.z; vb[3] = xb.w;
+                        vcw[0] = xc.x; vcw[1] = xc.y; vcw[2] = xc.z; vcw[3] = xc.w;
+                        vd[0] = xd.x; vd[1] = xd.y; vd[2] = xd.z; vd[3] = xd.w;
+                        sca = *reinterpret_cast<const uint32_t*>(vs + ta * 32 + g * 4);
+                        scb = *reinterpret_cast<const uint32_t*>(vs + tb * 32 + g * 4);
+                        scc = *reinterpret_cast<const uint32_t*>(vs + tc * 32 + g * 4);
+                        scd = *reinterpret_cast<const uint32_t*>(vs + td * 32 + g * 4);
+                    } else {
+                        const uint2 xa = *reinterpret_cast<const uint2*>(vc + ta * 64 + g * 8);
+                        const uint2 xb = *reinterpret_cast<const uint2*>(vc + tb * 64 + g * 8);
+                        const uint2 xc = *reinterpret_cast<const uint2*>(vc + tc * 64 + g * 8);
+                        const uint2 xd = *reinterpret_cast<const uint2*>(vc + td * 64 + g * 8);
+                        va[0] = xa.x; va[1] = xa.y;
+                        vb[0] = xb.x; vb[1] = xb.y;
+                        vcw[0] = xc.x; vcw[1] = xc.y;
+                        vd[0] = xd.x; vd[1] = xd.y;
+                        sca = *reinterpret_cast<const uint16_t*>(vs + ta * 16 + g * 2);
+                        scb = *reinterpret_cast<const uint16_t*>(vs + tb * 16 + g * 2);
+                        scc = *reinterpret_cast<const uint16_t*>(vs + tc * 16 + g * 2);
+                        scd = *reinterpret_cast<const uint16_t*>(vs + td * 16 + g * 2);
+                    }
+                    if (nvalid < kTileTok) {
+                        // rows past the end of the sequence hold other data (or nothing): their scales may be
+                        // anything, and 0 * NaN would poison the accumulator even though P is exactly 0 there
+                        sca = ta < nvalid ? sca : 0u;
+                        scb = tb < nvalid ? scb : 0u;
+                        scc = tc < nvalid ? scc : 0u;
+                        scd = td < nvalid ? scd : 0u;
+                    }
+#pragma unroll
+                    for (int q = 0; q < T::kVRegs; ++q) {
+                        // word q holds channels 4q..4q+3 of the thread's slab: group q/2 of the slab
+                        const uint32_t sel = (q & 2) ? 0x7632u : 0x5410u;
+                        const __half2 s_ab = u32_as_h2(prmt(sca, scb, sel));
+                        const __half2 s_cd = u32_as_h2(prmt(scc, scd, sel));
+                        uint32_t hab[4], hcd[4];
+                        dequant_v_pair(va[q], vb[q], s_ab, hab);
+                        dequant_v_pair(vcw[q], vd[q], s_cd, hcd);
+                        mma_m16n8k16_f16f32(o[2 * q], hab[0], hab[1], hcd[0], hcd[1], pb0, pb1);
+                        mma_m16n8k16_f16f32(o[2 * q + 1], hab[2], hab[3], hcd[2], hcd[3], pb0, pb1);
+                    }
+                }
+
+                __syncwarp();  // every lane has read this stage: it may be refilled
+                if (++c_stage == kStages) {
+                    c_stage = 0;
+                    c_phase ^= 1u;
+                }
+                if (gi < hi) {
+                    issue_one();
                 }
             }
 
-            __syncwarp();
-            if (lane == 0 && i + kStages < my_n) {
-                issue(i + kStages);
-            }
-        }
-        tiles_done += static_cast<uint32_t>(my_n);
-
-        // ---------------- merge the warps of this item and write ----------------
-        {
+            // ---------------- end of the piece: write fp16 output or an fp32 partial ----------------
 #pragma unroll
             for (int off = 4; off <= 16; off <<= 1) {
                 l0 += __shfl_xor_sync(0xffffffffu, l0, off);
                 l1 += __shfl_xor_sync(0xffffffffu, l1, off);
             }
-            float* wo = reinterpret_cast<float*>(wsm);  // [8 heads][DH], then max[8], sum[8]
+            const bool complete = (t_first == 0) && (t_end == cc.n);
+            // a range holds at most two partial pieces: its first piece (slot 0) and, if a different one, its
+            // last piece (slot 1)
+            const int64_t slot =
+                (static_cast<int64_t>(r) * a.head_lanes + cls) * 2 + ((t_first > 0 || gc == lo) ? 0 : 1);
 #pragma unroll
-            for (int jt = 0; jt < T::kMTiles; ++jt) {
-                const int ch = (DH / 8) * g + 2 * jt;
-                wo[(2 * t) * DH + ch] = o[jt][0];
-                wo[(2 * t + 1) * DH + ch] = o[jt][1];
-                wo[(2 * t) * DH + ch + 1] = o[jt][2];
-                wo[(2 * t + 1) * DH + ch + 1] = o[jt][3];
-            }
-            if (g == 0) {
-                wo[8 * DH + 2 * t] = m0;
-                wo[8 * DH + 2 * t + 1] = m1;
-                wo[8 * DH + 8 + 2 * t] = l0;
-                wo[8 * DH + 8 + 2 * t + 1] = l1;
-            }
-        }
-        __syncthreads();
-        for (int e = threadIdx.x; e < HW * 8 * DH; e += kThreads) {
-            const int hs = e / (8 * DH);
-            const int r = e - hs * (8 * DH);
-            const int h8 = r / DH;
-            const int ch = r - h8 * DH;
-            const int vh = hset * HW + hs;
-            const int kvh_e = vh / a.octets;
-            const int hq_in_group = (vh - kvh_e * a.octets) * 8 + h8;
-            if (hq_in_group >= a.group) {
-                continue;
-            }
-            float mx = kNegBig;
-            for (int w = hs; w < kWarps; w += HW) {
-                const float* src = reinterpret_cast<const float*>(smem + w * T::kWarpBytes);
-                mx = fmaxf(mx, src[8 * DH + h8]);
-            }
-            float acc = 0.0f, den = 0.0f;
-            for (int w = hs; w < kWarps; w += HW) {
-                const float* src = reinterpret_cast<const float*>(smem + w * T::kWarpBytes);
-                const float wgt = ex2_approx(src[8 * DH + h8] - mx);
-                acc += wgt * src[h8 * DH + ch];
-                den += wgt * src[8 * DH + 8 + h8];
-            }
-            const int qhead = kvh_e * a.group + hq_in_group;
-            if (nsplits == 1) {
-                const float v = den > 0.0f ? acc / den : 0.0f;
-                a.out[(qtok * a.num_heads + qhead) * DH + ch] = __float2half_rn(v);
-            } else {
-                const int64_t slot = static_cast<int64_t>(first_split + split) * a.num_heads + qhead;
-                a.part_o[slot * DH + ch] = acc;
-                if (ch == 0) {
-                    a.part_ml[slot * 2] = mx;
-                    a.part_ml[slot * 2 + 1] = den;
+            for (int hh = 0; hh < 2; ++hh) {
+                const int h8 = 2 * t + hh;
+                const int hq_in_group = oct * 8 + h8;
+                if (hq_in_group >= a.group) {
+                    continue;
+                }
+                const float lsum = hh ? l1 : l0;
+                if (complete) {
+                    const float inv = lsum > 0.0f ? 1.0f / lsum : 0.0f;
+                    __half* dst = a.out + (qtok * a.num_heads + kvh * a.group + hq_in_group) * DH + (DH / 8) * g;
+#pragma unroll
+                    for (int jj = 0; jj < T::kMTiles / 4; ++jj) {
+                        uint4 v;
+                        v.x = h2_as_u32(__floats2half2_rn(o[4 * jj][hh] * inv, o[4 * jj][hh + 2] * inv));
+                        v.y = h2_as_u32(__floats2half2_rn(o[4 * jj + 1][hh] * inv, o[4 * jj + 1][hh + 2] * inv));
+                        v.z = h2_as_u32(__floats2half2_rn(o[4 * jj + 2][hh] * inv, o[4 * jj + 2][hh + 2] * inv));
+                        v.w = h2_as_u32(__floats2half2_rn(o[4 * jj + 3][hh] * inv, o[4 * jj + 3][hh + 2] * inv));
+                        *reinterpret_cast<uint4*>(dst + 8 * jj) = v;
+                    }
+                } else {
+                    float* dst = a.part_o + (slot * 8 + h8) * DH + (DH / 8) * g;
+#pragma unroll
+                    for (int jj = 0; jj < T::kMTiles / 2; ++jj) {
+                        *reinterpret_cast<float4*>(dst + 4 * jj) =
+                            make_float4(o[2 * jj][hh], o[2 * jj][hh + 2], o[2 * jj + 1][hh], o[2 * jj + 1][hh + 2]);
+                    }
+                    if (g == 0) {
+                        a.part_ml[(slot * 8 + h8) * 2] = hh ? m1 : m0;
+                        a.part_ml[(slot * 8 + h8) * 2 + 1] = lsum;
+                    }
                 }
             }
+            gc += t_end - t_first;
+            advance(cc, t_end - t_first);
         }
-        // the stage buffers were read and written through the generic proxy; order that before the
-        // bulk-tensor copies of the next item land in them
-        fence_proxy_async_smem();
-        __syncthreads();
     }
 }
 
 // ------------------------------------------------------------------------------------------
-// Second pass: merge the fp32 partials of sequences that were split.  One warp per
+// Second pass: merge the fp32 partials of segments that were cut by range boundaries.  One warp per
 // (sequence, query head).
 // ------------------------------------------------------------------------------------------
 template <int DH>
 __global__ void __launch_bounds__(256)
-decode_reduce_kernel(const int32_t* __restrict__ split_starts, const float* __restrict__ part_ml,
-                     const float* __restrict__ part_o, const int64_t* __restrict__ seqstarts,
-                     __half* __restrict__ out, int32_t decoding_batches, int32_t num_heads) {
+decode_reduce_kernel(const PlanHeader* __restrict__ hdr, const int32_t* __restrict__ tile_prefix,
+                     const float* __restrict__ part_ml, const float* __restrict__ part_o,
+                     const int64_t* __restrict__ seqstarts, __half* __restrict__ out, int32_t decoding_batches,
+                     int32_t num_heads, int32_t group, int32_t octets, int32_t head_lanes, int32_t class_heads) {
+    if (hdr->per_segment) {
+        return;  // split-k off: every segment was written whole
+    }
     const int64_t wg = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (wg >= static_cast<int64_t>(decoding_batches) * num_heads) {
@@ -552,14 +625,29 @@ decode_reduce_kernel(const int32_t* __restrict__ split_starts, const float* __re
     }
     const int32_t b = static_cast<int32_t>(wg / num_heads);
     const int32_t qh = static_cast<int32_t>(wg - static_cast<int64_t>(b) * num_heads);
-    const int32_t first = split_starts[b];
-    const int32_t ns = split_starts[b + 1] - first;
-    if (ns <= 1) {
-        return;
+    const int32_t kvh = qh / group;
+    const int32_t hq = qh - kvh * group;
+    const int32_t vh = kvh * octets + (hq >> 3);
+    const int32_t h8 = hq & 7;
+    const int64_t R = hdr->range_tiles;
+    const int32_t n = tile_prefix[b + 1] - tile_prefix[b];
+    const int32_t cls = vh % head_lanes;
+    const int32_t vc = vh / head_lanes;
+    const int64_t seg_lo = static_cast<int64_t>(tile_prefix[b]) * class_heads + static_cast<int64_t>(vc) * n;
+    const int64_t seg_hi = seg_lo + n;
+    const int64_t r_first = seg_lo / R;
+    const int64_t r_last = (seg_hi - 1) / R;
+    if (r_first == r_last) {
+        return;  // the segment lies inside one range and was written whole
     }
+    auto slot_of = [&](int64_t rr) -> int64_t {
+        // the piece is the range's first piece unless the segment starts strictly inside the range
+        const int64_t s = (rr == r_first && seg_lo > rr * R) ? 1 : 0;
+        return ((rr * head_lanes + cls) * 2 + s) * 8 + h8;
+    };
     float mx = kNegBig;
-    for (int32_t s = lane; s < ns; s += 32) {
-        mx = fmaxf(mx, part_ml[(static_cast<int64_t>(first + s) * num_heads + qh) * 2]);
+    for (int64_t rr = r_first + lane; rr <= r_last; rr += 32) {
+        mx = fmaxf(mx, part_ml[slot_of(rr) * 2]);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -572,11 +660,11 @@ decode_reduce_kernel(const int32_t* __restrict__ split_starts, const float* __re
         acc[i] = 0.0f;
     }
     float den = 0.0f;
-    for (int32_t s = 0; s < ns; ++s) {
-        const int64_t slot = static_cast<int64_t>(first + s) * num_heads + qh;
-        const float w = ex2_approx(part_ml[slot * 2] - mx);
-        den += w * part_ml[slot * 2 + 1];
-        const float* po = part_o + slot * DH + lane * kPer;
+    for (int64_t rr = r_first; rr <= r_last; ++rr) {
+        const int64_t sl = slot_of(rr);
+        const float w = ex2_approx(part_ml[sl * 2] - mx);
+        den += w * part_ml[sl * 2 + 1];
+        const float* po = part_o + sl * DH + lane * kPer;
 #pragma unroll
         for (int i = 0; i < kPer; ++i) {
             acc[i] += w * po[i];
@@ -605,47 +693,30 @@ int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* pla
     const int group = p.num_heads / p.num_kv_heads;
     d.octets = (group + 7) / 8;
     d.num_vheads = static_cast<int64_t>(p.num_kv_heads) * d.octets;
-    d.head_warps = (d.num_vheads % 4 == 0) ? 4 : ((d.num_vheads % 2 == 0) ? 2 : 1);
-    d.token_warps = kWarps / d.head_warps;
-    d.num_hsets = d.num_vheads / d.head_warps;
-
-    const int64_t slots = static_cast<int64_t>(sm_count) * 2;
-    const int64_t max_kv = p.max_kvlen > 0 ? p.max_kvlen : 1;
-    const int64_t whole = (max_kv + 63) / 64 * 64;
-    int64_t chunk = whole;
-    if (p.split_k_mode != 0 && DB > 0) {
-        // Bound the largest work item to ~1/16 of a CTA slot's share of the (upper bound of the) work,
-        // but keep splits long enough that their fp32 partials stay a small fraction of the traffic.
-        const int64_t min_chunk = group >= 4 ? 512 : 256;
-        int64_t target = DB * d.num_hsets * max_kv / (slots * 16);
-        target = (target + 63) / 64 * 64;
-        chunk = target < min_chunk ? min_chunk : target;
-        if (p.split_k_mode == 2) {
-            const int64_t half = ((max_kv + 1) / 2 + 63) / 64 * 64;
-            chunk = chunk < half ? chunk : half;
+    d.head_lanes = (d.num_vheads % 4 == 0) ? 4 : ((d.num_vheads % 2 == 0) ? 2 : 1);
+    d.class_heads = d.num_vheads / d.head_lanes;
+    d.grid = static_cast<int64_t>(sm_count) * kCtasPerSm;
+    d.workers = d.grid * (kWarps / d.head_lanes);  // resident warps per head class
+    // upper bound of the number of ranges (per class) the planning kernel may create
+    if (p.split_k_mode == 0 || DB == 0) {
+        d.max_ranges = DB * d.class_heads;
+        d.partial_slots = 0;
+    } else {
+        d.max_ranges = d.workers;
+        if (p.split_k_mode == 2 && 2 * DB * d.class_heads + 1 > d.max_ranges) {
+            d.max_ranges = 2 * DB * d.class_heads + 1;
         }
-        chunk = chunk > whole ? whole : chunk;
-        chunk = chunk < 64 ? 64 : chunk;
+        d.partial_slots = 2 * d.max_ranges * d.head_lanes;
     }
-    d.chunk_tokens = chunk;
-    d.max_splits = (max_kv + chunk - 1) / chunk;
-    const int64_t items_ub = DB * d.max_splits * d.num_hsets;
-    d.grid = items_ub < slots ? items_ub : slots;
-    if (d.grid < 1) {
-        d.grid = 1;
-    }
-
     uint64_t off = 0;
-    d.off_status = off;
-    d.off_counter = off + 4;
+    d.off_header = off;  // the status word is the first word of the header
     off = 256;
-    d.off_split_starts = off;
+    d.off_tile_prefix = off;
     off = align_up_u64(off + static_cast<uint64_t>(DB + 1) * 4, 256);
-    const uint64_t slots_ub = d.max_splits > 1 ? static_cast<uint64_t>(DB) * d.max_splits * p.num_heads : 0;
     d.off_part_ml = off;
-    off = align_up_u64(off + slots_ub * 2 * 4, 256);
+    off = align_up_u64(off + static_cast<uint64_t>(d.partial_slots) * 8 * 2 * 4, 256);
     d.off_part_o = off;
-    off = align_up_u64(off + slots_ub * p.head_dim * 4, 256);
+    off = align_up_u64(off + static_cast<uint64_t>(d.partial_slots) * 8 * p.head_dim * 4, 256);
     d.bytes = off;
     return PPLB200_SUCCESS;
 }
@@ -656,10 +727,10 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
                             const int64_t* start_pos, const void* cache, const void* scale, void* workspace,
                             void* attn_output, cudaStream_t stream) {
     using T = Traits<DH>;
+    static_assert(sizeof(PlanHeader) <= 256, "the header must fit in front of the prefix sums");
     uint8_t* ws = static_cast<uint8_t*>(workspace);
-    uint32_t* status = reinterpret_cast<uint32_t*>(ws + plan.off_status);
-    int32_t* counter = reinterpret_cast<int32_t*>(ws + plan.off_counter);
-    int32_t* split_starts = reinterpret_cast<int32_t*>(ws + plan.off_split_starts);
+    PlanHeader* hdr = reinterpret_cast<PlanHeader*>(ws + plan.off_header);
+    int32_t* tile_prefix = reinterpret_cast<int32_t*>(ws + plan.off_tile_prefix);
 
     CUtensorMap tm_codes, tm_scales;
     CacheMapOrder order;
@@ -669,8 +740,9 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     }
 
     decode_plan_kernel<<<1, kPlanThreads, 0, stream>>>(seqstarts, start_pos, static_cast<int32_t>(p.decoding_batches),
-                                                       plan.chunk_tokens, p.max_kvlen, split_starts, counter, status,
-                                                       1);
+                                                       static_cast<int32_t>(plan.class_heads), p.max_kvlen,
+                                                       p.split_k_mode, static_cast<int32_t>(plan.workers),
+                                                       static_cast<int32_t>(plan.max_ranges), hdr, tile_prefix);
     rc = check_launch("decode_plan_kernel");
     if (rc != PPLB200_SUCCESS) {
         return rc;
@@ -682,22 +754,18 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.seqstarts = seqstarts;
     a.cachestarts = cachestarts;
     a.start_pos = start_pos;
-    a.status = status;
-    a.counter = counter;
-    a.split_starts = split_starts;
+    a.hdr = hdr;
+    a.tile_prefix = tile_prefix;
     a.part_ml = reinterpret_cast<float*>(ws + plan.off_part_ml);
     a.part_o = reinterpret_cast<float*>(ws + plan.off_part_o);
     a.geom = geom;
-    a.chunk_tokens = plan.chunk_tokens;
     a.max_kvlen = p.max_kvlen;
     a.decoding_batches = static_cast<int32_t>(p.decoding_batches);
     a.num_heads = p.num_heads;
-    a.num_kv_heads = p.num_kv_heads;
     a.group = p.num_heads / p.num_kv_heads;
     a.octets = plan.octets;
-    a.head_warps = plan.head_warps;
-    a.token_warps = plan.token_warps;
-    a.num_hsets = static_cast<int32_t>(plan.num_hsets);
+    a.head_lanes = plan.head_lanes;
+    a.class_heads = static_cast<int32_t>(plan.class_heads);
     a.layer_idx = p.layer_idx;
     a.order = order;
     a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
@@ -712,20 +780,27 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
         }
         attr_set = true;
     }
+    // never more CTAs than there can be ranges
+    int64_t grid = plan.grid;
+    const int64_t per_cta = kWarps / plan.head_lanes;
+    if ((plan.max_ranges + per_cta - 1) / per_cta < grid) {
+        grid = (plan.max_ranges + per_cta - 1) / per_cta;
+    }
     {
         KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
-        decode_splitk_kernel<DH><<<static_cast<unsigned>(plan.grid), kThreads, T::kSmemBytes, stream>>>(
-            tm_codes, tm_scales, a);
+        decode_splitk_kernel<DH><<<static_cast<unsigned>(grid), kThreads, T::kSmemBytes, stream>>>(tm_codes, tm_scales,
+                                                                                                  a);
     }
     rc = check_launch("decode_splitk_kernel");
     if (rc != PPLB200_SUCCESS) {
         return rc;
     }
-    if (plan.max_splits > 1) {
+    if (p.split_k_mode != 0) {
         const int64_t warps = p.decoding_batches * p.num_heads;
         const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
-        decode_reduce_kernel<DH><<<blocks, 256, 0, stream>>>(split_starts, a.part_ml, a.part_o, seqstarts, a.out,
-                                                             a.decoding_batches, p.num_heads);
+        decode_reduce_kernel<DH><<<blocks, 256, 0, stream>>>(hdr, tile_prefix, a.part_ml, a.part_o, seqstarts, a.out,
+                                                             a.decoding_batches, p.num_heads, a.group, a.octets,
+                                                             a.head_lanes, a.class_heads);
         rc = check_launch("decode_reduce_kernel");
     }
     return rc;

@@ -50,16 +50,16 @@ int launch_kv_gather_dequant(const pplb200_attn_params& p, const CacheGeom& geom
 // Host-side plan: pure function of the params and the SM count, used both for the workspace size
 // and for the launch, so the two always agree.
 struct DecodePlan {
-    int64_t chunk_tokens;      // tokens per split (a multiple of 64)
-    int64_t max_splits;        // ceil(max_kvlen / chunk_tokens)
     int32_t octets;            // ceil(group / 8): query-head octets per kv head
-    int32_t head_warps;        // warps of a CTA that work on different (kv head, octet) pairs
-    int32_t token_warps;       // warps of a CTA that share one pair and split its tokens
-    int64_t num_vheads;        // num_kv_heads * octets
-    int64_t num_hsets;         // num_vheads / head_warps
-    int64_t grid;              // persistent CTAs
+    int64_t num_vheads;        // num_kv_heads * octets: segments per sequence
+    int32_t head_lanes;        // 4, 2 or 1 head classes: warps of a CTA that stream adjacent heads of the same rows
+    int64_t class_heads;       // num_vheads / head_lanes
+    int64_t grid;              // persistent CTAs (4 warps each)
+    int64_t workers;           // resident warps per head class
+    int64_t max_ranges;        // upper bound of the ranges (per class) the planning kernel may create
+    int64_t partial_slots;     // fp32 partial records in the workspace (2 per range and class)
     // workspace layout (byte offsets)
-    uint64_t off_status, off_counter, off_split_starts, off_part_ml, off_part_o, bytes;
+    uint64_t off_header, off_tile_prefix, off_part_ml, off_part_o, bytes;
 };
 int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* plan);
 
