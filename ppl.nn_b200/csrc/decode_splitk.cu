@@ -97,17 +97,55 @@ struct DecodeArgs {
     float scale_log2;
 };
 
-// One head's tile of `kTileTok` cache rows, through a map whose outer dimensions are ordered by
-// stride (see CacheMapOrder).
-__device__ __forceinline__ void tma_load_cache_tile(void* dst, const CUtensorMap* map, uint64_t* bar,
+// Order of the four outer dimensions of the cache tensor maps (see CacheMapOrder), as a template
+// parameter so that the coordinates of a copy cost nothing to assemble in the two standard layouts.
+constexpr int kOrderRowLast = 0;   // (head, k|v, layer, row): cache_layout 0
+constexpr int kOrderRowFirst = 1;  // (row, head, k|v, layer): cache_layout 3
+constexpr int kOrderGeneric = 2;   // anything else: positions looked up at run time
+
+// One head's tile of `kTileTok` cache rows -> shared memory at `dst` (a shared-space address).
+template <int ORDER>
+__device__ __forceinline__ void tma_load_cache_tile(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                                     const CacheMapOrder& od, int row, int head, int kv, int layer) {
-    int c[4];
+    int c1, c2, c3, c4;
+    if constexpr (ORDER == kOrderRowLast) {
+        c1 = head; c2 = kv; c3 = layer; c4 = row;
+    } else if constexpr (ORDER == kOrderRowFirst) {
+        c1 = row; c2 = head; c3 = kv; c4 = layer;
+    } else {
+        int c[4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int pos = i + 1;
-        c[i] = od.pos_row == pos ? row : (od.pos_head == pos ? head : (od.pos_kv == pos ? kv : layer));
+        for (int i = 0; i < 4; ++i) {
+            const int pos = i + 1;
+            c[i] = od.pos_row == pos ? row : (od.pos_head == pos ? head : (od.pos_kv == pos ? kv : layer));
+        }
+        c1 = c[0]; c2 = c[1]; c3 = c[2]; c4 = c[3];
     }
-    tma_load_5d(dst, map, bar, 0, c[0], c[1], c[2], c[3]);
+    asm volatile(
+        "cp.async.bulk.tensor.5d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
+        : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -190,9 +228,6 @@ decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restr
 // ------------------------------------------------------------------------------------------
 // Main kernel
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint4 lds128(const uint8_t* p) {
-    return *reinterpret_cast<const uint4*>(p);
-}
 
 // K codes word -> two half2 (channels 0,1 and 2,3 of the word), scaled.
 __device__ __forceinline__ void dequant_k_word(uint32_t w, __half2 s2, uint32_t& lo, uint32_t& hi) {
@@ -213,19 +248,19 @@ __device__ __forceinline__ void dequant_v_pair(uint32_t wa, uint32_t wb, __half2
 
 // Position in the tile sequence of one head class: sequence b, class-local head index vc (the virtual
 // head, i.e. kv head x octet of query heads, is vc * head_lanes + class), tile index within the
-// segment, tiles per segment of this sequence, first cache row of the sequence.
+// segment, tiles per segment of this sequence, first cache row of the sequence and the kv head.
 struct Cursor {
     int32_t b, vc, tile, n;
-    int64_t row_base;
+    int32_t row_base;
+    int32_t kvh;
 };
 
-template <int DH>
+template <int DH, int ORDER>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_scales,
                      const DecodeArgs a) {
     using T = Traits<DH>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full_bar[kWarps * kStages];
     __shared__ int32_t s_base;
 
@@ -244,8 +279,27 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
     }
     __syncthreads();
 
-    uint8_t* wsm = smem + warp * T::kWarpBytes;
-    uint64_t* wbar = full_bar + warp * kStages;
+    // shared-space addresses of this warp's stage ring (1 KB aligned for the 128-byte swizzle) and barriers
+    const uint32_t wsm = ((smem_u32(smem_raw) + 1023u) & ~1023u) + warp * T::kWarpBytes;
+    const uint32_t wbar = smem_u32(full_bar + warp * kStages);
+    // per-thread byte offsets into a stage, fixed for the whole kernel
+    //   K rows g and g+8: the thread's channel slab (two 16-byte chunks at Dh 128, swizzled by the row);
+    //   V rows 2t, 2t+1 (+8): the thread's channel slab (one chunk, swizzled by the row)
+    uint32_t k_off, ks_off, v_off_a, v_off_b, vs_off;
+    if constexpr (DH == 128) {
+        k_off = g * 128 + (((2 * t) ^ g) << 4);
+        ks_off = 2 * T::kCodeBytes + g * 32 + t * 8;
+        v_off_a = T::kCodeBytes + (2 * t) * 128 + ((g ^ (2 * t)) << 4);
+        v_off_b = T::kCodeBytes + (2 * t + 1) * 128 + ((g ^ (2 * t + 1)) << 4);
+        vs_off = 2 * T::kCodeBytes + T::kScaleBytes + (2 * t) * 32 + g * 4;
+    } else {
+        k_off = g * 64 + t * 16;
+        ks_off = 2 * T::kCodeBytes + g * 16 + t * 4;
+        v_off_a = T::kCodeBytes + (2 * t) * 64 + g * 8;
+        v_off_b = v_off_a + 64;
+        vs_off = 2 * T::kCodeBytes + T::kScaleBytes + (2 * t) * 16 + g * 2;
+    }
+
     uint32_t c_stage = 0, c_phase = 0;  // consume position in the stage ring
     uint32_t i_stage = 0;               // issue position in the stage ring
     bool wait_dead = false;             // set after the first timed-out wait: stop waiting, just finish
@@ -259,8 +313,16 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
     const int32_t range_tiles = a.hdr->range_tiles;
     const int32_t per_segment = a.hdr->per_segment;
     const int64_t total_tiles = a.hdr->total_tiles;
+    const bool paged = a.geom.cache_mode != 0;
+    const int octets = a.octets;
+    const int head_lanes = a.head_lanes;
+    const int layer = a.layer_idx;
 
-    auto seq_row_base = [&](int32_t b) -> int64_t { return a.geom.cache_mode == 0 ? a.cachestarts[b] : 0; };
+    auto load_seq = [&](Cursor& c) {  // per-sequence fields
+        c.n = a.tile_prefix[c.b + 1] - a.tile_prefix[c.b];
+        c.row_base = paged ? 0 : static_cast<int32_t>(a.cachestarts[c.b]);
+    };
+    auto set_head = [&](Cursor& c) { c.kvh = octets == 1 ? c.vc * head_lanes + cls : (c.vc * head_lanes + cls) / octets; };
     auto advance = [&](Cursor& c, int32_t by) {
         // moves within the segment or to the start of the next one (by never crosses two boundaries)
         c.tile += by;
@@ -270,10 +332,10 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
                 c.vc = 0;
                 ++c.b;
                 if (c.b < DB) {
-                    c.n = a.tile_prefix[c.b + 1] - a.tile_prefix[c.b];
-                    c.row_base = seq_row_base(c.b);
+                    load_seq(c);
                 }
             }
+            set_head(c);
         }
     };
 
@@ -290,14 +352,14 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
         if (r >= num_ranges) {
             continue;
         }
-        // ---- the range [lo, hi) of the global tile sequence and the segment it starts in ----
+        // ---- the range [lo, hi) of the class's tile sequence and the segment it starts in ----
         int64_t lo, hi;
         Cursor cc;
         if (per_segment) {
             cc.b = r / nvc;
             cc.vc = r - cc.b * nvc;
             cc.tile = 0;
-            cc.n = a.tile_prefix[cc.b + 1] - a.tile_prefix[cc.b];
+            load_seq(cc);
             lo = static_cast<int64_t>(a.tile_prefix[cc.b]) * nvc + static_cast<int64_t>(cc.vc) * cc.n;
             hi = lo + cc.n;
         } else {
@@ -314,52 +376,51 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
                 }
             }
             cc.b = l;
-            const int32_t base = a.tile_prefix[l];
-            cc.n = a.tile_prefix[l + 1] - base;
-            const int64_t rem = lo - static_cast<int64_t>(base) * nvc;
+            load_seq(cc);
+            const int64_t rem = lo - static_cast<int64_t>(a.tile_prefix[l]) * nvc;
             cc.vc = static_cast<int32_t>(rem / cc.n);
             cc.tile = static_cast<int32_t>(rem - static_cast<int64_t>(cc.vc) * cc.n);
         }
-        cc.row_base = seq_row_base(cc.b);
-        Cursor ic = cc;      // issue cursor: runs up to kStages tiles ahead of the consume cursor
-        int64_t gi = lo;     // global index of the next tile to issue
+        set_head(cc);
+        Cursor ic = cc;                                // issue cursor: runs up to kStages tiles ahead
+        int32_t to_issue = static_cast<int32_t>(hi - lo);  // tiles of the range not yet issued
+        int32_t to_consume = to_issue;
 
         auto issue_one = [&]() {
             if (lane == 0) {
-                const int64_t tok = static_cast<int64_t>(ic.tile) * kTileTok;
-                const int row = static_cast<int>(a.geom.cache_mode == 0 ? ic.row_base + tok
-                                                                         : cache_row(a.geom, a.cachestarts, ic.b, tok));
-                const int kvh = (ic.vc * a.head_lanes + cls) / a.octets;
-                uint8_t* st = wsm + i_stage * T::kStageBytes;
-                uint64_t* bar = &wbar[i_stage];
-                mbar_arrive_expect_tx(bar, T::kStageBytes);
-                tma_load_cache_tile(st, &tmap_codes, bar, a.order, row, kvh, 0, a.layer_idx);
-                tma_load_cache_tile(st + T::kCodeBytes, &tmap_codes, bar, a.order, row, kvh, 1, a.layer_idx);
-                tma_load_cache_tile(st + 2 * T::kCodeBytes, &tmap_scales, bar, a.order, row, kvh, 0, a.layer_idx);
-                tma_load_cache_tile(st + 2 * T::kCodeBytes + T::kScaleBytes, &tmap_scales, bar, a.order, row, kvh, 1,
-                                    a.layer_idx);
+                const int tok = ic.tile * kTileTok;
+                const int row = paged ? static_cast<int>(cache_row(a.geom, a.cachestarts, ic.b, tok)) : ic.row_base + tok;
+                const uint32_t st = wsm + i_stage * T::kStageBytes;
+                const uint32_t bar = wbar + i_stage * 8;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(T::kStageBytes)
+                             : "memory");
+                tma_load_cache_tile<ORDER>(st, &tmap_codes, bar, a.order, row, ic.kvh, 0, layer);
+                tma_load_cache_tile<ORDER>(st + T::kCodeBytes, &tmap_codes, bar, a.order, row, ic.kvh, 1, layer);
+                tma_load_cache_tile<ORDER>(st + 2 * T::kCodeBytes, &tmap_scales, bar, a.order, row, ic.kvh, 0, layer);
+                tma_load_cache_tile<ORDER>(st + 2 * T::kCodeBytes + T::kScaleBytes, &tmap_scales, bar, a.order, row,
+                                           ic.kvh, 1, layer);
             }
             i_stage = (i_stage + 1 == kStages) ? 0 : i_stage + 1;
             advance(ic, 1);
-            ++gi;
+            --to_issue;
         };
-        for (int i = 0; i < kStages && gi < hi; ++i) {
+        for (int i = 0; i < kStages && to_issue > 0; ++i) {
             issue_one();
         }
 
-        int64_t gc = lo;  // global index of the next tile to consume
-        while (gc < hi) {
+        bool first_piece = true;
+        while (to_consume > 0) {
             // ---- one piece: the part of segment (cc.b, cc.vc) that lies inside the range ----
             const int32_t t_first = cc.tile;
-            const int64_t left = hi - gc;
-            const int32_t t_end = (cc.n - t_first) <= left ? cc.n : t_first + static_cast<int32_t>(left);
+            const int32_t t_end = (cc.n - t_first) <= to_consume ? cc.n : t_first + to_consume;
             const int32_t b = cc.b;
-            const int vh = cc.vc * a.head_lanes + cls;
-            const int kvh = vh / a.octets;
-            const int oct = vh - kvh * a.octets;
+            const int vh = cc.vc * head_lanes + cls;
+            const int kvh = cc.kvh;
+            const int oct = vh - kvh * octets;
             const int64_t qtok = a.seqstarts[b];
-            int64_t kvlen = a.start_pos[b] + (a.seqstarts[b + 1] - qtok);
-            kvlen = kvlen > a.max_kvlen ? a.max_kvlen : kvlen;
+            int64_t kvlen64 = a.start_pos[b] + (a.seqstarts[b + 1] - qtok);
+            kvlen64 = kvlen64 > a.max_kvlen ? a.max_kvlen : kvlen64;
+            const int32_t kvlen = static_cast<int32_t>(kvlen64);
 
             // Q fragments (B operand: k = channel, n = query head of the group)
             uint32_t qf[T::kKRegs][2];
@@ -392,53 +453,49 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
 
             for (int32_t tile = t_first; tile < t_end; ++tile) {
                 if (!wait_dead) {
-                    if (!mbar_wait_bounded(&wbar[c_stage], c_phase)) {
+                    if (!mbar_wait_bounded(reinterpret_cast<uint64_t*>(full_bar + warp * kStages + c_stage), c_phase)) {
                         wait_dead = true;
                         if (lane == 0) {
                             atomicOr(&a.hdr->status, kDevTmaTimeout);
                         }
                     }
                 }
-                const uint8_t* st = wsm + c_stage * T::kStageBytes;
-                const uint8_t* kc = st;
-                const uint8_t* vc = st + T::kCodeBytes;
-                const uint8_t* ks = st + 2 * T::kCodeBytes;
-                const uint8_t* vs = ks + T::kScaleBytes;
-                const int64_t tok0 = static_cast<int64_t>(tile) * kTileTok;
-                const int nvalid = (kvlen - tok0) < kTileTok ? static_cast<int>(kvlen - tok0) : kTileTok;
+                const uint32_t st = wsm + c_stage * T::kStageBytes;
+                const int nvalid = kvlen - tile * kTileTok;  // >= 16 except in the last tile of the sequence
 
                 // ---------------- S^T = K * Q^T ----------------
                 float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                 {
                     uint32_t wa[T::kKRegs], wb[T::kKRegs];          // rows g and g+8, this thread's channel slab
                     uint32_t sa[T::kKRegs / 4], sb[T::kKRegs / 4];  // packed group scales (2 halves per word)
+                    const uint32_t ka = st + k_off;
                     if constexpr (DH == 128) {
-                        const uint4 a0 = lds128(kc + g * 128 + (((2 * t) ^ g) << 4));
-                        const uint4 a1 = lds128(kc + g * 128 + (((2 * t + 1) ^ g) << 4));
-                        const uint4 b0 = lds128(kc + (g + 8) * 128 + (((2 * t) ^ g) << 4));
-                        const uint4 b1 = lds128(kc + (g + 8) * 128 + (((2 * t + 1) ^ g) << 4));
+                        const uint4 a0 = lds128(ka);
+                        const uint4 a1 = lds128(ka ^ 16u);
+                        const uint4 b0 = lds128(ka + 1024u);
+                        const uint4 b1 = lds128((ka ^ 16u) + 1024u);
                         wa[0] = a0.x; wa[1] = a0.y; wa[2] = a0.z; wa[3] = a0.w;
                         wa[4] = a1.x; wa[5] = a1.y; wa[6] = a1.z; wa[7] = a1.w;
                         wb[0] = b0.x; wb[1] = b0.y; wb[2] = b0.z; wb[3] = b0.w;
                         wb[4] = b1.x; wb[5] = b1.y; wb[6] = b1.z; wb[7] = b1.w;
-                        const uint2 s_a = *reinterpret_cast<const uint2*>(ks + g * 32 + t * 8);
-                        const uint2 s_b = *reinterpret_cast<const uint2*>(ks + (g + 8) * 32 + t * 8);
+                        const uint2 s_a = lds64(st + ks_off);
+                        const uint2 s_b = lds64(st + ks_off + 256u);
                         sa[0] = s_a.x; sa[1] = s_a.y;
                         sb[0] = s_b.x; sb[1] = s_b.y;
                     } else {
-                        const uint4 a0 = lds128(kc + g * 64 + t * 16);
-                        const uint4 b0 = lds128(kc + (g + 8) * 64 + t * 16);
+                        const uint4 a0 = lds128(ka);
+                        const uint4 b0 = lds128(ka + 512u);
                         wa[0] = a0.x; wa[1] = a0.y; wa[2] = a0.z; wa[3] = a0.w;
                         wb[0] = b0.x; wb[1] = b0.y; wb[2] = b0.z; wb[3] = b0.w;
-                        sa[0] = *reinterpret_cast<const uint32_t*>(ks + g * 16 + t * 4);
-                        sb[0] = *reinterpret_cast<const uint32_t*>(ks + (g + 8) * 16 + t * 4);
+                        sa[0] = lds32(st + ks_off);
+                        sb[0] = lds32(st + ks_off + 128u);
                     }
 #pragma unroll
                     for (int rr = 0; rr < T::kKRegs; ++rr) {
                         // word rr holds channels 4rr..4rr+3 of the slab: quantisation group rr/2 of the slab
-                        const uint32_t sel = (rr & 2) ? 0x3232u : 0x1010u;
-                        const __half2 s2a = u32_as_h2(prmt(sa[rr >> 2], 0u, sel));
-                        const __half2 s2b = u32_as_h2(prmt(sb[rr >> 2], 0u, sel));
+                        const __half2 pa = u32_as_h2(sa[rr >> 2]), pb = u32_as_h2(sb[rr >> 2]);
+                        const __half2 s2a = (rr & 2) ? __high2half2(pa) : __low2half2(pa);
+                        const __half2 s2b = (rr & 2) ? __high2half2(pb) : __low2half2(pb);
                         uint32_t a0, a1, a2, a3;
                         dequant_k_word(wa[rr], s2a, a0, a2);
                         dequant_k_word(wb[rr], s2b, a1, a3);
@@ -493,43 +550,42 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
 
                 // ---------------- O^T += V^T * P^T ----------------
                 {
-                    const int ta = 2 * t, tb = 2 * t + 1, tc = 2 * t + 8, td = 2 * t + 9;
                     uint32_t va[T::kVRegs], vb[T::kVRegs], vcw[T::kVRegs], vd[T::kVRegs];
                     uint32_t sca, scb, scc, scd;  // scales of the thread's channel groups, per token
                     if constexpr (DH == 128) {
-                        const uint4 xa = lds128(vc + ta * 128 + ((g ^ (ta & 7)) << 4));
-                        const uint4 xb = lds128(vc + tb * 128 + ((g ^ (tb & 7)) << 4));
-                        const uint4 xc = lds128(vc + tc * 128 + ((g ^ (tc & 7)) << 4));
-                        const uint4 xd = lds128(vc + td * 128 + ((g ^ (td & 7)) << 4));
+                        const uint4 xa = lds128(st + v_off_a);
+                        const uint4 xb = lds128(st + v_off_b);
+                        const uint4 xc = lds128(st + v_off_a + 1024u);
+                        const uint4 xd = lds128(st + v_off_b + 1024u);
                         va[0] = xa.x; va[1] = xa.y; va[2] = xa.z; va[3] = xa.w;
                         vb[0] = xb.x; vb[1] = xb.y; vb[2] = xb.z; vb[3] = xb.w;
                         vcw[0] = xc.x; vcw[1] = xc.y; vcw[2] = xc.z; vcw[3] = xc.w;
                         vd[0] = xd.x; vd[1] = xd.y; vd[2] = xd.z; vd[3] = xd.w;
-                        sca = *reinterpret_cast<const uint32_t*>(vs + ta * 32 + g * 4);
-                        scb = *reinterpret_cast<const uint32_t*>(vs + tb * 32 + g * 4);
-                        scc = *reinterpret_cast<const uint32_t*>(vs + tc * 32 + g * 4);
-                        scd = *reinterpret_cast<const uint32_t*>(vs + td * 32 + g * 4);
+                        sca = lds32(st + vs_off);
+                        scb = lds32(st + vs_off + 32u);
+                        scc = lds32(st + vs_off + 256u);
+                        scd = lds32(st + vs_off + 288u);
                     } else {
-                        const uint2 xa = *reinterpret_cast<const uint2*>(vc + ta * 64 + g * 8);
-                        const uint2 xb = *reinterpret_cast<const uint2*>(vc + tb * 64 + g * 8);
-                        const uint2 xc = *reinterpret_cast<const uint2*>(vc + tc * 64 + g * 8);
-                        const uint2 xd = *reinterpret_cast<const uint2*>(vc + td * 64 + g * 8);
+                        const uint2 xa = lds64(st + v_off_a);
+                        const uint2 xb = lds64(st + v_off_b);
+                        const uint2 xc = lds64(st + v_off_a + 512u);
+                        const uint2 xd = lds64(st + v_off_b + 512u);
                         va[0] = xa.x; va[1] = xa.y;
                         vb[0] = xb.x; vb[1] = xb.y;
                         vcw[0] = xc.x; vcw[1] = xc.y;
                         vd[0] = xd.x; vd[1] = xd.y;
-                        sca = *reinterpret_cast<const uint16_t*>(vs + ta * 16 + g * 2);
-                        scb = *reinterpret_cast<const uint16_t*>(vs + tb * 16 + g * 2);
-                        scc = *reinterpret_cast<const uint16_t*>(vs + tc * 16 + g * 2);
-                        scd = *reinterpret_cast<const uint16_t*>(vs + td * 16 + g * 2);
+                        sca = lds16(st + vs_off);
+                        scb = lds16(st + vs_off + 16u);
+                        scc = lds16(st + vs_off + 128u);
+                        scd = lds16(st + vs_off + 144u);
                     }
                     if (nvalid < kTileTok) {
                         // rows past the end of the sequence hold other data (or nothing): their scales may be
                         // anything, and 0 * NaN would poison the accumulator even though P is exactly 0 there
-                        sca = ta < nvalid ? sca : 0u;
-                        scb = tb < nvalid ? scb : 0u;
-                        scc = tc < nvalid ? scc : 0u;
-                        scd = td < nvalid ? scd : 0u;
+                        sca = 2 * t < nvalid ? sca : 0u;
+                        scb = 2 * t + 1 < nvalid ? scb : 0u;
+                        scc = 2 * t + 8 < nvalid ? scc : 0u;
+                        scd = 2 * t + 9 < nvalid ? scd : 0u;
                     }
 #pragma unroll
                     for (int q = 0; q < T::kVRegs; ++q) {
@@ -550,7 +606,7 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
                     c_stage = 0;
                     c_phase ^= 1u;
                 }
-                if (gi < hi) {
+                if (to_issue > 0) {
                     issue_one();
                 }
             }
@@ -565,7 +621,7 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
             // a range holds at most two partial pieces: its first piece (slot 0) and, if a different one, its
             // last piece (slot 1)
             const int64_t slot =
-                (static_cast<int64_t>(r) * a.head_lanes + cls) * 2 + ((t_first > 0 || gc == lo) ? 0 : 1);
+                (static_cast<int64_t>(r) * head_lanes + cls) * 2 + ((t_first > 0 || first_piece) ? 0 : 1);
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 const int h8 = 2 * t + hh;
@@ -599,7 +655,8 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
                     }
                 }
             }
-            gc += t_end - t_first;
+            to_consume -= t_end - t_first;
+            first_piece = false;
             advance(cc, t_end - t_first);
         }
     }
@@ -721,12 +778,43 @@ int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* pla
     return PPLB200_SUCCESS;
 }
 
+static int map_order_kind(const CacheMapOrder& od) {
+    if (od.pos_head == 1 && od.pos_kv == 2 && od.pos_layer == 3 && od.pos_row == 4) {
+        return kOrderRowLast;
+    }
+    if (od.pos_row == 1 && od.pos_head == 2 && od.pos_kv == 3 && od.pos_layer == 4) {
+        return kOrderRowFirst;
+    }
+    return kOrderGeneric;
+}
+
+template <int DH, int ORDER>
+static int launch_main(const CUtensorMap& tm_codes, const CUtensorMap& tm_scales, const DecodeArgs& a, int64_t grid,
+                       cudaStream_t stream) {
+    using T = Traits<DH>;
+    static bool attr_set = false;  // per template instance; setting it twice is harmless
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(decode_splitk_kernel<DH, ORDER>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+        if (e != cudaSuccess) {
+            fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(decode_splitk_kernel): %s\n", cudaGetErrorString(e));
+            return PPLB200_DEVICE_RUNTIME_ERROR;
+        }
+        attr_set = true;
+    }
+    {
+        KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
+        decode_splitk_kernel<DH, ORDER><<<static_cast<unsigned>(grid), kThreads, T::kSmemBytes, stream>>>(tm_codes,
+                                                                                                         tm_scales, a);
+    }
+    return check_launch("decode_splitk_kernel");
+}
+
 template <int DH>
 static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan,
                             const void* query, const int64_t* seqstarts, const int64_t* cachestarts,
                             const int64_t* start_pos, const void* cache, const void* scale, void* workspace,
                             void* attn_output, cudaStream_t stream) {
-    using T = Traits<DH>;
     static_assert(sizeof(PlanHeader) <= 256, "the header must fit in front of the prefix sums");
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     PlanHeader* hdr = reinterpret_cast<PlanHeader*>(ws + plan.off_header);
@@ -770,28 +858,17 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.order = order;
     a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
 
-    static bool attr_set = false;  // per template instance; setting it twice is harmless
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(decode_splitk_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             T::kSmemBytes);
-        if (e != cudaSuccess) {
-            fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(decode_splitk_kernel): %s\n", cudaGetErrorString(e));
-            return PPLB200_DEVICE_RUNTIME_ERROR;
-        }
-        attr_set = true;
-    }
     // never more CTAs than there can be ranges
     int64_t grid = plan.grid;
     const int64_t per_cta = kWarps / plan.head_lanes;
     if ((plan.max_ranges + per_cta - 1) / per_cta < grid) {
         grid = (plan.max_ranges + per_cta - 1) / per_cta;
     }
-    {
-        KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
-        decode_splitk_kernel<DH><<<static_cast<unsigned>(grid), kThreads, T::kSmemBytes, stream>>>(tm_codes, tm_scales,
-                                                                                                  a);
+    switch (map_order_kind(order)) {
+        case kOrderRowLast: rc = launch_main<DH, kOrderRowLast>(tm_codes, tm_scales, a, grid, stream); break;
+        case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst>(tm_codes, tm_scales, a, grid, stream); break;
+        default: rc = launch_main<DH, kOrderGeneric>(tm_codes, tm_scales, a, grid, stream); break;
     }
-    rc = check_launch("decode_splitk_kernel");
     if (rc != PPLB200_SUCCESS) {
         return rc;
     }
