@@ -75,7 +75,7 @@ class ClockSampler:
     }
 
     def __init__(self, device_index: int, period_s: float = 0.005):
-        self.samples, self.reasons = [], set()
+        self.samples, self.reasons, self.power_w, self.mem_mhz = [], set(), [], []
         self.max_mhz = None
         self._stop = threading.Event()
         self._thread = None
@@ -110,6 +110,8 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                self.mem_mhz.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_MEM)))
+                self.power_w.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
                 mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
                 for bit, name in self.REASONS.items():
                     if mask & bit and name != "gpu_idle":
@@ -133,7 +135,10 @@ class ClockSampler:
         if self._h is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "error": getattr(self, "error", "no NVML")}
         return {"sm_mhz": int(statistics.median(self.samples)) if self.samples else None,
-                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+                "sm_min_mhz": min(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples),
+                "mem_mhz": int(statistics.median(self.mem_mhz)) if self.mem_mhz else None,
+                "power_w_max": round(max(self.power_w), 1) if self.power_w else None}
 
 
 # ------------------------------------------------------------------------------------------------

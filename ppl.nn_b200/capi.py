@@ -9,8 +9,11 @@ from __future__ import annotations
 import ctypes
 from pathlib import Path
 
+import os
+
 HERE = Path(__file__).resolve().parent
-LIB_PATH = HERE / "lib" / "libppl_nn_b200.so"
+# PPLB200_LIBRARY selects another build of the same library (kernel tuning experiments)
+LIB_PATH = Path(os.environ["PPLB200_LIBRARY"]) if os.environ.get("PPLB200_LIBRARY") else HERE / "lib" / "libppl_nn_b200.so"
 
 SUCCESS = 0
 INVALID_VALUE = 1

@@ -60,15 +60,42 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-// Bounded wait.  Returns false when the poll budget ran out (the caller records a status code
-// and carries on with whatever is in shared memory; nothing hangs).
+// try_wait with a suspend-time hint: the hardware may park the thread for up to `hint_ns` and wakes
+// it as soon as the phase completes, so a waiting warp does not burn issue slots by polling.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar_addr, uint32_t parity, uint32_t hint_ns) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(bar_addr), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return done != 0;
+}
+
+#ifndef PPLB200_WAIT_HINT_NS
+#define PPLB200_WAIT_HINT_NS 20000
+#endif
+
+// Bounded wait.  Returns false when the time budget (about a second of SM clocks) ran out; the
+// caller records a status code and carries on with whatever is in shared memory; nothing hangs.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kMaxWaitPolls; ++i) {
-        if (mbar_try_wait(bar, parity)) {
+    const uint32_t addr = smem_u32(bar);
+    if (mbar_try_wait_hint(addr, parity, PPLB200_WAIT_HINT_NS)) {
+        return true;
+    }
+    const long long t0 = clock64();
+    for (;;) {
+        if (mbar_try_wait_hint(addr, parity, PPLB200_WAIT_HINT_NS)) {
             return true;
         }
+        if (clock64() - t0 > 2000000000LL) {
+            return false;
+        }
     }
-    return false;
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -16,9 +16,11 @@
 //     the same range of different classes, i.e. adjacent heads of the same token rows, so that in the
 //     token-major cache layout the CTA streams 4 x 128 contiguous bytes per row (with fewer classes
 //     the remaining warps take the next range of the same class).
-//   * Every warp is an independent worker with its own TMA pipeline: one lane issues four bulk-tensor
-//     copies per tile (K codes, V codes, K scales, V scales; 5 KB at head_dim 128) that complete on
-//     an mbarrier; the pipeline runs across segment boundaries without draining.  The only
+//   * Every warp is an independent worker with its own 2-stage pipeline.  Per tile (5 KB at head_dim
+//     128) one lane issues two bulk-tensor (TMA) copies, K codes and V codes, and all lanes together
+//     copy the two small scale tiles with one 16-byte cp.async each (a TMA copy costs the warp tens
+//     of issue slots whatever its size, which is too much for a 512-byte tile); everything completes
+//     on one mbarrier; the pipeline runs across segment boundaries without draining.  The only
 //     block-level synchronisation is the hand-out of the next range.
 //   * Per tile the warp computes S^T[16 tokens x 8 heads] = K[16 x Dh] * Q^T with mma.m16n8k16
 //     (tokens are the M dimension, the up-to-8 query heads of the group the N dimension),
@@ -42,11 +44,28 @@ namespace pplb200 {
 
 namespace {
 
+// Tuning knobs (compile-time).  Measured on B200 with the LLaMA-2-7B decode workload: throughput in the
+// token-major cache layout grows with the number of resident warps (each warp's row sequence is served
+// by few DRAM banks at a time), not with the depth of its pipeline, so 16 warps x 2 stages beat
+// 12 x 3 and 8 x 4 at equal bytes in flight; 126 registers per thread is what 16 warps allow.
+#ifndef PPLB200_DECODE_WARPS
+#define PPLB200_DECODE_WARPS 4
+#endif
+#ifndef PPLB200_DECODE_STAGES
+#define PPLB200_DECODE_STAGES 2
+#endif
+#ifndef PPLB200_DECODE_CTAS
+#define PPLB200_DECODE_CTAS 4
+#endif
+#ifndef PPLB200_DECODE_LOCKSTEP
+#define PPLB200_DECODE_LOCKSTEP 0
+#endif
+
 constexpr int kTileTok = 16;
-constexpr int kStages = 3;
-constexpr int kWarps = 4;
+constexpr int kStages = PPLB200_DECODE_STAGES;
+constexpr int kWarps = PPLB200_DECODE_WARPS;
 constexpr int kThreads = kWarps * 32;
-constexpr int kCtasPerSm = 3;
+constexpr int kCtasPerSm = PPLB200_DECODE_CTAS;
 constexpr int kMinRangeTiles = 8;  // never cut the work finer than 128 tokens per range
 constexpr float kNegBig = -1.0e30f;
 constexpr float kRescaleSlack = 8.0f;  // the reference maximum may lag by up to 2^8 before a rescale
@@ -94,6 +113,8 @@ struct DecodeArgs {
     int32_t class_heads;  // virtual heads per class: num_vheads / head_lanes
     int32_t layer_idx;
     CacheMapOrder order;
+    const __half* scale;  // the scale tensor (copied with cp.async, addressed with the cache strides / 8)
+    int64_t max_tokens;
     float scale_log2;
 };
 
@@ -125,6 +146,20 @@ __device__ __forceinline__ void tma_load_cache_tile(uint32_t dst, const CUtensor
         "cp.async.bulk.tensor.5d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
         : "memory");
+}
+
+// 16- or 8-byte asynchronous copy global -> shared; `src_bytes` < BYTES zero-fills the rest.
+template <int BYTES>
+__device__ __forceinline__ void cp_async(uint32_t dst, const void* src, uint32_t src_bytes) {
+    if constexpr (BYTES == 16) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+    } else {
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+    }
+}
+// The executing thread's earlier cp.async copies arrive on the mbarrier when they have landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -257,8 +292,7 @@ struct Cursor {
 
 template <int DH, int ORDER>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
-decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __grid_constant__ CUtensorMap tmap_scales,
-                     const DecodeArgs a) {
+decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const DecodeArgs a) {
     using T = Traits<DH>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[kWarps * kStages];
@@ -271,11 +305,10 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < kWarps * kStages; ++i) {
-            mbar_init(&full_bar[i], 1);
+            mbar_init(&full_bar[i], 33);  // lane 0's expect_tx arrival + one cp.async arrival per lane
         }
         mbar_fence_init();
         tma_prefetch_desc(&tmap_codes);
-        tma_prefetch_desc(&tmap_scales);
     }
     __syncthreads();
 
@@ -299,6 +332,15 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
         v_off_b = v_off_a + 64;
         vs_off = 2 * T::kCodeBytes + T::kScaleBytes + (2 * t) * 16 + g * 2;
     }
+
+    // scale tiles: lane l copies bytes [l * DH/8, (l + 1) * DH/8) of the tile, i.e. half a scale row
+    constexpr int kScaleCopy = DH / 8;  // 16 or 8 bytes per lane
+    const int64_t scale_row_bytes = a.geom.stride_s / 4;  // cache stride / 8 elements * 2 bytes
+    const int64_t scale_lane_off = (lane >> 1) * scale_row_bytes + (lane & 1) * kScaleCopy;
+    const int64_t scale_kv_bytes = a.geom.stride_kv / 4;
+    const uint32_t scale_dst_off = 2 * T::kCodeBytes + lane * kScaleCopy;
+    const char* scale_layer = reinterpret_cast<const char*>(a.scale) + a.layer_idx * (a.geom.stride_l / 4);
+    const int64_t scale_head_bytes = a.geom.stride_h / 4;
 
     uint32_t c_stage = 0, c_phase = 0;  // consume position in the stage ring
     uint32_t i_stage = 0;               // issue position in the stage ring
@@ -387,19 +429,26 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
         int32_t to_consume = to_issue;
 
         auto issue_one = [&]() {
+            const int tok = ic.tile * kTileTok;
+            const int row = paged ? static_cast<int>(cache_row(a.geom, a.cachestarts, ic.b, tok)) : ic.row_base + tok;
+            const uint32_t st = wsm + i_stage * T::kStageBytes;
+            const uint32_t bar = wbar + i_stage * 8;
+            {
+                // scales: every lane copies its half row of the K tile and of the V tile
+                const char* src = scale_layer + row * scale_row_bytes + ic.kvh * scale_head_bytes + scale_lane_off;
+                const uint32_t nbytes = (row + (lane >> 1)) < a.max_tokens ? kScaleCopy : 0;  // rows past the cache: zeros
+                cp_async<kScaleCopy>(st + scale_dst_off, src, nbytes);
+                cp_async<kScaleCopy>(st + scale_dst_off + T::kScaleBytes, src + scale_kv_bytes, nbytes);
+                cp_async_arrive(bar);
+            }
             if (lane == 0) {
-                const int tok = ic.tile * kTileTok;
-                const int row = paged ? static_cast<int>(cache_row(a.geom, a.cachestarts, ic.b, tok)) : ic.row_base + tok;
-                const uint32_t st = wsm + i_stage * T::kStageBytes;
-                const uint32_t bar = wbar + i_stage * 8;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(T::kStageBytes)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                             "r"(2 * T::kCodeBytes)
                              : "memory");
                 tma_load_cache_tile<ORDER>(st, &tmap_codes, bar, a.order, row, ic.kvh, 0, layer);
                 tma_load_cache_tile<ORDER>(st + T::kCodeBytes, &tmap_codes, bar, a.order, row, ic.kvh, 1, layer);
-                tma_load_cache_tile<ORDER>(st + 2 * T::kCodeBytes, &tmap_scales, bar, a.order, row, ic.kvh, 0, layer);
-                tma_load_cache_tile<ORDER>(st + 2 * T::kCodeBytes + T::kScaleBytes, &tmap_scales, bar, a.order, row,
-                                           ic.kvh, 1, layer);
             }
+            __syncwarp();
             i_stage = (i_stage + 1 == kStages) ? 0 : i_stage + 1;
             advance(ic, 1);
             --to_issue;
@@ -542,11 +591,16 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
                 }
                 const float p0 = ex2_approx(s0 - m0), p1 = ex2_approx(s1 - m1);
                 const float p2 = ex2_approx(s2 - m0), p3 = ex2_approx(s3 - m1);
-                l0 += p0 + p2;
-                l1 += p1 + p3;
+                // The MMA consumes P rounded to fp16, so the normaliser sums the SAME rounded values: a
+                // rounding of p then cancels between numerator and denominator (exactly so when one token
+                // dominates), which keeps the output within one fp16 ulp of an fp32 evaluation.
+                const __half2 ph01 = __floats2half2_rn(p0, p1), ph23 = __floats2half2_rn(p2, p3);
+                const float2 pf01 = __half22float2(ph01), pf23 = __half22float2(ph23);
+                l0 += pf01.x + pf23.x;
+                l1 += pf01.y + pf23.y;
                 // P^T as the B operand of the second MMA: k = token, n = head
-                const uint32_t pb0 = movmatrix_trans(h2_as_u32(__floats2half2_rn(p0, p1)));
-                const uint32_t pb1 = movmatrix_trans(h2_as_u32(__floats2half2_rn(p2, p3)));
+                const uint32_t pb0 = movmatrix_trans(h2_as_u32(ph01));
+                const uint32_t pb1 = movmatrix_trans(h2_as_u32(ph23));
 
                 // ---------------- O^T += V^T * P^T ----------------
                 {
@@ -601,6 +655,9 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const __gri
                     }
                 }
 
+#if PPLB200_DECODE_LOCKSTEP
+                __syncthreads();
+#endif
                 __syncwarp();  // every lane has read this stage: it may be refilled
                 if (++c_stage == kStages) {
                     c_stage = 0;
@@ -750,7 +807,13 @@ int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* pla
     const int group = p.num_heads / p.num_kv_heads;
     d.octets = (group + 7) / 8;
     d.num_vheads = static_cast<int64_t>(p.num_kv_heads) * d.octets;
-    d.head_lanes = (d.num_vheads % 4 == 0) ? 4 : ((d.num_vheads % 2 == 0) ? 2 : 1);
+    d.head_lanes = 1;
+    for (int hl = kWarps; hl > 1; hl >>= 1) {  // the largest power of two <= kWarps that divides the head count
+        if (d.num_vheads % hl == 0) {
+            d.head_lanes = hl;
+            break;
+        }
+    }
     d.class_heads = d.num_vheads / d.head_lanes;
     d.grid = static_cast<int64_t>(sm_count) * kCtasPerSm;
     d.workers = d.grid * (kWarps / d.head_lanes);  // resident warps per head class
@@ -789,8 +852,7 @@ static int map_order_kind(const CacheMapOrder& od) {
 }
 
 template <int DH, int ORDER>
-static int launch_main(const CUtensorMap& tm_codes, const CUtensorMap& tm_scales, const DecodeArgs& a, int64_t grid,
-                       cudaStream_t stream) {
+static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t grid, cudaStream_t stream) {
     using T = Traits<DH>;
     static bool attr_set = false;  // per template instance; setting it twice is harmless
     if (!attr_set) {
@@ -804,8 +866,7 @@ static int launch_main(const CUtensorMap& tm_codes, const CUtensorMap& tm_scales
     }
     {
         KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
-        decode_splitk_kernel<DH, ORDER><<<static_cast<unsigned>(grid), kThreads, T::kSmemBytes, stream>>>(tm_codes,
-                                                                                                         tm_scales, a);
+        decode_splitk_kernel<DH, ORDER><<<static_cast<unsigned>(grid), kThreads, T::kSmemBytes, stream>>>(tm_codes, a);
     }
     return check_launch("decode_splitk_kernel");
 }
@@ -820,9 +881,9 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     PlanHeader* hdr = reinterpret_cast<PlanHeader*>(ws + plan.off_header);
     int32_t* tile_prefix = reinterpret_cast<int32_t*>(ws + plan.off_tile_prefix);
 
-    CUtensorMap tm_codes, tm_scales;
+    CUtensorMap tm_codes;
     CacheMapOrder order;
-    int rc = make_cache_tensor_maps(p, cache, scale, kTileTok, &tm_codes, &tm_scales, &order);
+    int rc = make_cache_tensor_map(p, cache, kTileTok, &tm_codes, &order);
     if (rc != PPLB200_SUCCESS) {
         return rc;
     }
@@ -856,6 +917,8 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.class_heads = static_cast<int32_t>(plan.class_heads);
     a.layer_idx = p.layer_idx;
     a.order = order;
+    a.scale = static_cast<const __half*>(scale);
+    a.max_tokens = p.max_tokens;
     a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
 
     // never more CTAs than there can be ranges
@@ -865,9 +928,9 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
         grid = (plan.max_ranges + per_cta - 1) / per_cta;
     }
     switch (map_order_kind(order)) {
-        case kOrderRowLast: rc = launch_main<DH, kOrderRowLast>(tm_codes, tm_scales, a, grid, stream); break;
-        case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst>(tm_codes, tm_scales, a, grid, stream); break;
-        default: rc = launch_main<DH, kOrderGeneric>(tm_codes, tm_scales, a, grid, stream); break;
+        case kOrderRowLast: rc = launch_main<DH, kOrderRowLast>(tm_codes, a, grid, stream); break;
+        case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst>(tm_codes, a, grid, stream); break;
+        default: rc = launch_main<DH, kOrderGeneric>(tm_codes, a, grid, stream); break;
     }
     if (rc != PPLB200_SUCCESS) {
         return rc;

@@ -419,8 +419,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     float p1 = ex2_approx(__uint_as_float(v[e + 1]) * a.scale_log2 - m_ref);
                     p0 = (c * 32 + e <= limit) ? p0 : 0.0f;
                     p1 = (c * 32 + e + 1 <= limit) ? p1 : 0.0f;
-                    l_sum += p0 + p1;
-                    packed[e >> 1] = h2_as_u32(__floats2half2_rn(p0, p1));
+                    // the normaliser sums the fp16-rounded values the MMA will consume, so that the
+                    // rounding of P cancels between numerator and denominator
+                    const __half2 ph = __floats2half2_rn(p0, p1);
+                    const float2 pf = __half22float2(ph);
+                    l_sum += pf.x + pf.y;
+                    packed[e >> 1] = h2_as_u32(ph);
                 }
                 // columns 32c .. 32c+31 = 16-byte chunks 4c .. 4c+3 of the row; column block (4c)/8
                 uint8_t* prow = sP + (c >> 1) * T::kBlockBytes + r * 128;

@@ -6,6 +6,10 @@
 
 #include <mutex>
 
+#ifndef PPLB200_L2_PROMO
+#define PPLB200_L2_PROMO CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+#endif
+
 namespace pplb200 {
 
 namespace {
@@ -48,7 +52,7 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank
         }
     }
     CUresult r = fn(map, dtype, rank, const_cast<void*>(base), gdims, gstrides, gbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    swizzle, PPLB200_L2_PROMO, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         fprintf(stderr, "[ppl_nn_b200] cuTensorMapEncodeTiled failed: CUresult %d (rank %u, dims", static_cast<int>(r), rank);
         for (uint32_t i = 0; i < rank; ++i) {
@@ -60,8 +64,8 @@ int encode_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, uint32_t rank
     return PPLB200_SUCCESS;
 }
 
-int make_cache_tensor_maps(const pplb200_attn_params& p, const void* cache, const void* scale, int tile_tokens,
-                           CUtensorMap* codes, CUtensorMap* scales, CacheMapOrder* order) {
+int make_cache_tensor_map(const pplb200_attn_params& p, const void* cache, int tile_tokens, CUtensorMap* codes,
+                          CacheMapOrder* order) {
     // logical outer dimensions: 0 row, 1 kv head, 2 k|v, 3 layer
     const uint64_t extent[4] = {static_cast<uint64_t>(p.max_tokens), static_cast<uint64_t>(p.num_kv_heads), 2,
                                 static_cast<uint64_t>(p.num_layer)};
@@ -85,26 +89,18 @@ int make_cache_tensor_maps(const pplb200_attn_params& p, const void* cache, cons
     order->pos_layer = pos[3];
 
     const uint64_t dh = static_cast<uint64_t>(p.head_dim);
-    uint64_t dims_c[5], dims_s[5], str_c[4], str_s[4];
-    uint32_t box_c[5], box_s[5];
+    uint64_t dims_c[5], str_c[4];
+    uint32_t box_c[5];
     dims_c[0] = dh;
-    dims_s[0] = dh / 8;
     box_c[0] = static_cast<uint32_t>(dh);
-    box_s[0] = static_cast<uint32_t>(dh / 8);
     for (int i = 0; i < 4; ++i) {
         const int d = idx[i];
-        dims_c[i + 1] = dims_s[i + 1] = extent[d];
-        str_c[i] = stride[d];          // int8: elements == bytes
-        str_s[i] = stride[d] / 8 * 2;  // fp16 scale tensor: cache strides / 8 elements
-        box_c[i + 1] = box_s[i + 1] = (d == 0) ? static_cast<uint32_t>(tile_tokens) : 1u;
+        dims_c[i + 1] = extent[d];
+        str_c[i] = stride[d];  // int8: elements == bytes
+        box_c[i + 1] = (d == 0) ? static_cast<uint32_t>(tile_tokens) : 1u;
     }
-    int rc = encode_tensor_map(codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, cache, dims_c, str_c, box_c,
-                               p.head_dim == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
-    if (rc != PPLB200_SUCCESS) {
-        return rc;
-    }
-    return encode_tensor_map(scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, scale, dims_s, str_s, box_s,
-                             CU_TENSOR_MAP_SWIZZLE_NONE);
+    return encode_tensor_map(codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, cache, dims_c, str_c, box_c,
+                             p.head_dim == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 }  // namespace pplb200

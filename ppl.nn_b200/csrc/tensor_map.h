@@ -21,12 +21,11 @@ struct CacheMapOrder {
     int32_t pos_row, pos_head, pos_kv, pos_layer;
 };
 
-// Five-dimensional maps over `cache` (uint8 view, innermost extent head_dim) and `scale` (fp16,
-// innermost extent head_dim/8) whose outer dimensions are (row, kv head, k|v, layer) with the
-// strides of the params, sorted by stride.  The box is one head's rows of `tile_tokens` consecutive
-// cache rows.  Code rows of 128 bytes use the 128-byte swizzle so that the kernels' 16-byte
-// shared-memory reads are bank-conflict free.
-int make_cache_tensor_maps(const pplb200_attn_params& p, const void* cache, const void* scale, int tile_tokens,
-                           CUtensorMap* codes, CUtensorMap* scales, CacheMapOrder* order);
+// Five-dimensional map over `cache` (uint8 view, innermost extent head_dim) whose outer dimensions
+// are (row, kv head, k|v, layer) with the strides of the params, sorted by stride.  The box is one
+// head's rows of `tile_tokens` consecutive cache rows.  Code rows of 128 bytes use the 128-byte swizzle
+// so that the kernels' 16-byte shared-memory reads are bank-conflict free.
+int make_cache_tensor_map(const pplb200_attn_params& p, const void* cache, int tile_tokens, CUtensorMap* codes,
+                          CacheMapOrder* order);
 
 }  // namespace pplb200
