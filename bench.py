@@ -51,8 +51,8 @@ FALLBACK_HBM_GBS = 6650.0
 
 # DRAM bytes moved by decode_splitk_kernel per algorithmic byte, from the ncu capture summarised in
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured
-# launch).  None until a capture exists.
-DECODE_TRAFFIC_PER_ALGO_BYTE = None
+# launch): 692.57 MB + 3.97 MB for 690.86 MB (profiles/decode_splitk_kernel_cfg2_eighth.md).
+DECODE_TRAFFIC_PER_ALGO_BYTE = 1.0082
 
 
 def measured_peak_gbs():
@@ -63,6 +63,16 @@ def measured_peak_gbs():
         except Exception:
             pass
     return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def measured_peak_tflops():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, cuBLAS burst)"
+        except Exception:
+            pass
+    return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
 
 
 # ------------------------------------------------------------------------------------------------
@@ -288,6 +298,7 @@ def main():
     # the launching stream), so the dominant kernel's duration comes from the very same launches
     lib.profile_read(capi.KERNEL_DECODE)
     lib.profile_read(capi.KERNEL_APPEND)
+    lib.profile_read(capi.KERNEL_PREFILL)
     lib.profile_enable(True)
     with ClockSampler(local_rank) as clocks:
         barrier()
@@ -304,27 +315,41 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_total = float(t.item())
     ms_step = ms_total / args.steps
-    tokens_per_step = nd  # one new token per decode sequence, complete once all head shards are done
+    tokens_per_step = idx.total_tokens  # new tokens of the step: one per decode sequence plus every prefill token
     value = tokens_per_step / (ms_step * 1e-3)
 
     dec_ms, dec_n = lib.profile_read(capi.KERNEL_DECODE)
     app_ms, app_n = lib.profile_read(capi.KERNEL_APPEND)
-    kern_ms = dec_ms / max(dec_n, 1)
-    algo_bytes = workloads.decode_bytes(dc.num_kv_heads, spec.head_dim, idx.kvlens[:nd], dc.num_heads)
+    pre_ms, pre_n = lib.profile_read(capi.KERNEL_PREFILL)
+    times = {"decode": dec_ms / max(dec_n, 1), "append": app_ms / max(app_n, 1), "prefill": pre_ms / max(pre_n, 1)}
     if world > 1:
-        t = torch.tensor([kern_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([times["decode"], times["append"], times["prefill"]], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        kern_ms = float(t.item())
+        times = dict(zip(("decode", "append", "prefill"), (float(v) for v in t.tolist())))
+    algo_bytes = workloads.decode_bytes(dc.num_kv_heads, spec.head_dim, idx.kvlens[:nd], dc.num_heads) if nd else 0
+    algo_flops = workloads.prefill_flops(dc.num_heads, spec.head_dim, idx.seqlens[nd:])
     peak, peak_src = measured_peak_gbs()
-    achieved = algo_bytes / (kern_ms * 1e-3) / 1e9
-    roofline = {
-        "bound": "hbm", "kernel": "decode_splitk_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-        "frac": achieved / peak, "peak_source": peak_src, "frac_of_nominal_8TBs": achieved / 8000.0,
-        "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": kern_ms, "launches_timed": dec_n,
-        "per_gpu": True,
-        "traffic": (DECODE_TRAFFIC_PER_ALGO_BYTE * algo_bytes) if DECODE_TRAFFIC_PER_ALGO_BYTE else None,
-        "append_kernel_ms": app_ms / max(app_n, 1),
-    }
+    tpeak, tpeak_src = measured_peak_tflops()
+    kernels = {}
+    if dec_n:
+        ach = algo_bytes / (times["decode"] * 1e-3) / 1e9
+        kernels["decode_splitk_kernel"] = {
+            "bound": "hbm", "kernel": "decode_splitk_kernel", "achieved": ach, "peak": peak, "unit": "GB/s",
+            "frac": ach / peak, "peak_source": peak_src, "frac_of_nominal_8TBs": ach / 8000.0,
+            "algorithmic_bytes_per_launch": algo_bytes, "kernel_ms": times["decode"], "launches_timed": dec_n,
+            "per_gpu": True,
+            "traffic": (DECODE_TRAFFIC_PER_ALGO_BYTE * algo_bytes) if DECODE_TRAFFIC_PER_ALGO_BYTE else None}
+    if pre_n:
+        ach = algo_flops / (times["prefill"] * 1e-3) / 1e12
+        kernels["prefill_tcgen05_kernel"] = {
+            "bound": "tensor", "kernel": "prefill_tcgen05_kernel", "achieved": ach, "peak": tpeak, "unit": "TFLOP/s",
+            "frac": ach / tpeak, "peak_source": tpeak_src, "algorithmic_flops_per_launch": algo_flops,
+            "kernel_ms": times["prefill"], "launches_timed": pre_n, "per_gpu": True, "traffic": None}
+    dominant = max(kernels.values(), key=lambda k: k["kernel_ms"]) if kernels else None
+    roofline = dict(dominant) if dominant else None
+    if roofline is not None:
+        roofline["append_kernel_ms"] = times["append"]
+        roofline["other_kernels"] = [k for k in kernels.values() if k is not dominant]
 
     # ---- end to end: host buffers in, host buffer out, every step -------------------------------
     e2e = None
@@ -391,7 +416,7 @@ def main():
 
     # ---- CPU baseline on a bounded sample (rank 0, single-GPU run only) -------------------------
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and nd == idx.batch:
         entry.load_oracle().build()
         base_spec = workloads.SPECS[args.workload]
         tok_s, cores, per_step, steps, sample = cpu_time_sample(base_spec, min(base_spec.n_decode, args.cpu_seqs))
@@ -405,10 +430,14 @@ def main():
             "vs_baseline": None, "dtype": "fp16 in/out, int8 cache, fp32 accumulate", "data": "synthetic",
             "config": {"workload": spec.name, "num_heads": spec.num_heads, "num_kv_heads": spec.num_kv_heads,
                        "head_dim": spec.head_dim, "decode_sequences": nd, "kv_tokens": int(idx.kvlens[:nd].sum()),
+                       "prefill_sequences": idx.batch - nd, "prefill_tokens": int(idx.seqlens[nd:].sum()),
                        "cache_layout": args.layout, "sharding": f"kv-heads/{world}",
                        "l2": "no flush: the per-GPU cache working set is far larger than the 126 MB L2"
-                             if algo_bytes > 4 * 126e6 else "working set is NOT much larger than L2"},
+                             if algo_bytes > 4 * 126e6 else
+                             "no flush: the step is compute-bound prefill" if nd == 0 else
+                             "working set is NOT much larger than L2"},
             "hbm_gbs_per_gpu_whole_step": algo_bytes / (ms_step * 1e-3) / 1e9,
+            "tokens_per_step": int(tokens_per_step),
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(), "e2e": e2e,
             "gpu_launches": int(launches), "output_abs_mean": checksum, "device_status": int(status),
         }

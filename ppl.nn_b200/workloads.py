@@ -48,6 +48,8 @@ SPECS = {
     # LLaMA-3-8B attention layer, mixed continuous-batching step
     "cfg3_llama8b_mixed": Spec("cfg3_llama8b_mixed", 32, 8, 128, 248, 256, 8192, n_prefill=8, pf_lo=512, pf_hi=2048,
                                seed=2),
+    # the prefill half of the mixed step alone (for the tensor-core roofline of the prefill kernel)
+    "cfg3_prefill_only": Spec("cfg3_prefill_only", 32, 8, 128, 0, 1, 1, n_prefill=8, pf_lo=512, pf_hi=2048, seed=2),
     # LLaMA-2-70B attention layer, large-batch decode
     "cfg4_llama70b_decode": Spec("cfg4_llama70b_decode", 64, 8, 128, 512, 64, 8192, "loguniform", seed=3),
     # Long-context split-k stress
@@ -206,6 +208,13 @@ def cache_shapes(layout: int, max_tokens: int, num_layer: int, num_kv_heads: int
     if layout == 3:
         return (num_layer, 2, num_kv_heads, max_tokens, head_dim), (num_layer, 2, num_kv_heads, max_tokens, g)
     raise ValueError("cache_layout must be 0 or 3")
+
+
+def prefill_flops(num_heads: int, head_dim: int, seqlens: np.ndarray) -> float:
+    """Algorithmic flops of causal prefill without history: QK^T and PV over the lower triangle
+    (diagonal included), 2 * S * (S + 1) * Dh * Hq per sequence of length S."""
+    s = np.asarray(seqlens, dtype=np.float64)
+    return float((2.0 * s * (s + 1.0) * head_dim * num_heads).sum())
 
 
 def decode_bytes(spec_heads_kv: int, head_dim: int, kvlens: np.ndarray, num_heads: int) -> int:
