@@ -446,5 +446,33 @@ def main():
         dist.destroy_process_group()
 
 
+def _run_with_clean_stdout():
+    """Everything but the final JSON line goes to stderr: libraries (NCCL prints its version banner to
+    stdout, for one) must not add lines to the one-line contract."""
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    lines = []
+    real_print = print
+
+    def capture(*a, **kw):
+        if kw.get("file") in (None, sys.stdout):
+            lines.append(" ".join(str(x) for x in a))
+        else:
+            real_print(*a, **kw)
+
+    import builtins
+    builtins.print = capture
+    try:
+        main()
+    finally:
+        builtins.print = real_print
+        sys.stdout.flush()
+        os.dup2(saved, 1)
+        os.close(saved)
+    for ln in lines:
+        real_print(ln, flush=True)
+
+
 if __name__ == "__main__":
-    main()
+    _run_with_clean_stdout()

@@ -290,3 +290,131 @@ def test_cache_prefill_with_history(orc, torch_dev, pkg, layout):
 def test_smoke_entry_point(torch_dev):
     import __graft_entry__ as entry
     entry.smoke()
+
+
+def test_kv_head_shards_concatenate_to_the_unsharded_output(orc, torch_dev, pkg):
+    """The multi-GPU decomposition, rank by rank on one GPU: every rank's call on its kv-head shard
+    (own cache, replicated index tensors), outputs concatenated along the head axis.  With split-k off
+    every (sequence, head) is computed by the same instruction sequence as in the unsharded call, so
+    the result is bit-identical; with the stream-k split the cut points move, so it is compared within
+    the tolerance."""
+    import torch
+    from ppl_nn_b200 import ops, sharding, workloads
+    spec = workloads.scaled(workloads.SPECS["cfg4_llama70b_decode"], seqs=24 / 512, length=0.2)
+    full = workloads.host_case(spec)
+    idx, hidx = full.index, full.hist_index
+    Hq, Hkv, Dh = spec.num_heads, spec.num_kv_heads, spec.head_dim
+    dev = torch_dev
+
+    def run(q, ck, cv, hk, hv, hq, hkv, split_k):
+        cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, hkv, Dh)
+        cache = torch.zeros(cshape, dtype=torch.int8, device=dev)
+        scale = torch.zeros(sshape, dtype=torch.float16, device=dev)
+        kvc = ops.KeyValueCache(ops.KeyValueCacheParam(num_layer=1, layer_idx=0, quant_bit=8))
+        kvc.forward(_t(hk, dev), _t(hv, dev), _t(hidx.seqstarts, dev), _t(hidx.kvstarts, dev),
+                    _t(hidx.cachestarts, dev), _t(hidx.start_pos, dev), hidx.max_seqlen, hidx.max_kvlen, cache, scale,
+                    total_kv=0)
+        op = ops.MultiHeadCacheAttention(
+            ops.MultiHeadCacheAttentionParam(num_heads=hq, num_kv_heads=hkv, head_dim=Dh, num_layer=1, layer_idx=0,
+                                             quant_bit=8), ops.EngineConfig(specify_decoding_attn_split_k=split_k))
+        out = op.forward(_t(q, dev), _t(ck, dev), _t(cv, dev), _t(idx.seqstarts, dev), _t(idx.kvstarts, dev),
+                         _t(idx.cachestarts, dev), _t(idx.start_pos, dev), idx.decoding_batches, idx.max_seqlen,
+                         idx.max_kvlen, cache, scale)
+        assert op.device_status() == 0
+        return out.cpu().numpy()
+
+    for split_k in (0, 1):
+        whole = run(full.query, full.current_key, full.current_value, full.hist_key, full.hist_value, Hq, Hkv, split_k)
+        for world in (2, 8):
+            parts = []
+            for rank in range(world):
+                qs, kvs = sharding.head_shard(Hq, Hkv, rank, world)
+                lq, lk, lv = sharding.shard_call(full.query, full.current_key, full.current_value, Hq, Hkv, rank, world)
+                parts.append(run(lq, lk, lv, np.ascontiguousarray(full.hist_key[:, kvs]),
+                                 np.ascontiguousarray(full.hist_value[:, kvs]), qs.stop - qs.start,
+                                 kvs.stop - kvs.start, split_k))
+            joined = np.concatenate(parts, axis=1)
+            if split_k == 0:
+                np.testing.assert_array_equal(joined.view(np.uint16), whole.view(np.uint16))
+            else:
+                err = np.abs(joined.astype(np.float32) - whole.astype(np.float32))
+                assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
+
+
+def _two_gpu_rank(rank, world, port, result_dir):
+    import os
+    import sys
+    from pathlib import Path
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root))
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    entry.load_package()
+    from ppl_nn_b200 import ops, sharding, workloads
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        spec = workloads.scaled(workloads.SPECS["cfg4_llama70b_decode"], seqs=16 / 512, length=0.1)
+        full = workloads.host_case(spec)  # same seed on every rank: identical full tensors
+        idx, hidx = full.index, full.hist_index
+        Hq, Hkv, Dh = spec.num_heads, spec.num_kv_heads, spec.head_dim
+        qs, kvs = sharding.head_shard(Hq, Hkv, rank, world)
+        lq, lk, lv = sharding.shard_call(full.query, full.current_key, full.current_value, Hq, Hkv, rank, world)
+        hq, hkv = qs.stop - qs.start, kvs.stop - kvs.start
+        cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, hkv, Dh)
+        cache = torch.zeros(cshape, dtype=torch.int8, device=dev)
+        scale = torch.zeros(sshape, dtype=torch.float16, device=dev)
+
+        def t(a):
+            return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+        kvc = ops.KeyValueCache(ops.KeyValueCacheParam(num_layer=1, layer_idx=0, quant_bit=8))
+        kvc.forward(t(full.hist_key[:, kvs]), t(full.hist_value[:, kvs]), t(hidx.seqstarts), t(hidx.kvstarts),
+                    t(hidx.cachestarts), t(hidx.start_pos), hidx.max_seqlen, hidx.max_kvlen, cache, scale, total_kv=0)
+        op = ops.MultiHeadCacheAttention(ops.MultiHeadCacheAttentionParam(num_heads=hq, num_kv_heads=hkv, head_dim=Dh,
+                                                                         num_layer=1, layer_idx=0, quant_bit=8))
+        out = op.forward(t(lq), t(lk), t(lv), t(idx.seqstarts), t(idx.kvstarts), t(idx.cachestarts), t(idx.start_pos),
+                         idx.decoding_batches, idx.max_seqlen, idx.max_kvlen, cache, scale)
+        gathered = sharding.gather_heads(out, world)  # NCCL all-gather, verification only
+        torch.cuda.synchronize(dev)
+        if rank == 0:
+            np.save(os.path.join(result_dir, "gathered.npy"), gathered.cpu().numpy())
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gpus_nccl_gather_matches_the_oracle(orc, torch_dev, pkg, tmp_path):
+    """Real ranks on real GPUs (needs two of them): each rank runs its shard, NCCL gathers the heads,
+    and the gathered tensor is checked against the oracle on the unsharded problem."""
+    import socket
+    import torch
+    import torch.multiprocessing as mp
+    from ppl_nn_b200 import workloads
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs on the node")
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_two_gpu_rank, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    got = np.load(tmp_path / "gathered.npy").astype(np.float32)
+    spec = workloads.scaled(workloads.SPECS["cfg4_llama70b_decode"], seqs=16 / 512, length=0.1)
+    full = workloads.host_case(spec)
+    idx, hidx = full.index, full.hist_index
+    Hq, Hkv, Dh = spec.num_heads, spec.num_kv_heads, spec.head_dim
+    cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, Hkv, Dh)
+    cache = np.zeros(cshape, dtype=np.int8)
+    scale = np.zeros(sshape, dtype=np.float16)
+    kw = dict(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=idx.batch, max_tokens=idx.max_tokens)
+    orc.kv_append(orc.desc(decoding_batches=0, **kw), full.hist_key, full.hist_value, hidx.seqstarts, hidx.cachestarts,
+                  hidx.start_pos, cache, scale)
+    want = orc.mhca(orc.desc(decoding_batches=idx.decoding_batches, **kw), full.query, full.current_key,
+                    full.current_value, idx.seqstarts, idx.cachestarts, idx.start_pos, cache, scale).astype(np.float32)
+    err = np.abs(got - want)
+    assert got.shape == want.shape and err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
