@@ -2,16 +2,20 @@
 // dense contraction on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators, operands
 // staged in shared memory by TMA (no multicast), fp16 inputs, fp32 accumulation.
 //
-// One CTA computes a 128-row query tile of one (sequence, query head):
-//   warp 0      TMA producer: the Q tile once, then K/V tiles of 128 rows through a 2-stage ring
-//   warp 1      allocates TMEM and issues the MMAs (one lane): S = Q K^T into one of two 128-column
-//               TMEM buffers, then O += P V into a third accumulator; completion is reported to
-//               mbarriers with tcgen05.commit
-//   warps 2..5  128 softmax threads, one query row each (TMEM lane = row): read S with tcgen05.ld,
-//               causal mask, running maximum in the exp2 domain (the O accumulator is rescaled in
-//               TMEM only when the maximum grew by more than 2^8), write P as fp16 into shared memory
-//               in the 128-byte-swizzled K-major layout the MMA expects, and finally normalise O and
-//               store fp16 rows.
+// One CTA computes a 128-row query tile of one (sequence, query head); two CTAs share an SM, so that
+// one CTA's MMAs run under the other's softmax:
+//   warp 0      TMA producer: the Q tile once, then K/V tiles of 64 rows through a 2-stage ring
+//   warp 1      allocates TMEM (256 columns) and issues the MMAs (one lane): S = Q K^T into a 64-column
+//               TMEM buffer, then O += P V and, with a constant tile of ones as the B operand, the
+//               row sums L += P 1 into two more accumulators; completion is reported to mbarriers with
+//               tcgen05.commit
+//   warps 2..5  128 softmax threads, one query row each (TMEM lane = row): read S once with tcgen05.ld
+//               (the buffer is handed back to the MMA warp straight away), causal mask on diagonal
+//               tiles only, running maximum in the exp2 domain (the O and L accumulators are rescaled
+//               in TMEM only when the maximum grew by more than 2^8), write P as fp16 into shared
+//               memory in the 128-byte-swizzled K-major layout the MMA expects, and finally divide O
+//               by L and store fp16 rows.  Taking L from the MMA means the normaliser sums exactly the
+//               fp16-rounded P values that the numerator uses, at no cost to the softmax threads.
 // K/V come from this call's fp16 current_key/current_value (the default), or, with
 // enable_cache_prefill, from an fp16 staging copy of the INT8 cache rows (history included) that a
 // dequantising gather writes into the workspace first.
@@ -31,22 +35,28 @@ namespace pplb200 {
 namespace {
 
 constexpr int kBlockM = 128;   // query rows per CTA
-constexpr int kBlockN = 128;   // kv rows per tile
+constexpr int kBlockN = 64;    // kv rows per tile
 constexpr int kThreads = 192;  // 6 warps
 constexpr int kKvStages = 2;
+constexpr int kCtasPerSm = 2;
 constexpr float kNegBig = -1.0e30f;
 constexpr float kRescaleSlack = 8.0f;
 
 template <int DH>
 struct PTraits {
-    static constexpr int kColBlocks = DH / 64;                  // 64-element (128-byte) swizzled column blocks
-    static constexpr int kBlockBytes = 128 * 128;               // one [128 rows][64 halves] block
-    static constexpr int kQBytes = kColBlocks * kBlockBytes;    // Q tile
-    static constexpr int kKVBytes = kColBlocks * kBlockBytes;   // one K (or V) tile
-    static constexpr int kPBytes = 2 * kBlockBytes;             // P tile: 128 x 128 halves
-    static constexpr int kSmemBytes = kQBytes + 2 * kKvStages * kKVBytes + kPBytes + 1024;
-    static constexpr uint32_t kTmemCols = 512;                  // S0 | S1 | O  (power of two >= 256 + DH)
-    static constexpr uint32_t kColS0 = 0, kColS1 = 128, kColO = 256;
+    static constexpr int kColBlocks = DH / 64;                   // 64-element (128-byte) swizzled column blocks
+    static constexpr int kQBlockBytes = kBlockM * 128;           // one [128 rows][64 halves] block of Q
+    static constexpr int kKVBlockBytes = kBlockN * 128;          // one [64 rows][64 halves] block of K or V
+    static constexpr int kQBytes = kColBlocks * kQBlockBytes;
+    static constexpr int kKVBytes = kColBlocks * kKVBlockBytes;  // one K (or V) tile
+    static constexpr int kPBytes = kBlockM * kBlockN * 2;        // P tile: one [128 rows][64 halves] block
+    static constexpr int kOnesBytes = 512;                       // 16 x 16 halves of 1.0 (four 8x8 core matrices)
+    static constexpr int kBarrierBytes = 128;
+    // The same for every head size (the Dh = 128 figure), so that never more than two CTAs share an SM
+    // and the two 256-column TMEM allocations always fit.
+    static constexpr int kSmemBytes = 32768 + 2 * kKvStages * 16384 + 16384 + kOnesBytes + kBarrierBytes;
+    static constexpr uint32_t kTmemCols = 256;                   // S | L | O
+    static constexpr uint32_t kColS = 0, kColL = 64, kColO = 128;
 };
 
 struct PrefillArgs {
@@ -68,10 +78,14 @@ struct Barriers {
     uint64_t k_full[kKvStages];
     uint64_t v_full[kKvStages];
     uint64_t kv_empty[kKvStages];
-    uint64_t s_full[2];
+    uint64_t s_full;
+    uint64_t s_free;
     uint64_t p_full;
     uint64_t o_done;
+    uint32_t tmem_slot;
+    int abort_word;
 };
+static_assert(sizeof(Barriers) <= 128, "barrier block");
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
@@ -130,6 +144,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    return r;
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r) : "memory");
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ void tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -148,6 +175,16 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
     d |= static_cast<uint64_t>(1) << 46;
     d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Shared-memory matrix descriptor without swizzle: 8 x 8-half core matrices of 128 contiguous bytes.
+__device__ __forceinline__ uint64_t smem_desc_plain(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
     return d;
 }
 
@@ -176,20 +213,20 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
 }
 
 template <int DH>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
     using T = PTraits<DH>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // No static shared memory in this kernel: the dynamic window then starts on a 1 KB boundary, which the
+    // 128-byte swizzle needs.  Checked below; a kernel that finds it otherwise reports it and returns.
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + T::kQBytes;
     uint8_t* sV = sK + kKvStages * T::kKVBytes;
     uint8_t* sP = sV + kKvStages * T::kKVBytes;
-    __shared__ Barriers bars;
-    __shared__ uint32_t tmem_slot;
-    __shared__ int abort_word;
-    volatile int* abort_flag = &abort_word;
+    uint8_t* sOnes = sP + T::kPBytes;
+    Barriers& bars = *reinterpret_cast<Barriers*>(sOnes + T::kOnesBytes);
+    volatile int* abort_flag = &bars.abort_word;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -210,6 +247,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (qt_rev >= n_qt) {
         return;  // uniform for the CTA, before any barrier or TMEM allocation
     }
+    if ((smem_u32(smem) & 1023u) != 0u) {
+        if (threadIdx.x == 0) {
+            atomicOr(a.status, kDevTmaTimeout);
+        }
+        return;  // uniform as well
+    }
     const int qt = n_qt - 1 - qt_rev;  // longest (latest) query tiles first
     const int head = blockIdx.x - qt_rev * a.num_heads;
     const int kvh = head / a.group;
@@ -223,15 +266,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
     // ---- setup ----
     if (threadIdx.x == 0) {
-        abort_word = 0;
+        bars.abort_word = 0;
         mbar_init(&bars.q_full, 1);
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(&bars.k_full[s], 1);
             mbar_init(&bars.v_full[s], 1);
             mbar_init(&bars.kv_empty[s], 1);
         }
-        mbar_init(&bars.s_full[0], 1);
-        mbar_init(&bars.s_full[1], 1);
+        mbar_init(&bars.s_full, 1);
+        mbar_init(&bars.s_free, 128);
         mbar_init(&bars.p_full, 128);
         mbar_init(&bars.o_done, 1);
         mbar_fence_init();
@@ -239,14 +282,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
     }
+    if (threadIdx.x >= 64) {  // the constant B operand of the row-sum MMA: 256 halves of 1.0
+        reinterpret_cast<uint32_t*>(sOnes)[threadIdx.x - 64] = 0x3c003c00u;
+        fence_proxy_async_smem();
+    }
     if (warp == 1) {
-        tmem_alloc(&tmem_slot, T::kTmemCols);
+        tmem_alloc(&bars.tmem_slot, T::kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = tmem_slot;
+    const uint32_t tmem_base = bars.tmem_slot;
 
     if (warp == 0) {
         // =========================== TMA producer ===========================
@@ -254,7 +301,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             mbar_arrive_expect_tx(&bars.q_full, T::kQBytes);
 #pragma unroll
             for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                tma_load_3d(sQ + cb * T::kBlockBytes, &tm_q, &bars.q_full, cb * 64, head, static_cast<int>(q_row0));
+                tma_load_3d(sQ + cb * T::kQBlockBytes, &tm_q, &bars.q_full, cb * 64, head, static_cast<int>(q_row0));
             }
             int issued = 0;
             for (int j = 0; j < n_kv; ++j) {
@@ -269,12 +316,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 mbar_arrive_expect_tx(&bars.k_full[s], T::kKVBytes);
 #pragma unroll
                 for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                    tma_load_3d(sK + s * T::kKVBytes + cb * T::kBlockBytes, &tm_k, &bars.k_full[s], cb * 64, kvh, row);
+                    tma_load_3d(sK + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_k, &bars.k_full[s], cb * 64, kvh, row);
                 }
                 mbar_arrive_expect_tx(&bars.v_full[s], T::kKVBytes);
 #pragma unroll
                 for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                    tma_load_3d(sV + s * T::kKVBytes + cb * T::kBlockBytes, &tm_v, &bars.v_full[s], cb * 64, kvh, row);
+                    tma_load_3d(sV + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_v, &bars.v_full[s], cb * 64, kvh, row);
                 }
                 issued = j + 1;
             }
@@ -292,57 +339,62 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (lane == 0) {
             constexpr uint32_t idesc_qk = instr_desc_f16(kBlockN, false);
             constexpr uint32_t idesc_pv = instr_desc_f16(DH, true);
+            constexpr uint32_t idesc_l = instr_desc_f16(16, false);
             const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            const uint64_t ones_desc = smem_desc_plain(smem_u32(sOnes), 128, 256);
             auto issue_qk = [&](int j) {
-                const int s = j % kKvStages;
-                const uint32_t k_addr = smem_u32(sK + s * T::kKVBytes);
-                const uint32_t d = tmem_base + ((j & 1) ? T::kColS1 : T::kColS0);
+                const uint32_t k_addr = smem_u32(sK + (j % kKvStages) * T::kKVBytes);
 #pragma unroll
                 for (int cb = 0; cb < T::kColBlocks; ++cb) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const uint32_t off = cb * T::kBlockBytes + k * 32;
-                        tc_mma_f16(d, smem_desc_sw128(q_addr + off, 16, 1024), smem_desc_sw128(k_addr + off, 16, 1024),
-                                   idesc_qk, (cb | k) ? 1u : 0u);
+                        tc_mma_f16(tmem_base + T::kColS,
+                                   smem_desc_sw128(q_addr + cb * T::kQBlockBytes + k * 32, 16, 1024),
+                                   smem_desc_sw128(k_addr + cb * T::kKVBlockBytes + k * 32, 16, 1024), idesc_qk,
+                                   (cb | k) ? 1u : 0u);
                     }
                 }
-                tc_commit(&bars.s_full[j & 1]);
+                tc_commit(&bars.s_full);
             };
-            bool ok = wait_or_abort(&bars.q_full, 0, abort_flag, a.status, kDevTmaTimeout) &&
-                      wait_or_abort(&bars.k_full[0], 0, abort_flag, a.status, kDevTmaTimeout);
-            if (ok) {
-                tc_fence_after();
-                issue_qk(0);
-            }
-            for (int j = 0; ok && j < n_kv; ++j) {
+            auto issue_pv = [&](int j) {
                 const int s = j % kKvStages;
-                if (j + 1 < n_kv) {
-                    ok = wait_or_abort(&bars.k_full[(j + 1) % kKvStages], ((j + 1) / kKvStages) & 1, abort_flag, a.status,
+                const uint32_t v_addr = smem_u32(sV + s * T::kKVBytes);
+#pragma unroll
+                for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                    // P: K-major, kv index 16 ks = 32-byte step ks of the row
+                    const uint64_t pa = smem_desc_sw128(p_addr + ks * 32, 16, 1024);
+                    // V: MN-major, kv rows 16 ks .. 16 ks + 15 of every 64-channel block
+                    const uint64_t vb = smem_desc_sw128(v_addr + ks * 2048, T::kKVBlockBytes, 1024);
+                    tc_mma_f16(tmem_base + T::kColO, pa, vb, idesc_pv, (j | ks) ? 1u : 0u);
+                    tc_mma_f16(tmem_base + T::kColL, pa, ones_desc, idesc_l, (j | ks) ? 1u : 0u);
+                }
+                tc_commit(&bars.kv_empty[s]);
+                tc_commit(&bars.o_done);
+            };
+            bool ok = wait_or_abort(&bars.q_full, 0, abort_flag, a.status, kDevTmaTimeout);
+            for (int j = 0; ok && j <= n_kv; ++j) {
+                if (j < n_kv) {
+                    // S(j) = Q K(j)^T as soon as K(j) has landed and the softmax threads hold S(j-1) in registers
+                    ok = wait_or_abort(&bars.k_full[j % kKvStages], (j / kKvStages) & 1, abort_flag, a.status,
+                                       kDevTmaTimeout) &&
+                         (j == 0 || wait_or_abort(&bars.s_free, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout));
+                    if (!ok) {
+                        break;
+                    }
+                    tc_fence_after();
+                    issue_qk(j);
+                }
+                if (j > 0) {
+                    // O += P(j-1) V(j-1), L += P(j-1) 1
+                    ok = wait_or_abort(&bars.p_full, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout) &&
+                         wait_or_abort(&bars.v_full[(j - 1) % kKvStages], ((j - 1) / kKvStages) & 1, abort_flag, a.status,
                                        kDevTmaTimeout);
                     if (!ok) {
                         break;
                     }
                     tc_fence_after();
-                    issue_qk(j + 1);
+                    issue_pv(j - 1);
                 }
-                ok = wait_or_abort(&bars.p_full, j & 1, abort_flag, a.status, kDevMmaTimeout) &&
-                     wait_or_abort(&bars.v_full[s], (j / kKvStages) & 1, abort_flag, a.status, kDevTmaTimeout);
-                if (!ok) {
-                    break;
-                }
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(sV + s * T::kKVBytes);
-                const uint32_t d = tmem_base + T::kColO;
-#pragma unroll
-                for (int ks = 0; ks < kBlockN / 16; ++ks) {
-                    // P: K-major, kv index = 16 ks -> column block ks / 4, 32-byte step ks % 4
-                    const uint64_t pa = smem_desc_sw128(p_addr + (ks >> 2) * T::kBlockBytes + (ks & 3) * 32, 16, 1024);
-                    // V: MN-major, kv rows 16 ks .. 16 ks + 15 of every 64-channel block
-                    const uint64_t vb = smem_desc_sw128(v_addr + ks * 2048, T::kBlockBytes, 1024);
-                    tc_mma_f16(d, pa, vb, idesc_pv, (j | ks) ? 1u : 0u);
-                }
-                tc_commit(&bars.kv_empty[s]);
-                tc_commit(&bars.o_done);
             }
         }
     } else {
@@ -350,33 +402,55 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int lane_group = warp & 3;          // TMEM lanes this warp may touch: 32 * (warp % 4) ..
         const int r = lane_group * 32 + lane;     // query row of this thread within the tile
         const uint32_t t_lane = static_cast<uint32_t>(lane_group * 32) << 16;
-        float m_ref = kNegBig, l_sum = 0.0f;
+        const uint32_t t_s = tmem_base + t_lane + T::kColS;
+        const uint32_t t_o = tmem_base + t_lane + T::kColO;
+        const uint32_t t_l = tmem_base + t_lane + T::kColL;
+        uint8_t* prow = sP + r * 128;
+        const int swz = r & 7;
+        const float sc = a.scale_log2;
+        float m_ref = kNegBig;
         bool ok = true;
         for (int j = 0; ok && j < n_kv; ++j) {
-            ok = wait_or_abort(&bars.s_full[j & 1], (j >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+            ok = wait_or_abort(&bars.s_full, j & 1, abort_flag, a.status, kDevMmaTimeout);
             if (!ok) {
                 break;
             }
             tc_fence_after();
-            const uint32_t t_s = tmem_base + t_lane + ((j & 1) ? T::kColS1 : T::kColS0);
-            // columns of this tile that row r may see: col <= limit
-            const int64_t lim64 = hist + i0 + r - static_cast<int64_t>(j) * kBlockN;
-            const int limit = lim64 > kBlockN ? kBlockN : (lim64 < -1 ? -1 : static_cast<int>(lim64));
-            // pass 1: row maximum of the visible scores
-            float mx = kNegBig;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_s + c * 32, v);
+            float sv[kBlockN];
+            {
+                uint32_t v0[32], v1[32];
+                tmem_ld32(t_s, v0);
+                tmem_ld32(t_s + 32, v1);
                 tmem_wait_ld();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    const float s = __uint_as_float(v[e]);
-                    mx = (c * 32 + e <= limit) ? fmaxf(mx, s) : mx;
+                    sv[e] = __uint_as_float(v0[e]);
+                    sv[32 + e] = __uint_as_float(v1[e]);
                 }
             }
-            mx *= a.scale_log2;  // scale_log2 > 0, so the maximum commutes with the scaling
-            // P and O are free again once the previous P V has completed
+            // S is in registers: the MMA warp may overwrite the buffer with the next tile's scores
+            tc_fence_before();
+            mbar_arrive(&bars.s_free);
+            // columns of this tile that row r may see: col <= limit.  Only tiles that reach past the first
+            // row's horizon need the mask (uniform for the CTA).
+            const int64_t tile_hi = static_cast<int64_t>(j + 1) * kBlockN - 1;
+            if (tile_hi > hist + i0) {
+                const int64_t lim64 = hist + i0 + r - static_cast<int64_t>(j) * kBlockN;
+                const int limit = lim64 > kBlockN ? kBlockN : (lim64 < -1 ? -1 : static_cast<int>(lim64));
+#pragma unroll
+                for (int e = 0; e < kBlockN; ++e) {
+                    sv[e] = e <= limit ? sv[e] : kNegBig;
+                }
+            }
+            float mx0 = fmax3(sv[0], sv[1], sv[2]), mx1 = fmax3(sv[3], sv[4], sv[5]);
+#pragma unroll
+            for (int e = 6; e + 3 < kBlockN; e += 4) {
+                mx0 = fmax3(mx0, sv[e], sv[e + 1]);
+                mx1 = fmax3(mx1, sv[e + 2], sv[e + 3]);
+            }
+            float mx = fmax3(mx0, mx1, fmaxf(sv[kBlockN - 2], sv[kBlockN - 1]));
+            mx *= sc;  // sc > 0, so the maximum commutes with the scaling
+            // P, O and L are free again once the previous P V has completed
             if (j > 0) {
                 ok = wait_or_abort(&bars.o_done, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                 if (!ok) {
@@ -386,12 +460,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             const bool grow = mx > m_ref + kRescaleSlack;
             if (__any_sync(0xffffffffu, grow)) {
-                const float m_new = fmaxf(m_ref, mx);
+                const float m_new = grow ? mx : m_ref;
                 const float f = ex2_approx(m_ref - m_new);
                 m_ref = m_new;
-                l_sum *= f;
                 if (j > 0) {
-                    const uint32_t t_o = tmem_base + t_lane + T::kColO;
 #pragma unroll
                     for (int c = 0; c < DH / 32; ++c) {
                         uint32_t v[32];
@@ -403,51 +475,40 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         }
                         tmem_st32(t_o + c * 32, v);
                     }
+                    const uint32_t lv = tmem_ld1(t_l);
+                    tmem_wait_ld();
+                    tmem_st1(t_l, __float_as_uint(__uint_as_float(lv) * f));
                     tmem_wait_st();
                 }
             }
-            // pass 2: P = exp2(s * scale - m_ref), fp16, into the swizzled K-major P tile
+            // P = exp2(s * scale - m_ref), fp16, into the swizzled K-major P tile
+            const float neg_m = -m_ref;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_s + c * 32, v);
-                tmem_wait_ld();
-                uint32_t packed[16];
+            for (int q = 0; q < kBlockN / 8; ++q) {
+                uint32_t pk[4];
 #pragma unroll
-                for (int e = 0; e < 32; e += 2) {
-                    float p0 = ex2_approx(__uint_as_float(v[e]) * a.scale_log2 - m_ref);
-                    float p1 = ex2_approx(__uint_as_float(v[e + 1]) * a.scale_log2 - m_ref);
-                    p0 = (c * 32 + e <= limit) ? p0 : 0.0f;
-                    p1 = (c * 32 + e + 1 <= limit) ? p1 : 0.0f;
-                    // the normaliser sums the fp16-rounded values the MMA will consume, so that the
-                    // rounding of P cancels between numerator and denominator
-                    const __half2 ph = __floats2half2_rn(p0, p1);
-                    const float2 pf = __half22float2(ph);
-                    l_sum += pf.x + pf.y;
-                    packed[e >> 1] = h2_as_u32(ph);
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = ex2_approx(fmaf(sv[8 * q + 2 * e], sc, neg_m));
+                    const float p1 = ex2_approx(fmaf(sv[8 * q + 2 * e + 1], sc, neg_m));
+                    pk[e] = h2_as_u32(__floats2half2_rn(p0, p1));
                 }
-                // columns 32c .. 32c+31 = 16-byte chunks 4c .. 4c+3 of the row; column block (4c)/8
-                uint8_t* prow = sP + (c >> 1) * T::kBlockBytes + r * 128;
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int chunk = ((c & 1) * 4 + q) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(prow + chunk * 16) =
-                        make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-                }
+                *reinterpret_cast<uint4*>(prow + ((q ^ swz) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
-            // S buffer fully read (TMEM) and P fully written (shared, generic proxy): publish both
+            // TMEM updates done and P fully written (shared, generic proxy): publish both
             tc_fence_before();
             fence_proxy_async_smem();
             mbar_arrive(&bars.p_full);
         }
-        // ---- epilogue: O / l -> fp16 rows ----
+        // ---- epilogue: O / L -> fp16 rows ----
         if (ok) {
             ok = wait_or_abort(&bars.o_done, (n_kv - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
         }
         if (ok) {
             tc_fence_after();
+            const uint32_t lv = tmem_ld1(t_l);
+            tmem_wait_ld();
+            const float l_sum = __uint_as_float(lv);
             const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
-            const uint32_t t_o = tmem_base + t_lane + T::kColO;
             __half* dst = a.out + ((q_row0 + r) * a.num_heads + head) * DH;
 #pragma unroll
             for (int c = 0; c < DH / 32; ++c) {
@@ -478,7 +539,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
 }
 
-// Prefix sum of the (128-row padded) kv lengths of the prefill sequences: first staging row of each.
+// Prefix sum of the (tile-padded) kv lengths of the prefill sequences: first staging row of each.
 __global__ void prefill_stage_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
                                           int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen,
                                           int64_t* __restrict__ stage_starts) {
@@ -496,7 +557,7 @@ __global__ void prefill_stage_plan_kernel(const int64_t* __restrict__ seqstarts,
 }
 
 // Dequantise the cache rows of the prefill sequences (history and this call's tokens) into fp16
-// staging tensors [rows, Hkv, Dh]; pad rows up to the next multiple of 128 are zeroed.
+// staging tensors [rows, Hkv, Dh]; pad rows up to the next multiple of the kv tile are zeroed.
 __global__ void __launch_bounds__(256)
 prefill_stage_dequant_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
                              const int64_t* __restrict__ cachestarts, const int64_t* __restrict__ stage_starts,
@@ -615,13 +676,14 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
         stage_starts = ss;
     }
 
-    // tensor maps: {Dh, heads, rows} with a box of one head's [128 rows][64 halves], 128-byte swizzle
+    // tensor maps: {Dh, heads, rows} with a box of one head's [tile rows][64 halves], 128-byte swizzle
     CUtensorMap tm_q, tm_k, tm_v;
     {
         const uint64_t dq[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(p.num_heads),
                                 static_cast<uint64_t>(p.total_tokens)};
         const uint64_t sq[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(p.num_heads) * DH * 2};
         const uint32_t box[3] = {64, 1, kBlockM};
+        const uint32_t box_kv[3] = {64, 1, kBlockN};
         rc = encode_tensor_map(&tm_q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, query, dq, sq, box, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PPLB200_SUCCESS) {
             return rc;
@@ -629,11 +691,11 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
         const uint64_t dk[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(p.num_kv_heads),
                                 static_cast<uint64_t>(kv_rows)};
         const uint64_t sk[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(p.num_kv_heads) * DH * 2};
-        rc = encode_tensor_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, k_src, dk, sk, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = encode_tensor_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, k_src, dk, sk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
-        rc = encode_tensor_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, v_src, dk, sk, box, CU_TENSOR_MAP_SWIZZLE_128B);
+        rc = encode_tensor_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, v_src, dk, sk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
