@@ -4,7 +4,8 @@
 //
 // One CTA computes a 128-row query tile of one (sequence, query head); two CTAs share an SM, so that
 // one CTA's MMAs run under the other's softmax:
-//   warp 0      TMA producer: the Q tile once, then K/V tiles of 64 rows through a 2-stage ring
+//   warp 0      TMA producer: the Q tile once, then K and V tiles of 64 rows through two 2-stage rings
+//               (one lane each)
 //   warp 1      allocates TMEM (256 columns) and issues the MMAs (one lane): S = Q K^T into a 64-column
 //               TMEM buffer, then O += P V and, with a constant tile of ones as the B operand, the
 //               row sums L += P 1 into two more accumulators; completion is reported to mbarriers with
@@ -77,7 +78,8 @@ struct Barriers {
     uint64_t q_full;
     uint64_t k_full[kKvStages];
     uint64_t v_full[kKvStages];
-    uint64_t kv_empty[kKvStages];
+    uint64_t k_empty[kKvStages];
+    uint64_t v_empty[kKvStages];
     uint64_t s_full;
     uint64_t s_free;
     uint64_t p_full;
@@ -164,28 +166,36 @@ __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (sm_100).
-//   K-major operand ([rows][64 halves] blocks): lbo is unused (1), sbo = 1024 (8 rows of 128 bytes).
-//   MN-major operand (V as [kv rows][64 channels]): lbo = bytes between 64-channel blocks,
-//   sbo = 1024 (8 kv rows of 128 bytes).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+// Shared-memory matrix descriptors (descriptor version 1, sm_100).
+//   K-major operand, 128-byte swizzle ([rows][64 halves] blocks): lbo is unused (16), sbo = 1024 (8 rows
+//   of 128 bytes).
+//   MN-major operand, 128-byte swizzle (V as [kv rows][64 channels]): lbo = bytes between 64-channel
+//   blocks, sbo = 1024 (8 kv rows of 128 bytes).
+//   No swizzle: 8 x 8-half core matrices of 128 contiguous bytes, lbo / sbo apart along K / along N.
+// Descriptors are built once as (low word, high word); stepping through a tile only adds to the low word
+// (the start address in 16-byte units), which stays in uniform registers in warp-uniform code.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+    return ((saddr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__device__ __forceinline__ constexpr uint32_t desc_hi(uint32_t sbo_bytes, uint32_t layout) {
+    return ((sbo_bytes >> 4) & 0x3fffu) | (1u << 14) | (layout << 29);
+}
+__device__ __forceinline__ uint64_t desc_join(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
     return d;
 }
-
-// Shared-memory matrix descriptor without swizzle: 8 x 8-half core matrices of 128 contiguous bytes.
-__device__ __forceinline__ uint64_t smem_desc_plain(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((saddr & 0x3ffffu) >> 4);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    return d;
+// One lane of a converged warp; the code around it stays warp-uniform.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "elect.sync _|p, 0xffffffff;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 // Instruction descriptor for kind::f16: fp16 A and B, fp32 D, M = 128.
@@ -271,7 +281,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(&bars.k_full[s], 1);
             mbar_init(&bars.v_full[s], 1);
-            mbar_init(&bars.kv_empty[s], 1);
+            mbar_init(&bars.k_empty[s], 1);
+            mbar_init(&bars.v_empty[s], 1);
         }
         mbar_init(&bars.s_full, 1);
         mbar_init(&bars.s_free, 128);
@@ -297,104 +308,135 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
 
     if (warp == 0) {
         // =========================== TMA producer ===========================
-        if (lane == 0) {
+        // The whole warp runs the loop (waits are warp-uniform); an elected lane issues the copies.  A K
+        // stage is free again as soon as its Q K^T has completed, a V stage once its P V has; the copies are
+        // issued in the order in which those completions arrive: K(i), then V(i-1).
+        if (elect_one()) {
             mbar_arrive_expect_tx(&bars.q_full, T::kQBytes);
 #pragma unroll
             for (int cb = 0; cb < T::kColBlocks; ++cb) {
                 tma_load_3d(sQ + cb * T::kQBlockBytes, &tm_q, &bars.q_full, cb * 64, head, static_cast<int>(q_row0));
             }
-            int issued = 0;
-            for (int j = 0; j < n_kv; ++j) {
-                const int s = j % kKvStages;
-                if (j >= kKvStages) {
-                    if (!wait_or_abort(&bars.kv_empty[s], ((j / kKvStages) - 1) & 1, abort_flag, a.status,
-                                       kDevMmaTimeout)) {
+        }
+        __syncwarp();
+        bool ok = true;
+        int k_issued = 0, v_issued = 0;
+        for (int i = 0; ok && i <= n_kv; ++i) {
+            if (i < n_kv) {
+                const int s = i % kKvStages;
+                if (i >= kKvStages) {
+                    ok = wait_or_abort(&bars.k_empty[s], ((i / kKvStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                    if (!ok) {
                         break;
                     }
                 }
-                const int row = static_cast<int>(kv_row0 + static_cast<int64_t>(j) * kBlockN);
-                mbar_arrive_expect_tx(&bars.k_full[s], T::kKVBytes);
+                if (elect_one()) {
+                    const int row = static_cast<int>(kv_row0 + static_cast<int64_t>(i) * kBlockN);
+                    mbar_arrive_expect_tx(&bars.k_full[s], T::kKVBytes);
 #pragma unroll
-                for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                    tma_load_3d(sK + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_k, &bars.k_full[s], cb * 64, kvh, row);
+                    for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                        tma_load_3d(sK + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_k, &bars.k_full[s], cb * 64, kvh, row);
+                    }
                 }
-                mbar_arrive_expect_tx(&bars.v_full[s], T::kKVBytes);
-#pragma unroll
-                for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                    tma_load_3d(sV + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_v, &bars.v_full[s], cb * 64, kvh, row);
-                }
-                issued = j + 1;
+                __syncwarp();
+                k_issued = i + 1;
             }
-            if (*abort_flag) {
-                // drain: every copy this thread issued must have landed before the CTA may exit
-                mbar_wait_bounded(&bars.q_full, 0);
-                for (int j = issued > kKvStages ? issued - kKvStages : 0; j < issued; ++j) {
-                    mbar_wait_bounded(&bars.k_full[j % kKvStages], (j / kKvStages) & 1);
-                    mbar_wait_bounded(&bars.v_full[j % kKvStages], (j / kKvStages) & 1);
+            if (i > 0) {
+                const int jv = i - 1;
+                const int s = jv % kKvStages;
+                if (jv >= kKvStages) {
+                    ok = wait_or_abort(&bars.v_empty[s], ((jv / kKvStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                    if (!ok) {
+                        break;
+                    }
                 }
+                if (elect_one()) {
+                    const int row = static_cast<int>(kv_row0 + static_cast<int64_t>(jv) * kBlockN);
+                    mbar_arrive_expect_tx(&bars.v_full[s], T::kKVBytes);
+#pragma unroll
+                    for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                        tma_load_3d(sV + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_v, &bars.v_full[s], cb * 64, kvh, row);
+                    }
+                }
+                __syncwarp();
+                v_issued = jv + 1;
+            }
+        }
+        if (*abort_flag) {
+            // drain: every copy this warp issued must have landed before the CTA may exit
+            mbar_wait_bounded(&bars.q_full, 0);
+            for (int j = k_issued > kKvStages ? k_issued - kKvStages : 0; j < k_issued; ++j) {
+                mbar_wait_bounded(&bars.k_full[j % kKvStages], (j / kKvStages) & 1);
+            }
+            for (int j = v_issued > kKvStages ? v_issued - kKvStages : 0; j < v_issued; ++j) {
+                mbar_wait_bounded(&bars.v_full[j % kKvStages], (j / kKvStages) & 1);
             }
         }
     } else if (warp == 1) {
         // =========================== MMA issuer ===========================
-        if (lane == 0) {
-            constexpr uint32_t idesc_qk = instr_desc_f16(kBlockN, false);
-            constexpr uint32_t idesc_pv = instr_desc_f16(DH, true);
-            constexpr uint32_t idesc_l = instr_desc_f16(16, false);
-            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-            const uint64_t ones_desc = smem_desc_plain(smem_u32(sOnes), 128, 256);
-            auto issue_qk = [&](int j) {
-                const uint32_t k_addr = smem_u32(sK + (j % kKvStages) * T::kKVBytes);
-#pragma unroll
-                for (int cb = 0; cb < T::kColBlocks; ++cb) {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        tc_mma_f16(tmem_base + T::kColS,
-                                   smem_desc_sw128(q_addr + cb * T::kQBlockBytes + k * 32, 16, 1024),
-                                   smem_desc_sw128(k_addr + cb * T::kKVBlockBytes + k * 32, 16, 1024), idesc_qk,
-                                   (cb | k) ? 1u : 0u);
-                    }
-                }
-                tc_commit(&bars.s_full);
-            };
-            auto issue_pv = [&](int j) {
+        // Warp-uniform as well: all lanes wait, an elected lane issues.  Operand descriptors are built once.
+        constexpr uint32_t idesc_qk = instr_desc_f16(kBlockN, false);
+        constexpr uint32_t idesc_pv = instr_desc_f16(DH, true);
+        constexpr uint32_t idesc_l = instr_desc_f16(16, false);
+        constexpr uint32_t hi_sw128 = desc_hi(1024, 2);  // 128-byte swizzle, 8-row groups 1024 bytes apart
+        constexpr uint32_t hi_plain = desc_hi(256, 0);
+        const uint32_t q_lo = desc_lo(smem_u32(sQ), 16);
+        const uint32_t k_lo = desc_lo(smem_u32(sK), 16);
+        const uint32_t p_lo = desc_lo(smem_u32(sP), 16);
+        const uint32_t v_lo = desc_lo(smem_u32(sV), T::kKVBlockBytes);  // MN-major: 64-channel blocks lbo apart
+        const uint64_t ones_desc = desc_join(desc_lo(smem_u32(sOnes), 128), hi_plain);
+        const uint32_t d_s = tmem_base + T::kColS, d_o = tmem_base + T::kColO, d_l = tmem_base + T::kColL;
+        bool ok = wait_or_abort(&bars.q_full, 0, abort_flag, a.status, kDevTmaTimeout);
+        for (int j = 0; ok && j <= n_kv; ++j) {
+            if (j < n_kv) {
+                // S(j) = Q K(j)^T as soon as K(j) has landed and the softmax threads hold S(j-1) in registers
                 const int s = j % kKvStages;
-                const uint32_t v_addr = smem_u32(sV + s * T::kKVBytes);
+                ok = wait_or_abort(&bars.k_full[s], (j / kKvStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
+                     (j == 0 || wait_or_abort(&bars.s_free, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout));
+                if (!ok) {
+                    break;
+                }
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint32_t ks_lo = k_lo + s * (T::kKVBytes >> 4);
 #pragma unroll
-                for (int ks = 0; ks < kBlockN / 16; ++ks) {
-                    // P: K-major, kv index 16 ks = 32-byte step ks of the row
-                    const uint64_t pa = smem_desc_sw128(p_addr + ks * 32, 16, 1024);
-                    // V: MN-major, kv rows 16 ks .. 16 ks + 15 of every 64-channel block
-                    const uint64_t vb = smem_desc_sw128(v_addr + ks * 2048, T::kKVBlockBytes, 1024);
-                    tc_mma_f16(tmem_base + T::kColO, pa, vb, idesc_pv, (j | ks) ? 1u : 0u);
-                    tc_mma_f16(tmem_base + T::kColL, pa, ones_desc, idesc_l, (j | ks) ? 1u : 0u);
-                }
-                tc_commit(&bars.kv_empty[s]);
-                tc_commit(&bars.o_done);
-            };
-            bool ok = wait_or_abort(&bars.q_full, 0, abort_flag, a.status, kDevTmaTimeout);
-            for (int j = 0; ok && j <= n_kv; ++j) {
-                if (j < n_kv) {
-                    // S(j) = Q K(j)^T as soon as K(j) has landed and the softmax threads hold S(j-1) in registers
-                    ok = wait_or_abort(&bars.k_full[j % kKvStages], (j / kKvStages) & 1, abort_flag, a.status,
-                                       kDevTmaTimeout) &&
-                         (j == 0 || wait_or_abort(&bars.s_free, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout));
-                    if (!ok) {
-                        break;
+                    for (int cb = 0; cb < T::kColBlocks; ++cb) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            tc_mma_f16(d_s, desc_join(q_lo + cb * (T::kQBlockBytes >> 4) + 2 * k, hi_sw128),
+                                       desc_join(ks_lo + cb * (T::kKVBlockBytes >> 4) + 2 * k, hi_sw128), idesc_qk,
+                                       (cb | k) ? 1u : 0u);
+                        }
                     }
-                    tc_fence_after();
-                    issue_qk(j);
+                    tc_commit(&bars.s_full);
+                    tc_commit(&bars.k_empty[s]);
                 }
-                if (j > 0) {
-                    // O += P(j-1) V(j-1), L += P(j-1) 1
-                    ok = wait_or_abort(&bars.p_full, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout) &&
-                         wait_or_abort(&bars.v_full[(j - 1) % kKvStages], ((j - 1) / kKvStages) & 1, abort_flag, a.status,
-                                       kDevTmaTimeout);
-                    if (!ok) {
-                        break;
+                __syncwarp();
+            }
+            if (j > 0) {
+                // O += P(j-1) V(j-1), L += P(j-1) 1
+                const int jp = j - 1;
+                const int s = jp % kKvStages;
+                ok = wait_or_abort(&bars.p_full, jp & 1, abort_flag, a.status, kDevMmaTimeout) &&
+                     wait_or_abort(&bars.v_full[s], (jp / kKvStages) & 1, abort_flag, a.status, kDevTmaTimeout);
+                if (!ok) {
+                    break;
+                }
+                tc_fence_after();
+                if (elect_one()) {
+                    const uint32_t vs_lo = v_lo + s * (T::kKVBytes >> 4);
+#pragma unroll
+                    for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                        // P: K-major, kv index 16 ks = 32-byte step ks of the row;
+                        // V: MN-major, kv rows 16 ks .. 16 ks + 15 (2048 bytes) of every 64-channel block
+                        const uint64_t pa = desc_join(p_lo + 2 * ks, hi_sw128);
+                        tc_mma_f16(d_o, pa, desc_join(vs_lo + ks * (2048 >> 4), hi_sw128), idesc_pv, (jp | ks) ? 1u : 0u);
+                        tc_mma_f16(d_l, pa, ones_desc, idesc_l, (jp | ks) ? 1u : 0u);
                     }
-                    tc_fence_after();
-                    issue_pv(j - 1);
+                    tc_commit(&bars.v_empty[s]);
+                    tc_commit(&bars.o_done);
                 }
+                __syncwarp();
             }
         }
     } else {
