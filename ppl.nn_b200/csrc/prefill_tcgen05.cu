@@ -4,19 +4,19 @@
 //
 // One CTA computes a 128-row query tile of one (sequence, query head); two CTAs share an SM, so that
 // one CTA's MMAs run under the other's softmax:
-//   warp 0      TMA producer: the Q tile once, then K and V tiles of 64 rows through two 2-stage rings
-//               (one lane each)
-//   warp 1      allocates TMEM (256 columns) and issues the MMAs (one lane): S = Q K^T into a 64-column
-//               TMEM buffer, then O += P V and, with a constant tile of ones as the B operand, the
-//               row sums L += P 1 into two more accumulators; completion is reported to mbarriers with
-//               tcgen05.commit
+//   warp 0      TMA producer: the Q tile once, then K tiles (3-stage ring) and V tiles (2-stage ring)
+//               of 64 rows each
+//   warp 1      allocates TMEM (256 columns) and issues the MMAs: S = Q K^T into a 64-column TMEM buffer
+//               (both operands in shared memory), then O += P V with P read from TMEM (the A operand)
+//               and V from shared memory; completion is reported to mbarriers with tcgen05.commit
 //   warps 2..5  128 softmax threads, one query row each (TMEM lane = row): read S once with tcgen05.ld
 //               (the buffer is handed back to the MMA warp straight away), causal mask on diagonal
-//               tiles only, running maximum in the exp2 domain (the O and L accumulators are rescaled
-//               in TMEM only when the maximum grew by more than 2^8), write P as fp16 into shared
-//               memory in the 128-byte-swizzled K-major layout the MMA expects, and finally divide O
-//               by L and store fp16 rows.  Taking L from the MMA means the normaliser sums exactly the
-//               fp16-rounded P values that the numerator uses, at no cost to the softmax threads.
+//               tiles only, running maximum in the exp2 domain (the O accumulator is rescaled in TMEM
+//               only when the maximum grew by more than 2^8), write P as packed fp16 into one of two
+//               TMEM buffers with tcgen05.st, so that the next tile's softmax does not wait for this
+//               tile's P V, and finally divide O by the row sum and store fp16 rows.  The row sum adds
+//               the fp16-rounded P values, the very numbers the numerator uses.
+// Both the producer and the MMA warp run warp-uniform code (every lane waits, an elected lane issues).
 // K/V come from this call's fp16 current_key/current_value (the default), or, with
 // enable_cache_prefill, from an fp16 staging copy of the INT8 cache rows (history included) that a
 // dequantising gather writes into the workspace first.
@@ -38,7 +38,8 @@ namespace {
 constexpr int kBlockM = 128;   // query rows per CTA
 constexpr int kBlockN = 64;    // kv rows per tile
 constexpr int kThreads = 192;  // 6 warps
-constexpr int kKvStages = 2;
+constexpr int kKStages = 3;
+constexpr int kVStages = 2;
 constexpr int kCtasPerSm = 2;
 constexpr float kNegBig = -1.0e30f;
 constexpr float kRescaleSlack = 8.0f;
@@ -50,14 +51,13 @@ struct PTraits {
     static constexpr int kKVBlockBytes = kBlockN * 128;          // one [64 rows][64 halves] block of K or V
     static constexpr int kQBytes = kColBlocks * kQBlockBytes;
     static constexpr int kKVBytes = kColBlocks * kKVBlockBytes;  // one K (or V) tile
-    static constexpr int kPBytes = kBlockM * kBlockN * 2;        // P tile: one [128 rows][64 halves] block
-    static constexpr int kOnesBytes = 512;                       // 16 x 16 halves of 1.0 (four 8x8 core matrices)
-    static constexpr int kBarrierBytes = 128;
+    static constexpr int kBarrierBytes = 256;
     // The same for every head size (the Dh = 128 figure), so that never more than two CTAs share an SM
     // and the two 256-column TMEM allocations always fit.
-    static constexpr int kSmemBytes = 32768 + 2 * kKvStages * 16384 + 16384 + kOnesBytes + kBarrierBytes;
-    static constexpr uint32_t kTmemCols = 256;                   // S | L | O
-    static constexpr uint32_t kColS = 0, kColL = 64, kColO = 128;
+    static constexpr int kSmemBytes = 32768 + (kKStages + kVStages) * 16384 + kBarrierBytes;
+    static constexpr uint32_t kTmemCols = 256;                   // S | P0 | P1 | O
+    static constexpr uint32_t kColS = 0, kColP = 64, kColO = 128;
+    static constexpr uint32_t kPCols = kBlockN / 2;              // packed fp16: two kv columns per TMEM column
 };
 
 struct PrefillArgs {
@@ -76,18 +76,18 @@ struct PrefillArgs {
 
 struct Barriers {
     uint64_t q_full;
-    uint64_t k_full[kKvStages];
-    uint64_t v_full[kKvStages];
-    uint64_t k_empty[kKvStages];
-    uint64_t v_empty[kKvStages];
+    uint64_t k_full[kKStages];
+    uint64_t v_full[kVStages];
+    uint64_t k_empty[kKStages];
+    uint64_t v_empty[kVStages];
     uint64_t s_full;
     uint64_t s_free;
-    uint64_t p_full;
-    uint64_t o_done;
+    uint64_t p_full[2];   // one per P buffer, so that a waiter can never be lapped
+    uint64_t pv_done[2];  // P V of the tile that used P buffer 0 / 1 has completed
     uint32_t tmem_slot;
     int abort_word;
 };
-static_assert(sizeof(Barriers) <= 128, "barrier block");
+static_assert(sizeof(Barriers) <= 256, "barrier block");
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
@@ -123,6 +123,37 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 rows x 16 halves, two per column) read from TMEM
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// l += lo(ph) + hi(ph), the two fp16 values widened exactly
+__device__ __forceinline__ void add_half2_to_float(float& l, uint32_t ph) {
+    asm("{\n"
+        ".reg .b16 h0, h1;\n"
+        "mov.b32 {h0, h1}, %1;\n"
+        "add.rn.f32.f16 %0, h0, %0;\n"
+        "add.rn.f32.f16 %0, h1, %0;\n"
+        "}\n"
+        : "+f"(l)
+        : "r"(ph));
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -145,14 +176,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
-}
-__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
-    uint32_t r;
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
-    return r;
-}
-__device__ __forceinline__ void tmem_st1(uint32_t taddr, uint32_t r) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(r) : "memory");
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
@@ -232,10 +255,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + T::kQBytes;
-    uint8_t* sV = sK + kKvStages * T::kKVBytes;
-    uint8_t* sP = sV + kKvStages * T::kKVBytes;
-    uint8_t* sOnes = sP + T::kPBytes;
-    Barriers& bars = *reinterpret_cast<Barriers*>(sOnes + T::kOnesBytes);
+    uint8_t* sV = sK + kKStages * T::kKVBytes;
+    Barriers& bars = *reinterpret_cast<Barriers*>(sV + kVStages * T::kKVBytes);
     volatile int* abort_flag = &bars.abort_word;
 
     const int warp = threadIdx.x >> 5;
@@ -278,24 +299,24 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     if (threadIdx.x == 0) {
         bars.abort_word = 0;
         mbar_init(&bars.q_full, 1);
-        for (int s = 0; s < kKvStages; ++s) {
+        for (int s = 0; s < kKStages; ++s) {
             mbar_init(&bars.k_full[s], 1);
-            mbar_init(&bars.v_full[s], 1);
             mbar_init(&bars.k_empty[s], 1);
+        }
+        for (int s = 0; s < kVStages; ++s) {
+            mbar_init(&bars.v_full[s], 1);
             mbar_init(&bars.v_empty[s], 1);
         }
         mbar_init(&bars.s_full, 1);
         mbar_init(&bars.s_free, 128);
-        mbar_init(&bars.p_full, 128);
-        mbar_init(&bars.o_done, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&bars.p_full[i], 128);
+            mbar_init(&bars.pv_done[i], 1);
+        }
         mbar_fence_init();
         tma_prefetch_desc(&tm_q);
         tma_prefetch_desc(&tm_k);
         tma_prefetch_desc(&tm_v);
-    }
-    if (threadIdx.x >= 64) {  // the constant B operand of the row-sum MMA: 256 halves of 1.0
-        reinterpret_cast<uint32_t*>(sOnes)[threadIdx.x - 64] = 0x3c003c00u;
-        fence_proxy_async_smem();
     }
     if (warp == 1) {
         tmem_alloc(&bars.tmem_slot, T::kTmemCols);
@@ -323,9 +344,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         int k_issued = 0, v_issued = 0;
         for (int i = 0; ok && i <= n_kv; ++i) {
             if (i < n_kv) {
-                const int s = i % kKvStages;
-                if (i >= kKvStages) {
-                    ok = wait_or_abort(&bars.k_empty[s], ((i / kKvStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                const int s = i % kKStages;
+                if (i >= kKStages) {
+                    ok = wait_or_abort(&bars.k_empty[s], ((i / kKStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                     if (!ok) {
                         break;
                     }
@@ -343,9 +364,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             if (i > 0) {
                 const int jv = i - 1;
-                const int s = jv % kKvStages;
-                if (jv >= kKvStages) {
-                    ok = wait_or_abort(&bars.v_empty[s], ((jv / kKvStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                const int s = jv % kVStages;
+                if (jv >= kVStages) {
+                    ok = wait_or_abort(&bars.v_empty[s], ((jv / kVStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                     if (!ok) {
                         break;
                     }
@@ -365,11 +386,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         if (*abort_flag) {
             // drain: every copy this warp issued must have landed before the CTA may exit
             mbar_wait_bounded(&bars.q_full, 0);
-            for (int j = k_issued > kKvStages ? k_issued - kKvStages : 0; j < k_issued; ++j) {
-                mbar_wait_bounded(&bars.k_full[j % kKvStages], (j / kKvStages) & 1);
+            for (int j = k_issued > kKStages ? k_issued - kKStages : 0; j < k_issued; ++j) {
+                mbar_wait_bounded(&bars.k_full[j % kKStages], (j / kKStages) & 1);
             }
-            for (int j = v_issued > kKvStages ? v_issued - kKvStages : 0; j < v_issued; ++j) {
-                mbar_wait_bounded(&bars.v_full[j % kKvStages], (j / kKvStages) & 1);
+            for (int j = v_issued > kVStages ? v_issued - kVStages : 0; j < v_issued; ++j) {
+                mbar_wait_bounded(&bars.v_full[j % kVStages], (j / kVStages) & 1);
             }
         }
     } else if (warp == 1) {
@@ -377,21 +398,17 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // Warp-uniform as well: all lanes wait, an elected lane issues.  Operand descriptors are built once.
         constexpr uint32_t idesc_qk = instr_desc_f16(kBlockN, false);
         constexpr uint32_t idesc_pv = instr_desc_f16(DH, true);
-        constexpr uint32_t idesc_l = instr_desc_f16(16, false);
         constexpr uint32_t hi_sw128 = desc_hi(1024, 2);  // 128-byte swizzle, 8-row groups 1024 bytes apart
-        constexpr uint32_t hi_plain = desc_hi(256, 0);
         const uint32_t q_lo = desc_lo(smem_u32(sQ), 16);
         const uint32_t k_lo = desc_lo(smem_u32(sK), 16);
-        const uint32_t p_lo = desc_lo(smem_u32(sP), 16);
         const uint32_t v_lo = desc_lo(smem_u32(sV), T::kKVBlockBytes);  // MN-major: 64-channel blocks lbo apart
-        const uint64_t ones_desc = desc_join(desc_lo(smem_u32(sOnes), 128), hi_plain);
-        const uint32_t d_s = tmem_base + T::kColS, d_o = tmem_base + T::kColO, d_l = tmem_base + T::kColL;
+        const uint32_t d_s = tmem_base + T::kColS, d_o = tmem_base + T::kColO, a_p = tmem_base + T::kColP;
         bool ok = wait_or_abort(&bars.q_full, 0, abort_flag, a.status, kDevTmaTimeout);
         for (int j = 0; ok && j <= n_kv; ++j) {
             if (j < n_kv) {
                 // S(j) = Q K(j)^T as soon as K(j) has landed and the softmax threads hold S(j-1) in registers
-                const int s = j % kKvStages;
-                ok = wait_or_abort(&bars.k_full[s], (j / kKvStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
+                const int s = j % kKStages;
+                ok = wait_or_abort(&bars.k_full[s], (j / kKStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
                      (j == 0 || wait_or_abort(&bars.s_free, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout));
                 if (!ok) {
                     break;
@@ -414,27 +431,27 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 __syncwarp();
             }
             if (j > 0) {
-                // O += P(j-1) V(j-1), L += P(j-1) 1
+                // O += P(j-1) V(j-1)
                 const int jp = j - 1;
-                const int s = jp % kKvStages;
-                ok = wait_or_abort(&bars.p_full, jp & 1, abort_flag, a.status, kDevMmaTimeout) &&
-                     wait_or_abort(&bars.v_full[s], (jp / kKvStages) & 1, abort_flag, a.status, kDevTmaTimeout);
+                const int s = jp % kVStages;
+                ok = wait_or_abort(&bars.p_full[jp & 1], (jp >> 1) & 1, abort_flag, a.status, kDevMmaTimeout) &&
+                     wait_or_abort(&bars.v_full[s], (jp / kVStages) & 1, abort_flag, a.status, kDevTmaTimeout);
                 if (!ok) {
                     break;
                 }
                 tc_fence_after();
                 if (elect_one()) {
                     const uint32_t vs_lo = v_lo + s * (T::kKVBytes >> 4);
+                    const uint32_t pa = a_p + (jp & 1) * T::kPCols;
 #pragma unroll
                     for (int ks = 0; ks < kBlockN / 16; ++ks) {
-                        // P: K-major, kv index 16 ks = 32-byte step ks of the row;
+                        // P: kv index 16 ks = TMEM column 8 ks of the buffer (two halves per column);
                         // V: MN-major, kv rows 16 ks .. 16 ks + 15 (2048 bytes) of every 64-channel block
-                        const uint64_t pa = desc_join(p_lo + 2 * ks, hi_sw128);
-                        tc_mma_f16(d_o, pa, desc_join(vs_lo + ks * (2048 >> 4), hi_sw128), idesc_pv, (jp | ks) ? 1u : 0u);
-                        tc_mma_f16(d_l, pa, ones_desc, idesc_l, (jp | ks) ? 1u : 0u);
+                        tc_mma_f16_ts(d_o, pa + 8 * ks, desc_join(vs_lo + ks * (2048 >> 4), hi_sw128), idesc_pv,
+                                      (jp | ks) ? 1u : 0u);
                     }
                     tc_commit(&bars.v_empty[s]);
-                    tc_commit(&bars.o_done);
+                    tc_commit(&bars.pv_done[jp & 1]);
                 }
                 __syncwarp();
             }
@@ -446,11 +463,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const uint32_t t_lane = static_cast<uint32_t>(lane_group * 32) << 16;
         const uint32_t t_s = tmem_base + t_lane + T::kColS;
         const uint32_t t_o = tmem_base + t_lane + T::kColO;
-        const uint32_t t_l = tmem_base + t_lane + T::kColL;
-        uint8_t* prow = sP + r * 128;
-        const int swz = r & 7;
+        const uint32_t t_p = tmem_base + t_lane + T::kColP;
         const float sc = a.scale_log2;
-        float m_ref = kNegBig;
+        float m_ref = kNegBig, l_sum = 0.0f;
         bool ok = true;
         for (int j = 0; ok && j < n_kv; ++j) {
             ok = wait_or_abort(&bars.s_full, j & 1, abort_flag, a.status, kDevMmaTimeout);
@@ -474,7 +489,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             tc_fence_before();
             mbar_arrive(&bars.s_free);
             // columns of this tile that row r may see: col <= limit.  Only tiles that reach past the first
-            // row's horizon need the mask (uniform for the CTA).
+            // row's horizon need the mask (uniform for the CTA).  Column 0 of tile 0 is visible to every row,
+            // so m_ref is a real score from the first tile on.
             const int64_t tile_hi = static_cast<int64_t>(j + 1) * kBlockN - 1;
             if (tile_hi > hist + i0) {
                 const int64_t lim64 = hist + i0 + r - static_cast<int64_t>(j) * kBlockN;
@@ -492,20 +508,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             float mx = fmax3(mx0, mx1, fmaxf(sv[kBlockN - 2], sv[kBlockN - 1]));
             mx *= sc;  // sc > 0, so the maximum commutes with the scaling
-            // P, O and L are free again once the previous P V has completed
-            if (j > 0) {
-                ok = wait_or_abort(&bars.o_done, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
-                if (!ok) {
-                    break;
-                }
-                tc_fence_after();
-            }
             const bool grow = mx > m_ref + kRescaleSlack;
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? mx : m_ref;
                 const float f = ex2_approx(m_ref - m_new);
                 m_ref = m_new;
+                l_sum *= f;
                 if (j > 0) {
+                    // O may be touched once the previous tile's P V has completed
+                    ok = wait_or_abort(&bars.pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                    if (!ok) {
+                        break;
+                    }
+                    tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < DH / 32; ++c) {
                         uint32_t v[32];
@@ -517,39 +532,42 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         }
                         tmem_st32(t_o + c * 32, v);
                     }
-                    const uint32_t lv = tmem_ld1(t_l);
-                    tmem_wait_ld();
-                    tmem_st1(t_l, __float_as_uint(__uint_as_float(lv) * f));
                     tmem_wait_st();
                 }
             }
-            // P = exp2(s * scale - m_ref), fp16, into the swizzled K-major P tile
-            const float neg_m = -m_ref;
-#pragma unroll
-            for (int q = 0; q < kBlockN / 8; ++q) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float p0 = ex2_approx(fmaf(sv[8 * q + 2 * e], sc, neg_m));
-                    const float p1 = ex2_approx(fmaf(sv[8 * q + 2 * e + 1], sc, neg_m));
-                    pk[e] = h2_as_u32(__floats2half2_rn(p0, p1));
+            // this tile's P buffer is free once the P V of the tile before the previous one has completed
+            if (j >= 2) {
+                ok = wait_or_abort(&bars.pv_done[j & 1], ((j - 2) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                if (!ok) {
+                    break;
                 }
-                *reinterpret_cast<uint4*>(prow + ((q ^ swz) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                tc_fence_after();
             }
-            // TMEM updates done and P fully written (shared, generic proxy): publish both
+            // P = exp2(s * scale - m_ref) as packed fp16 into TMEM: column c of the buffer = kv columns 2c, 2c+1
+            const float neg_m = -m_ref;
+            const uint32_t t_pb = t_p + (j & 1) * T::kPCols;
+#pragma unroll
+            for (int q = 0; q < kBlockN / 32; ++q) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                    const float p0 = ex2_approx(fmaf(sv[32 * q + 2 * e], sc, neg_m));
+                    const float p1 = ex2_approx(fmaf(sv[32 * q + 2 * e + 1], sc, neg_m));
+                    pk[e] = h2_as_u32(__floats2half2_rn(p0, p1));
+                    add_half2_to_float(l_sum, pk[e]);
+                }
+                tmem_st16(t_pb + 16 * q, pk);
+            }
+            tmem_wait_st();
             tc_fence_before();
-            fence_proxy_async_smem();
-            mbar_arrive(&bars.p_full);
+            mbar_arrive(&bars.p_full[j & 1]);
         }
-        // ---- epilogue: O / L -> fp16 rows ----
+        // ---- epilogue: O / l -> fp16 rows ----
         if (ok) {
-            ok = wait_or_abort(&bars.o_done, (n_kv - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+            ok = wait_or_abort(&bars.pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
         }
         if (ok) {
             tc_fence_after();
-            const uint32_t lv = tmem_ld1(t_l);
-            tmem_wait_ld();
-            const float l_sum = __uint_as_float(lv);
             const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
             __half* dst = a.out + ((q_row0 + r) * a.num_heads + head) * DH;
 #pragma unroll
