@@ -31,6 +31,10 @@
 #include "launch.h"
 #include "tensor_map.h"
 
+#ifndef PPLB200_PREFILL_WAIT
+#define PPLB200_PREFILL_WAIT mbar_test_wait
+#endif
+
 namespace pplb200 {
 
 namespace {
@@ -68,6 +72,9 @@ struct PrefillArgs {
     uint32_t* status;
     int64_t max_seqlen;
     int32_t decoding_batches;
+    int32_t prefill_batches;
+    int32_t q_tiles;    // query tiles per sequence the grid provides
+    int32_t seq_major;  // grid order
     int32_t num_heads;
     int32_t group;
     int32_t cache_prefill;
@@ -229,20 +236,48 @@ __host__ __device__ constexpr uint32_t instr_desc_f16(int n, bool b_mn_major) {
            (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kBlockM >> 4) << 24);
 }
 
-// Bounded wait that also gives up as soon as another thread of the CTA has given up.
-__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                              uint32_t* status, uint32_t code) {
-    for (uint32_t i = 0; i < kMaxWaitPolls; ++i) {
-        if (mbar_try_wait(bar, parity)) {
-            return true;
+// Non-blocking test of an mbarrier phase.  The waits below poll with it: the blocking form
+// (mbarrier.try_wait) parks the thread, and a parked thread was measured to resume a few hundred cycles
+// after the phase had completed, which is as long as some of the pipeline stages here.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait that also gives up as soon as another thread of the CTA has given up.  The common case,
+// a phase that has completed already, costs one test; the polling loop is kept out of line.
+__device__ __noinline__ bool wait_or_abort_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                uint32_t* status, uint32_t code) {
+    for (uint32_t i = 0; i < kMaxWaitPolls; i += 4) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if (PPLB200_PREFILL_WAIT(bar, parity)) {
+                return true;
+            }
         }
-        if ((i & 255u) == 255u && *abort_flag) {
+        if ((i & 255u) == 252u && *abort_flag) {
             return false;
         }
     }
     *abort_flag = 1;
     atomicOr(status, code);
     return false;
+}
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                              uint32_t* status, uint32_t code) {
+    if (PPLB200_PREFILL_WAIT(bar, parity)) {
+        return true;
+    }
+    return wait_or_abort_slow(bar, parity, abort_flag, status, code);
 }
 
 template <int DH>
@@ -263,18 +298,35 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int lane = threadIdx.x & 31;
 
     // ---- which tile ----
-    const int pb = blockIdx.y;
+    // Two grid orders, both with the heads of one query tile adjacent (they share K/V in L2):
+    //   tile-major      blockIdx.x = (qt_rev * prefill_batches + pb) * num_heads + head: the latest (longest)
+    //                   query tile of every sequence first, then the ones before them; best balance
+    //   sequence-major  blockIdx.x = (pb * q_tiles + qt_rev) * num_heads + head: the CTAs in flight work on
+    //                   one or two sequences, whose K/V then stay in L2
+    int qt_rev, pb, head;
+    if (a.seq_major) {
+        const int per_seq = a.q_tiles * a.num_heads;
+        pb = blockIdx.x / per_seq;
+        const int rem = blockIdx.x - pb * per_seq;
+        qt_rev = rem / a.num_heads;
+        head = rem - qt_rev * a.num_heads;
+    } else {
+        const int per_rev = a.prefill_batches * a.num_heads;
+        qt_rev = blockIdx.x / per_rev;
+        const int rem = blockIdx.x - qt_rev * per_rev;
+        pb = rem / a.num_heads;
+        head = rem - pb * a.num_heads;
+    }
     const int b = a.decoding_batches + pb;
     const int64_t seq0 = a.seqstarts[b];
     int64_t seqlen = a.seqstarts[b + 1] - seq0;
     if (seqlen > a.max_seqlen) {
         seqlen = a.max_seqlen;
-        if (threadIdx.x == 0 && blockIdx.x == 0) {
+        if (threadIdx.x == 0 && qt_rev == 0 && head == 0) {
             atomicOr(a.status, kDevLengthClamped);
         }
     }
     const int n_qt = static_cast<int>((seqlen + kBlockM - 1) / kBlockM);
-    const int qt_rev = blockIdx.x / a.num_heads;
     if (qt_rev >= n_qt) {
         return;  // uniform for the CTA, before any barrier or TMEM allocation
     }
@@ -285,7 +337,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         return;  // uniform as well
     }
     const int qt = n_qt - 1 - qt_rev;  // longest (latest) query tiles first
-    const int head = blockIdx.x - qt_rev * a.num_heads;
     const int kvh = head / a.group;
     const int64_t i0 = static_cast<int64_t>(qt) * kBlockM;
     const int rows_valid = (seqlen - i0) < kBlockM ? static_cast<int>(seqlen - i0) : kBlockM;
@@ -769,6 +820,10 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
     a.status = status;
     a.max_seqlen = p.max_seqlen;
     a.decoding_batches = static_cast<int32_t>(p.decoding_batches);
+    a.prefill_batches = static_cast<int32_t>(plan.prefill_batches);
+    a.q_tiles = static_cast<int32_t>(plan.q_tiles_per_seq);
+    // K and V of everything this call may read against half of a 126 MB L2
+    a.seq_major = static_cast<uint64_t>(kv_rows) * p.num_kv_heads * DH * 4 > (64ull << 20) ? 1 : 0;
     a.num_heads = p.num_heads;
     a.group = p.num_heads / p.num_kv_heads;
     a.cache_prefill = p.enable_cache_prefill ? 1 : 0;
@@ -784,8 +839,11 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
         }
         attr_set = true;
     }
-    const dim3 grid(static_cast<unsigned>(plan.q_tiles_per_seq * p.num_heads),
-                    static_cast<unsigned>(plan.prefill_batches));
+    const int64_t ctas = plan.q_tiles_per_seq * plan.prefill_batches * p.num_heads;
+    if (ctas > 0x7fffffff) {
+        return PPLB200_UNSUPPORTED;
+    }
+    const dim3 grid(static_cast<unsigned>(ctas));
     {
         KernelTimer timer(PPLB200_KERNEL_PREFILL, stream);
         prefill_tcgen05_kernel<DH><<<grid, kThreads, T::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
@@ -799,9 +857,6 @@ int launch_prefill(const pplb200_attn_params& p, const CacheGeom& geom, const Pr
                    uint32_t* status_word, void* attn_output, cudaStream_t stream) {
     if (plan.prefill_batches <= 0 || plan.q_tiles_per_seq <= 0) {
         return PPLB200_SUCCESS;
-    }
-    if (plan.prefill_batches > 65535) {
-        return PPLB200_UNSUPPORTED;
     }
     if (p.head_dim == 128) {
         return launch_prefill_dh<128>(p, geom, plan, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache,
