@@ -190,7 +190,25 @@ __device__ __forceinline__ __half2 biased_bytes_to_half2(uint32_t x) {
 //   a = max|x|, s16 = fp16_rn(a / 127.0f), c = s == 0 ? 0 : clamp(rint(x / float(s16)), -127, 127)
 // IEEE division and round-half-even throughout: the file must be compiled without fast-math so
 // that codes and scales are reproducible bit for bit on any IEEE host.
+//
+// The eight divisions are not carried out one by one.  q' = x * fl(1/s) lies within 4e-5 of fl(x/s)
+// whenever |q'| <= 128, so if q' is further than that from every half-integer, rint(q') IS
+// rint(fl(x/s)); only elements that close to a rounding boundary (a few in ten thousand), and
+// anything non-finite, take the true division.  The rounding itself is the add-and-subtract of
+// 1.5 * 2^23, which is round-half-even in the default rounding mode and leaves the integer in the
+// low mantissa bits.
 // ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int quant_code_exact(float v, float s) {
+    float q = rintf(__fdiv_rn(v, s));
+    if (!(q >= -127.0f)) {
+        q = -127.0f;  // NaN as well
+    }
+    if (q > 127.0f) {
+        q = 127.0f;
+    }
+    return static_cast<int>(q);
+}
+
 __device__ __forceinline__ void quant_group8(const uint4 in, uint2& codes, __half& scale16) {
     const __half2* h2 = reinterpret_cast<const __half2*>(&in);
     float v[8];
@@ -208,20 +226,24 @@ __device__ __forceinline__ void quant_group8(const uint4 in, uint2& codes, __hal
     scale16 = __float2half_rn(__fdiv_rn(a, 127.0f));
     const float s = __half2float(scale16);
     uint32_t w[2] = {0u, 0u};
+    if (s != 0.0f) {
+        constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+        const float r = __frcp_rn(s);
+        uint32_t ub[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float q = 0.0f;
-        if (s != 0.0f) {
-            q = rintf(__fdiv_rn(v[i], s));
-            if (!(q >= -127.0f)) {
-                q = -127.0f;
-            }
-            if (q > 127.0f) {
-                q = 127.0f;
+        for (int i = 0; i < 8; ++i) {
+            const float qf = __fmul_rn(v[i], r);
+            const float u = __fadd_rn(qf, kMagic);
+            const float t = __fsub_rn(u, kMagic);  // rint(qf) for |qf| < 2^22
+            // |qf| <= 127.4 also means that no clamp is needed; false for NaN
+            const bool safe = fabsf(qf) <= 127.4f && fabsf(__fsub_rn(qf, t)) < 0.499f;
+            ub[i] = __float_as_uint(u);  // low mantissa byte = the code in two's complement
+            if (!safe) {
+                ub[i] = static_cast<uint32_t>(quant_code_exact(v[i], s));
             }
         }
-        const int c = static_cast<int>(q);
-        w[i >> 2] |= (static_cast<uint32_t>(c) & 0xffu) << (8 * (i & 3));
+        w[0] = prmt(prmt(ub[0], ub[1], 0x0040u), prmt(ub[2], ub[3], 0x0040u), 0x5410u);
+        w[1] = prmt(prmt(ub[4], ub[5], 0x0040u), prmt(ub[6], ub[7], 0x0040u), 0x5410u);
     }
     codes = make_uint2(w[0], w[1]);
 }

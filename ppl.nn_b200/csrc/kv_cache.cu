@@ -1,96 +1,162 @@
 // KeyValueCache kernels: INT8 group quantise-and-append, and the dequantising gather that produces
-// the operator's key/value outputs.  Both are pure streaming kernels (HBM-bound, a few MB per call):
-// one thread owns one quantisation group of 8 channels = one 128-bit load of halves, one 64-bit
-// store of codes and one 16-bit store of the scale, so a warp moves 512 B in and 320 B out fully
-// coalesced.
+// the operator's key/value outputs.  Both are pure streaming kernels (HBM-bound).  A warp owns 32
+// consecutive quantisation groups of ONE token, kChunks times over: a lane's group is one 128-bit load of
+// halves, one 64-bit store of codes and one 16-bit store of the scale, so each chunk moves 512 B in and
+// 320 B out fully coalesced.  The sequence that owns the token is looked up once per warp item, by all
+// lanes together, while the item's kChunks loads are in flight.
 #include "common.cuh"
 #include "launch.h"
 
 namespace pplb200 {
 
-// the segment b in [0, n) that holds x: starts[b] <= x < starts[b + 1]   (starts has n + 1
-// non-decreasing entries and starts[0] <= x < starts[n])
-__device__ __forceinline__ int64_t find_segment(const int64_t* __restrict__ starts, int64_t n, int64_t x) {
-    int64_t lo = 0, hi = n;  // answer in [lo, hi)
+// The segment b in [0, n) that holds x: starts[b] <= x < starts[b + 1] (starts has n + 1 non-decreasing
+// entries and starts[0] <= x < starts[n]); the largest such b, so empty segments are skipped.  All 32
+// lanes call it with the same arguments: each round probes 32 pivots at once, so 1024 segments take two
+// dependent loads instead of ten.
+__device__ __forceinline__ int32_t warp_find_segment(const int64_t* __restrict__ starts, int32_t n, int64_t x,
+                                                     int lane) {
+    int32_t lo = 0, hi = n;  // answer in [lo, hi)
     while (hi - lo > 1) {
-        const int64_t mid = (lo + hi) >> 1;
-        if (starts[mid] <= x) {
-            lo = mid;
-        } else {
-            hi = mid;
+        const int32_t step = (hi - lo + 31) >> 5;
+        const int64_t piv = static_cast<int64_t>(lo) + static_cast<int64_t>(lane + 1) * step;
+        const bool le = piv < hi && starts[piv] <= x;  // true for a prefix of the lanes
+        const int c = __popc(__ballot_sync(0xffffffffu, le));
+        const int64_t nlo = static_cast<int64_t>(lo) + static_cast<int64_t>(c) * step;
+        hi = nlo + step < hi ? static_cast<int32_t>(nlo + step) : hi;
+        lo = static_cast<int32_t>(nlo);
+    }
+    return lo;
+}
+
+constexpr int kChunks = 4;  // 32-group chunks per warp item: 2 KB of fp16 in flight per warp during the lookup
+
+// Work items of a warp: (token, run of kChunks chunks of 32 groups), walked without divisions in the loop.
+struct WarpItems {
+    int64_t tok;
+    int32_t chunk;
+    int64_t step_tok;
+    int32_t step_chunk;
+    int32_t chunks_per_token;
+
+    __device__ __forceinline__ WarpItems(int32_t groups_per_token) {
+        chunks_per_token = (groups_per_token + 32 * kChunks - 1) / (32 * kChunks);  // items per token
+        const int64_t warp_id = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
+        const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
+        tok = warp_id / chunks_per_token;
+        chunk = static_cast<int32_t>(warp_id - tok * chunks_per_token);
+        step_tok = warps / chunks_per_token;
+        step_chunk = static_cast<int32_t>(warps - step_tok * chunks_per_token);
+    }
+    __device__ __forceinline__ void next() {
+        tok += step_tok;
+        chunk += step_chunk;
+        if (chunk >= chunks_per_token) {
+            chunk -= chunks_per_token;
+            ++tok;
         }
     }
-    return lo;  // the largest b with starts[b] <= x, so empty segments are skipped
+};
+
+// head_dim is 64 or 128, so a head has 8 or 16 groups: shifts instead of divisions
+__device__ __forceinline__ void split_group(int32_t g, int32_t groups_per_tensor_row, int group_shift, int& kv,
+                                            int& head, int& grp) {
+    kv = g >= groups_per_tensor_row ? 1 : 0;
+    const int32_t r2 = g - kv * groups_per_tensor_row;
+    head = r2 >> group_shift;
+    grp = r2 & ((1 << group_shift) - 1);
 }
 
 __global__ void __launch_bounds__(256)
 kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict__ cur_v,
                       const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ cachestarts,
                       const int64_t* __restrict__ start_pos, int8_t* __restrict__ cache, __half* __restrict__ scale,
-                      CacheGeom geom, int64_t batch, int64_t total_tokens, int num_kv_heads, int head_dim) {
-    const int groups_per_head = head_dim >> 3;
-    const int64_t groups_per_tensor_row = static_cast<int64_t>(num_kv_heads) * groups_per_head;
-    const int64_t groups_per_token = 2 * groups_per_tensor_row;
-    const int64_t total = total_tokens * groups_per_token;
-    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
-         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t tok = idx / groups_per_token;
-        const int64_t r = idx - tok * groups_per_token;
-        const int kv = r >= groups_per_tensor_row ? 1 : 0;
-        const int64_t r2 = r - kv * groups_per_tensor_row;
-        const int head = static_cast<int>(r2 / groups_per_head);
-        const int grp = static_cast<int>(r2 - static_cast<int64_t>(head) * groups_per_head);
-
-        const __half* src = (kv ? cur_v : cur_k) + (tok * num_kv_heads + head) * head_dim + grp * 8;
-        const uint4 in = *reinterpret_cast<const uint4*>(src);
-
-        uint2 codes;
-        __half s16;
-        quant_group8(in, codes, s16);
-
-        const int64_t b = find_segment(seqstarts, batch, tok);
-        const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (tok - seqstarts[b]));
-        const int64_t off = cache_offset(geom, row, kv, head);
-        *reinterpret_cast<uint2*>(cache + off + grp * 8) = codes;
-        scale[(off >> 3) + grp] = s16;
+                      CacheGeom geom, int32_t batch, int64_t total_tokens, int num_kv_heads, int head_dim) {
+    const int lane = threadIdx.x & 31;
+    const int group_shift = head_dim == 128 ? 4 : 3;
+    const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
+    const int32_t groups_per_token = 2 * groups_per_tensor_row;
+    for (WarpItems it(groups_per_token); it.tok < total_tokens; it.next()) {
+        // the payload loads go out before the lookups, which then overlap with them
+        uint4 in[kChunks];
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+            in[c] = make_uint4(0u, 0u, 0u, 0u);
+            if (g < groups_per_token) {
+                int kv, head, grp;
+                split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
+                const __half* src = (kv ? cur_v : cur_k) + (it.tok * num_kv_heads + head) * head_dim + grp * 8;
+                in[c] = *reinterpret_cast<const uint4*>(src);
+            }
+        }
+        const int32_t b = warp_find_segment(seqstarts, batch, it.tok, lane);
+        const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (it.tok - seqstarts[b]));
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+            uint2 codes;
+            __half s16;
+            quant_group8(in[c], codes, s16);
+            if (g < groups_per_token) {
+                int kv, head, grp;
+                split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
+                const int64_t off = cache_offset(geom, row, kv, head);
+                *reinterpret_cast<uint2*>(cache + off + grp * 8) = codes;
+                scale[(off >> 3) + grp] = s16;
+            }
+        }
     }
 }
 
 __global__ void __launch_bounds__(256)
 kv_gather_dequant_kernel(const int64_t* __restrict__ kvstarts, const int64_t* __restrict__ cachestarts,
                          const int8_t* __restrict__ cache, const __half* __restrict__ scale,
-                         __half* __restrict__ key_out, __half* __restrict__ value_out, CacheGeom geom, int64_t batch,
+                         __half* __restrict__ key_out, __half* __restrict__ value_out, CacheGeom geom, int32_t batch,
                          int64_t total_kv, int num_kv_heads, int head_dim) {
-    const int groups_per_head = head_dim >> 3;
-    const int64_t groups_per_tensor_row = static_cast<int64_t>(num_kv_heads) * groups_per_head;
-    const int64_t groups_per_token = 2 * groups_per_tensor_row;
-    const int64_t total = total_kv * groups_per_token;
-    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
-         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t j = idx / groups_per_token;
-        const int64_t r = idx - j * groups_per_token;
-        const int kv = r >= groups_per_tensor_row ? 1 : 0;
-        const int64_t r2 = r - kv * groups_per_tensor_row;
-        const int head = static_cast<int>(r2 / groups_per_head);
-        const int grp = static_cast<int>(r2 - static_cast<int64_t>(head) * groups_per_head);
-
-        const int64_t b = find_segment(kvstarts, batch, j);
+    const int lane = threadIdx.x & 31;
+    const int group_shift = head_dim == 128 ? 4 : 3;
+    const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
+    const int32_t groups_per_token = 2 * groups_per_tensor_row;
+    for (WarpItems it(groups_per_token); it.tok < total_kv; it.next()) {
+        const int64_t j = it.tok;
+        const int32_t b = warp_find_segment(kvstarts, batch, j, lane);
         const int64_t row = cache_row(geom, cachestarts, b, j - kvstarts[b]);
-        const int64_t off = cache_offset(geom, row, kv, head);
-        const uint2 codes = *reinterpret_cast<const uint2*>(cache + off + grp * 8);
-        const float s = __half2float(scale[(off >> 3) + grp]);
-
-        uint4 out;
-        __half2* o2 = reinterpret_cast<__half2*>(&out);
-        const uint32_t w[2] = {codes.x, codes.y};
+        uint2 codes[kChunks];
+        uint16_t sbits[kChunks];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int c0 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1))) & 0xffu);
-            const int c1 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1) + 8)) & 0xffu);
-            o2[i] = __floats2half2_rn(static_cast<float>(c0) * s, static_cast<float>(c1) * s);
+        for (int c = 0; c < kChunks; ++c) {
+            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+            codes[c] = make_uint2(0u, 0u);
+            sbits[c] = 0;
+            if (g < groups_per_token) {
+                int kv, head, grp;
+                split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
+                const int64_t off = cache_offset(geom, row, kv, head);
+                codes[c] = *reinterpret_cast<const uint2*>(cache + off + grp * 8);
+                sbits[c] = reinterpret_cast<const uint16_t*>(scale)[(off >> 3) + grp];
+            }
         }
-        __half* dst = (kv ? value_out : key_out) + (j * num_kv_heads + head) * head_dim + grp * 8;
-        *reinterpret_cast<uint4*>(dst) = out;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+            if (g >= groups_per_token) {
+                continue;
+            }
+            int kv, head, grp;
+            split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
+            const float sf = __half2float(__ushort_as_half(sbits[c]));
+            uint4 out;
+            __half2* o2 = reinterpret_cast<__half2*>(&out);
+            const uint32_t w[2] = {codes[c].x, codes[c].y};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int c0 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1))) & 0xffu);
+                const int c1 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1) + 8)) & 0xffu);
+                o2[i] = __floats2half2_rn(static_cast<float>(c0) * sf, static_cast<float>(c1) * sf);
+            }
+            __half* dst = (kv ? value_out : key_out) + (j * num_kv_heads + head) * head_dim + grp * 8;
+            *reinterpret_cast<uint4*>(dst) = out;
+        }
     }
 }
 
@@ -109,12 +175,13 @@ int launch_kv_append(const pplb200_attn_params& p, const CacheGeom& geom, const 
     if (p.total_tokens <= 0) {
         return PPLB200_SUCCESS;
     }
-    const int64_t work = p.total_tokens * 2 * p.num_kv_heads * (p.head_dim / 8);
-    const int grid = grid_for(work, 256, sm_count);
+    const int64_t items_per_token = (2 * p.num_kv_heads * (p.head_dim / 8) + 32 * kChunks - 1) / (32 * kChunks);
+    const int grid = grid_for(p.total_tokens * items_per_token * 32, 256, sm_count);  // a warp per item
     KernelTimer timer(PPLB200_KERNEL_APPEND, stream);
     kv_append_i8g8_kernel<<<grid, 256, 0, stream>>>(
         static_cast<const __half*>(cur_k), static_cast<const __half*>(cur_v), seqstarts, cachestarts, start_pos,
-        static_cast<int8_t*>(cache), static_cast<__half*>(scale), geom, p.batch, p.total_tokens, p.num_kv_heads,
+        static_cast<int8_t*>(cache), static_cast<__half*>(scale), geom, static_cast<int32_t>(p.batch), p.total_tokens,
+        p.num_kv_heads,
         p.head_dim);
     return check_launch("kv_append_i8g8_kernel");
 }
@@ -125,11 +192,12 @@ int launch_kv_gather_dequant(const pplb200_attn_params& p, const CacheGeom& geom
     if (total_kv <= 0) {
         return PPLB200_SUCCESS;
     }
-    const int64_t work = total_kv * 2 * p.num_kv_heads * (p.head_dim / 8);
-    const int grid = grid_for(work, 256, sm_count);
+    const int64_t items_per_token = (2 * p.num_kv_heads * (p.head_dim / 8) + 32 * kChunks - 1) / (32 * kChunks);
+    const int grid = grid_for(total_kv * items_per_token * 32, 256, sm_count);  // a warp per item
     kv_gather_dequant_kernel<<<grid, 256, 0, stream>>>(
         kvstarts, cachestarts, static_cast<const int8_t*>(cache), static_cast<const __half*>(scale),
-        static_cast<__half*>(key_out), static_cast<__half*>(value_out), geom, p.batch, total_kv, p.num_kv_heads,
+        static_cast<__half*>(key_out), static_cast<__half*>(value_out), geom, static_cast<int32_t>(p.batch), total_kv,
+        p.num_kv_heads,
         p.head_dim);
     return check_launch("kv_gather_dequant_kernel");
 }
