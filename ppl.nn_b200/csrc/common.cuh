@@ -98,6 +98,16 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
+// Programmatic dependent launch (see launch_dependent in launch.h).  wait: everything the preceding grids
+// of the stream wrote is visible after it (a no-op for a grid launched the ordinary way).
+// launch_dependents: the next grid of the stream may be scheduled from here on.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

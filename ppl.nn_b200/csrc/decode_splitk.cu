@@ -198,6 +198,8 @@ decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restr
     __shared__ typename Scan::TempStorage tmp;
     __shared__ int32_t carry;
     __shared__ int32_t longest;
+    grid_launch_dependents();
+    grid_dependency_wait();  // the workspace may still be read by the previous call's kernels
     if (threadIdx.x == 0) {
         carry = 0;
         longest = 1;
@@ -310,7 +312,9 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
         mbar_fence_init();
         tma_prefetch_desc(&tmap_codes);
     }
+    grid_launch_dependents();
     __syncthreads();
+    grid_dependency_wait();  // from here on: the plan, and the cache rows the append kernel wrote
 
     // shared-space addresses of this warp's stage ring (1 KB aligned for the 128-byte swizzle) and barriers
     const uint32_t wsm = ((smem_u32(smem_raw) + 1023u) & ~1023u) + warp * T::kWarpBytes;
@@ -729,6 +733,8 @@ decode_reduce_kernel(const PlanHeader* __restrict__ hdr, const int32_t* __restri
                      const float* __restrict__ part_ml, const float* __restrict__ part_o,
                      const int64_t* __restrict__ seqstarts, __half* __restrict__ out, int32_t decoding_batches,
                      int32_t num_heads, int32_t group, int32_t octets, int32_t head_lanes, int32_t class_heads) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     if (hdr->per_segment) {
         return;  // split-k off: every segment was written whole
     }
@@ -866,7 +872,8 @@ static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t
     }
     {
         KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
-        decode_splitk_kernel<DH, ORDER><<<static_cast<unsigned>(grid), kThreads, T::kSmemBytes, stream>>>(tm_codes, a);
+        launch_dependent(decode_splitk_kernel<DH, ORDER>, dim3(static_cast<unsigned>(grid)), dim3(kThreads),
+                         T::kSmemBytes, stream, tm_codes, a);
     }
     return check_launch("decode_splitk_kernel");
 }
@@ -888,10 +895,10 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
         return rc;
     }
 
-    decode_plan_kernel<<<1, kPlanThreads, 0, stream>>>(seqstarts, start_pos, static_cast<int32_t>(p.decoding_batches),
-                                                       static_cast<int32_t>(plan.class_heads), p.max_kvlen,
-                                                       p.split_k_mode, static_cast<int32_t>(plan.workers),
-                                                       static_cast<int32_t>(plan.max_ranges), hdr, tile_prefix);
+    launch_dependent(decode_plan_kernel, dim3(1), dim3(kPlanThreads), 0, stream, seqstarts, start_pos,
+                     static_cast<int32_t>(p.decoding_batches), static_cast<int32_t>(plan.class_heads), p.max_kvlen,
+                     p.split_k_mode, static_cast<int32_t>(plan.workers), static_cast<int32_t>(plan.max_ranges), hdr,
+                     tile_prefix);
     rc = check_launch("decode_plan_kernel");
     if (rc != PPLB200_SUCCESS) {
         return rc;
@@ -938,9 +945,10 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     if (p.split_k_mode != 0) {
         const int64_t warps = p.decoding_batches * p.num_heads;
         const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
-        decode_reduce_kernel<DH><<<blocks, 256, 0, stream>>>(hdr, tile_prefix, a.part_ml, a.part_o, seqstarts, a.out,
-                                                             a.decoding_batches, p.num_heads, a.group, a.octets,
-                                                             a.head_lanes, a.class_heads);
+        launch_dependent(decode_reduce_kernel<DH>, dim3(blocks), dim3(256), 0, stream,
+                         static_cast<const PlanHeader*>(hdr), static_cast<const int32_t*>(tile_prefix),
+                         static_cast<const float*>(a.part_ml), static_cast<const float*>(a.part_o), seqstarts, a.out,
+                         a.decoding_batches, p.num_heads, a.group, a.octets, a.head_lanes, a.class_heads);
         rc = check_launch("decode_reduce_kernel");
     }
     return rc;

@@ -71,6 +71,8 @@ kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict
                       const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ cachestarts,
                       const int64_t* __restrict__ start_pos, int8_t* __restrict__ cache, __half* __restrict__ scale,
                       CacheGeom geom, int32_t batch, int64_t total_tokens, int num_kv_heads, int head_dim) {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const int group_shift = head_dim == 128 ? 4 : 3;
     const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
@@ -178,11 +180,10 @@ int launch_kv_append(const pplb200_attn_params& p, const CacheGeom& geom, const 
     const int64_t items_per_token = (2 * p.num_kv_heads * (p.head_dim / 8) + 32 * kChunks - 1) / (32 * kChunks);
     const int grid = grid_for(p.total_tokens * items_per_token * 32, 256, sm_count);  // a warp per item
     KernelTimer timer(PPLB200_KERNEL_APPEND, stream);
-    kv_append_i8g8_kernel<<<grid, 256, 0, stream>>>(
-        static_cast<const __half*>(cur_k), static_cast<const __half*>(cur_v), seqstarts, cachestarts, start_pos,
-        static_cast<int8_t*>(cache), static_cast<__half*>(scale), geom, static_cast<int32_t>(p.batch), p.total_tokens,
-        p.num_kv_heads,
-        p.head_dim);
+    launch_dependent(kv_append_i8g8_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const __half*>(cur_k),
+                     static_cast<const __half*>(cur_v), seqstarts, cachestarts, start_pos, static_cast<int8_t*>(cache),
+                     static_cast<__half*>(scale), geom, static_cast<int32_t>(p.batch), p.total_tokens, p.num_kv_heads,
+                     p.head_dim);
     return check_launch("kv_append_i8g8_kernel");
 }
 

@@ -28,6 +28,29 @@ private:
     cudaEvent_t stop_;
 };
 
+// Launch with programmatic stream serialisation: the grid may be scheduled while its predecessor in the
+// stream drains, and runs its prologue there; every kernel launched this way executes
+// grid_dependency_wait() (common.cuh) before it touches anything a predecessor wrote, which waits for the
+// predecessor's completion and memory flush.  Saves the launch gap between the short kernels of a step.
+#ifndef PPLB200_PDL
+#define PPLB200_PDL 1
+#endif
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = PPLB200_PDL;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // Properties of the current device, cached per device id.
 struct DeviceInfo {
     int device_id;
