@@ -167,6 +167,39 @@ int pplb200_mhca_forward_noalloc(const pplb200_attn_params* p, const void* query
 uint64_t pplb200_static_scratch_bytes(void);
 
 /*
+ * MultiHeadAttention without a cache (opmx.dynamic_batching.MultiHeadAttention).  Replaces
+ * ppl::kernel::llm::cuda::pmx::dynamic_batching_multi_head_attention as called from
+ * src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/multi_head_attention_kernel.cc:96-121
+ * (attributes: src/ppl/nn/params/opmx/multi_head_attention_param.h).
+ *   query [total_tokens, num_heads, head_dim], key/value [total_kv_tokens, num_kv_heads, head_dim], fp16;
+ *   sequence b owns query rows [seqstarts[b], seqstarts[b+1]) and kv rows [kvstarts[b], kvstarts[b+1]).
+ *   is_causal: query row i of a sequence sees kv positions <= (kvlen - seqlen) + i, i.e. the mask is
+ *   aligned to the end of the kv range; a row that sees nothing yields zeros.  Scores are scaled by
+ *   1/sqrt(head_dim).  `decoding_batches` is accepted for symmetry with the cached operator and not used.
+ * The attn_mask input and is_alibi of the reference operator are not supported; the host-side
+ * operator rejects them.  `workspace`: at least pplb200_mha_workspace_size() bytes of device memory
+ * (it only holds the device status word, readable with pplb200_mhca_device_status).
+ */
+typedef struct pplb200_mha_params {
+    int32_t num_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim; /* 64 or 128 */
+    int32_t is_causal;
+    int64_t batch;
+    int64_t decoding_batches;
+    int64_t max_seqlen;
+    int64_t max_kvlen;
+    int64_t total_tokens;    /* = seqstarts[batch] */
+    int64_t total_kv_tokens; /* = kvstarts[batch] */
+} pplb200_mha_params;
+
+int pplb200_mha_workspace_size(const pplb200_mha_params* p, uint64_t* bytes);
+
+int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const void* key, const void* value,
+                        const int64_t* seqstarts, const int64_t* kvstarts, void* workspace, uint64_t workspace_bytes,
+                        void* attn_output, void* stream);
+
+/*
  * Reads the device-side status word that the kernels of the last pplb200_mhca_forward on this
  * workspace left behind (0 = clean; non-zero = a bounded wait gave up, see PPLB200_DEV_*).
  * Synchronises `stream`.  Has no counterpart in the reference; it exists because every wait

@@ -367,6 +367,69 @@ int orc_mhca(const orc_desc* d, const uint16_t* query, const uint16_t* cur_k, co
                          d->batch);
 }
 
+/* MultiHeadAttention without a cache (contract: src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/
+ * multi_head_attention_kernel.cc:24-128; the arithmetic is not in the reference tree).  Sequence b owns query
+ * rows [seqstarts[b], seqstarts[b+1]) and key/value rows [kvstarts[b], kvstarts[b+1]) of tensors shaped
+ * [rows, heads, head_dim].  With is_causal, query row i sees kv positions <= (kvlen - seqlen) + i (the mask
+ * is aligned to the end of the kv range; a choice of this repository); a row that sees nothing gives zeros.
+ * Only num_heads, num_kv_heads, head_dim, is_causal and batch of the descriptor are read. */
+int orc_mha(const orc_desc* d, const uint16_t* query, const uint16_t* key, const uint16_t* value,
+            const int64_t* seqstarts, const int64_t* kvstarts, uint16_t* out) {
+    const int64_t Dh = d->head_dim, Hq = d->num_heads, Hkv = d->num_kv_heads;
+    if (Hkv <= 0 || Hq % Hkv != 0) {
+        return 1;
+    }
+    const int group = (int)(Hq / Hkv);
+    int64_t max_kv = 0;
+    for (int64_t b = 0; b < d->batch; ++b) {
+        const int64_t n = kvstarts[b + 1] - kvstarts[b];
+        if (n > max_kv) {
+            max_kv = n;
+        }
+    }
+    int failed = 0;
+#pragma omp parallel
+    {
+        float* scores = (float*)malloc(sizeof(float) * (size_t)(max_kv > 0 ? max_kv : 1));
+        float* krow = (float*)malloc(sizeof(float) * (size_t)Dh);
+        float* qf = (float*)malloc(sizeof(float) * (size_t)Dh);
+        if (!scores || !krow || !qf) {
+#pragma omp atomic write
+            failed = 1;
+        } else {
+            for (int64_t b = 0; b < d->batch; ++b) {
+                const int64_t seqlen = seqstarts[b + 1] - seqstarts[b];
+                const int64_t kvlen = kvstarts[b + 1] - kvstarts[b];
+                const int64_t work = seqlen * Hq;
+#pragma omp for schedule(dynamic, 1) nowait
+                for (int64_t w = 0; w < work; ++w) {
+                    const int64_t i = w / Hq;
+                    const int h = (int)(w % Hq);
+                    const int64_t tok = seqstarts[b] + i;
+                    uint16_t* o = out + (tok * Hq + h) * Dh;
+                    int64_t n_kv = d->is_causal ? (kvlen - seqlen) + i + 1 : kvlen;
+                    n_kv = n_kv > kvlen ? kvlen : n_kv;
+                    if (n_kv <= 0) {
+                        for (int64_t e = 0; e < Dh; ++e) {
+                            o[e] = 0;
+                        }
+                        continue;
+                    }
+                    const uint16_t* q16 = query + (tok * Hq + h) * Dh;
+                    for (int64_t e = 0; e < Dh; ++e) {
+                        qf[e] = orc_half_to_float(q16[e]);
+                    }
+                    attend_one(d, qf, n_kv, 1, b, h / group, NULL, NULL, NULL, key, value, kvstarts[b], scores, krow, o);
+                }
+            }
+        }
+        free(scores);
+        free(krow);
+        free(qf);
+    }
+    return failed;
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -78,6 +78,8 @@ class COracle:
         L.orc_attention.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 9 + [ctypes.c_int64, ctypes.c_int64]
         L.orc_mhca.restype = ctypes.c_int
         L.orc_mhca.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 9
+        L.orc_mha.restype = ctypes.c_int
+        L.orc_mha.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 6
         L.orc_num_threads.restype = ctypes.c_int
 
     # -- scalar helpers ---------------------------------------------------------------
@@ -152,6 +154,15 @@ class COracle:
             raise RuntimeError(f"orc_mhca failed: {rc}")
         return out
 
+    def mha(self, d, query, key, value, seqstarts, kvstarts):
+        """The un-cached operator: attention over the call's own key/value tensors."""
+        out = np.zeros(query.shape, dtype=np.float16)
+        rc = self.lib.orc_mha(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts), _ptr(kvstarts),
+                              _ptr(out))
+        if rc != 0:
+            raise RuntimeError(f"orc_mha failed: {rc}")
+        return out
+
 
 # ------------------------------------------------------------------ numpy twin ---------
 
@@ -181,3 +192,22 @@ def np_attention_one(q: np.ndarray, k: np.ndarray, v: np.ndarray) -> np.ndarray:
     s = (k @ q) * np.float32(1.0 / np.sqrt(np.float32(q.shape[0])))
     p = np.exp(s - s.max())
     return (p @ v) / p.sum()
+
+
+def np_mha(query, key, value, seqstarts, kvstarts, num_kv_heads: int, is_causal: bool) -> np.ndarray:
+    """numpy twin of orc_mha (float32 inside, fp16 result): causal masks aligned to the end of the kv range."""
+    T, Hq, Dh = query.shape
+    group = Hq // num_kv_heads
+    out = np.zeros((T, Hq, Dh), dtype=np.float16)
+    q32, k32, v32 = (np.asarray(x, dtype=np.float32) for x in (query, key, value))
+    for b in range(len(seqstarts) - 1):
+        s0, s1, k0, k1 = int(seqstarts[b]), int(seqstarts[b + 1]), int(kvstarts[b]), int(kvstarts[b + 1])
+        seqlen, kvlen = s1 - s0, k1 - k0
+        for i in range(seqlen):
+            n = min(kvlen, (kvlen - seqlen) + i + 1) if is_causal else kvlen
+            if n <= 0:
+                continue
+            for h in range(Hq):
+                kvh = h // group
+                out[s0 + i, h] = np_attention_one(q32[s0 + i, h], k32[k0:k0 + n, kvh], v32[k0:k0 + n, kvh]).astype(np.float16)
+    return out

@@ -42,6 +42,8 @@ EXPORTS = (
     "pplb200_mhca_forward_noalloc",
     "pplb200_static_scratch_bytes",
     "pplb200_mhca_device_status",
+    "pplb200_mha_workspace_size",
+    "pplb200_mha_forward",
     "pplb200_status_str",
     "pplb200_device_ready",
     "pplb200_launch_count",
@@ -73,6 +75,17 @@ class AttnParams(ctypes.Structure):
         other = AttnParams()
         ctypes.memmove(ctypes.byref(other), ctypes.byref(self), ctypes.sizeof(self))
         return other
+
+
+class MhaParams(ctypes.Structure):
+    """Mirror of ``pplb200_mha_params``."""
+
+    _fields_ = [
+        ("num_heads", ctypes.c_int32), ("num_kv_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("is_causal", ctypes.c_int32),
+        ("batch", ctypes.c_int64), ("decoding_batches", ctypes.c_int64), ("max_seqlen", ctypes.c_int64),
+        ("max_kvlen", ctypes.c_int64), ("total_tokens", ctypes.c_int64), ("total_kv_tokens", ctypes.c_int64),
+    ]
 
 
 class StatusError(RuntimeError):
@@ -112,6 +125,11 @@ class Library:
         d.pplb200_static_scratch_bytes.argtypes = []
         d.pplb200_mhca_device_status.restype = ctypes.c_int
         d.pplb200_mhca_device_status.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_uint32)]
+        mp = ctypes.POINTER(MhaParams)
+        d.pplb200_mha_workspace_size.restype = ctypes.c_int
+        d.pplb200_mha_workspace_size.argtypes = [mp, ctypes.POINTER(ctypes.c_uint64)]
+        d.pplb200_mha_forward.restype = ctypes.c_int
+        d.pplb200_mha_forward.argtypes = [mp, vp, vp, vp, i64p, i64p, vp, ctypes.c_uint64, vp, vp]
         d.pplb200_status_str.restype = ctypes.c_char_p
         d.pplb200_status_str.argtypes = [ctypes.c_int]
         d.pplb200_device_ready.restype = ctypes.c_int
@@ -174,6 +192,15 @@ class Library:
         """Same as mhca_forward but with the library's built-in scratch: no workspace, no allocation."""
         return self.dll.pplb200_mhca_forward_noalloc(ctypes.byref(p), q, cur_k, cur_v, seqstarts, kvstarts,
                                                      cachestarts, start_pos, cache, scale, out, stream)
+
+    def mha_workspace_size(self, p) -> tuple[int, int]:
+        n = ctypes.c_uint64(0)
+        rc = self.dll.pplb200_mha_workspace_size(ctypes.byref(p), ctypes.byref(n))
+        return rc, int(n.value)
+
+    def mha_forward(self, p, q, k, v, seqstarts, kvstarts, workspace, workspace_bytes, out, stream) -> int:
+        return self.dll.pplb200_mha_forward(ctypes.byref(p), q, k, v, seqstarts, kvstarts, workspace,
+                                            int(workspace_bytes), out, stream)
 
     def static_scratch_bytes(self) -> int:
         return int(self.dll.pplb200_static_scratch_bytes())

@@ -364,6 +364,61 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     return PPLB200_SUCCESS;
 }
 
+int pplb200_mha_workspace_size(const pplb200_mha_params* p, uint64_t* bytes) {
+    if (!p || !bytes) {
+        return fail(PPLB200_NOT_FOUND, "null argument");
+    }
+    *bytes = 256;  // the device status word
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const void* key, const void* value,
+                        const int64_t* seqstarts, const int64_t* kvstarts, void* workspace, uint64_t workspace_bytes,
+                        void* attn_output, void* stream_v) {
+    if (!p) {
+        return fail(PPLB200_NOT_FOUND, "params is null");
+    }
+    if (p->head_dim != 64 && p->head_dim != 128) {
+        return fail(PPLB200_UNSUPPORTED, "head_dim must be 64 or 128");
+    }
+    if (p->num_heads <= 0 || p->num_kv_heads <= 0 || p->num_heads % p->num_kv_heads != 0) {
+        return fail(PPLB200_INVALID_VALUE, "num_heads must be a positive multiple of num_kv_heads");
+    }
+    if (p->batch < 0 || p->max_seqlen < 0 || p->max_kvlen < 0 || p->total_tokens < 0 || p->total_kv_tokens < 0 ||
+        p->decoding_batches < 0 || p->decoding_batches > p->batch) {
+        return fail(PPLB200_INVALID_VALUE, "negative size or decoding_batches > batch");
+    }
+    if (p->total_tokens > 0x7fffffff || p->total_kv_tokens > 0x7fffffff) {
+        return fail(PPLB200_UNSUPPORTED, "more than 2^31 rows");
+    }
+    if (!query || !key || !value || !seqstarts || !kvstarts || !attn_output) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    if (p->batch == 0 || p->total_tokens == 0) {
+        return PPLB200_SUCCESS;
+    }
+    DeviceInfo di;
+    int rc = require_device(&di);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!workspace) {
+        return fail(PPLB200_NOT_FOUND, "workspace is null");
+    }
+    if (workspace_bytes < 256) {
+        return fail(PPLB200_OUT_OF_MEMORY, "workspace is smaller than pplb200_mha_workspace_size()");
+    }
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+    uint32_t* status = static_cast<uint32_t*>(workspace);
+    if (cudaMemsetAsync(status, 0, 4, stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(PPLB200_DEVICE_RUNTIME_ERROR, "cudaMemsetAsync(status) failed");
+    }
+    return launch_mha(p->num_heads, p->num_kv_heads, p->head_dim, p->is_causal, p->batch, p->max_seqlen, p->max_kvlen,
+                      p->total_tokens, p->total_kv_tokens, query, key, value, seqstarts, kvstarts, status, attn_output,
+                      stream);
+}
+
 int pplb200_mhca_device_status(const void* workspace, void* stream, uint32_t* status) {
     if (!workspace || !status) {
         return PPLB200_NOT_FOUND;

@@ -104,4 +104,10 @@ int launch_prefill(const pplb200_attn_params& p, const CacheGeom& geom, const Pr
                    const int64_t* start_pos, const void* cache, const void* scale, void* workspace_region,
                    uint32_t* status_word, void* attn_output, cudaStream_t stream);
 
+// The un-cached attention operator through the prefill kernel (K/V from their own tensors).
+int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int64_t batch, int64_t max_seqlen,
+               int64_t max_kvlen, int64_t total_q, int64_t total_kv, const void* query, const void* key,
+               const void* value, const int64_t* seqstarts, const int64_t* kvstarts, uint32_t* status_word,
+               void* attn_output, cudaStream_t stream);
+
 }  // namespace pplb200

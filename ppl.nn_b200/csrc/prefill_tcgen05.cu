@@ -68,7 +68,8 @@ struct PrefillArgs {
     __half* out;
     const int64_t* seqstarts;
     const int64_t* start_pos;
-    const int64_t* stage_starts;  // cache prefill: first staging row of each prefill sequence
+    const int64_t* stage_starts;  // kv_mode 1: first staging row of each prefill sequence
+    const int64_t* kvstarts;      // kv_mode 2: first K/V row of each sequence (a tensor of its own)
     uint32_t* status;
     int64_t max_seqlen;
     int32_t decoding_batches;
@@ -77,7 +78,9 @@ struct PrefillArgs {
     int32_t seq_major;  // grid order
     int32_t num_heads;
     int32_t group;
-    int32_t cache_prefill;
+    int32_t kv_mode;    // 0: K/V are this call's rows (same indexing as Q); 1: staged cache rows; 2: own K/V tensor
+    int32_t is_causal;  // query row i sees kv positions <= (kvlen - seqlen) + i; otherwise all of them
+    int64_t max_kvlen;
     float scale_log2;
 };
 
@@ -340,11 +343,34 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int kvh = head / a.group;
     const int64_t i0 = static_cast<int64_t>(qt) * kBlockM;
     const int rows_valid = (seqlen - i0) < kBlockM ? static_cast<int>(seqlen - i0) : kBlockM;
-    const int64_t hist = a.cache_prefill ? a.start_pos[b] : 0;
-    const int64_t kv_visible = hist + i0 + rows_valid;  // kv positions the last valid row may see
-    const int n_kv = static_cast<int>((kv_visible + kBlockN - 1) / kBlockN);
+    // kv rows of the sequence, how many there are, and how many of them precede query row 0 (hist)
+    int64_t kv_row0 = seq0, kvlen = seqlen, hist = 0;
+    if (a.kv_mode == 1) {
+        hist = a.start_pos[b];
+        kvlen = hist + seqlen;
+        kv_row0 = a.stage_starts[pb];
+    } else if (a.kv_mode == 2) {
+        kv_row0 = a.kvstarts[b];
+        kvlen = a.kvstarts[b + 1] - kv_row0;
+        kvlen = kvlen > a.max_kvlen ? a.max_kvlen : kvlen;
+        hist = kvlen - seqlen;  // causal masks are aligned to the END of the kv range
+    }
+    int64_t kv_visible = a.is_causal ? hist + i0 + rows_valid : kvlen;  // kv positions the last valid row may see
+    kv_visible = kv_visible > kvlen ? kvlen : kv_visible;
+    const int n_kv = kv_visible > 0 ? static_cast<int>((kv_visible + kBlockN - 1) / kBlockN) : 0;
     const int64_t q_row0 = seq0 + i0;
-    const int64_t kv_row0 = a.cache_prefill ? a.stage_starts[pb] : seq0;
+    if (n_kv == 0) {
+        // nothing visible to any row of the tile: zeros (uniform for the CTA, before any barrier)
+        for (int idx = threadIdx.x; idx < rows_valid * (DH / 8); idx += kThreads) {
+            const int r = idx / (DH / 8), c = idx - r * (DH / 8);
+            *reinterpret_cast<uint4*>(a.out + ((q_row0 + r) * a.num_heads + head) * DH + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        return;
+    }
+    // first kv position no row may see, and whether rows of this tile see nothing at all (causal, more
+    // query rows than kv rows)
+    const int64_t first_row_last = a.is_causal ? hist + i0 : kvlen - 1;  // last kv position visible to row 0 of the tile
+    const bool dead_rows = first_row_last < 0;
 
     // ---- setup ----
     if (threadIdx.x == 0) {
@@ -540,11 +566,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             tc_fence_before();
             mbar_arrive(&bars.s_free);
             // columns of this tile that row r may see: col <= limit.  Only tiles that reach past the first
-            // row's horizon need the mask (uniform for the CTA).  Column 0 of tile 0 is visible to every row,
-            // so m_ref is a real score from the first tile on.
+            // row's horizon or past the end of the kv range need the mask (uniform for the CTA).  Unless the
+            // tile has rows that see nothing at all (handled below), column 0 of tile 0 is visible to every
+            // row, so m_ref is a real score from the first tile on.
             const int64_t tile_hi = static_cast<int64_t>(j + 1) * kBlockN - 1;
-            if (tile_hi > hist + i0) {
-                const int64_t lim64 = hist + i0 + r - static_cast<int64_t>(j) * kBlockN;
+            if (tile_hi > first_row_last || tile_hi >= kvlen) {
+                int64_t lim64 = (a.is_causal ? first_row_last + r : kvlen - 1);
+                lim64 = lim64 > kvlen - 1 ? kvlen - 1 : lim64;
+                lim64 -= static_cast<int64_t>(j) * kBlockN;
                 const int limit = lim64 > kBlockN ? kBlockN : (lim64 < -1 ? -1 : static_cast<int>(lim64));
 #pragma unroll
                 for (int e = 0; e < kBlockN; ++e) {
@@ -595,7 +624,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 tc_fence_after();
             }
             // P = exp2(s * scale - m_ref) as packed fp16 into TMEM: column c of the buffer = kv columns 2c, 2c+1
-            const float neg_m = -m_ref;
+            // a row that sees no kv position at all gets zero weights (exp2(-inf)), hence a zero output row
+            const float neg_m = (dead_rows && first_row_last + r < 0) ? -INFINITY : -m_ref;
             const uint32_t t_pb = t_p + (j & 1) * T::kPCols;
 #pragma unroll
             for (int q = 0; q < kBlockN / 32; ++q) {
@@ -747,12 +777,68 @@ int make_prefill_plan(const pplb200_attn_params& p, PrefillPlan* plan) {
     return PPLB200_SUCCESS;
 }
 
+// Tensor maps + launch for one configuration of the kernel: Q rows [q_rows, Hq, Dh], K/V rows [kv_rows, Hkv, Dh].
+template <int DH>
+static int launch_attention_core(const void* query, const void* k_src, const void* v_src, int64_t q_rows, int64_t kv_rows,
+                                 int num_heads, int num_kv_heads, int64_t q_tiles_per_seq, PrefillArgs a,
+                                 cudaStream_t stream) {
+    using T = PTraits<DH>;
+    // tensor maps: {Dh, heads, rows} with a box of one head's [tile rows][64 halves], 128-byte swizzle
+    CUtensorMap tm_q, tm_k, tm_v;
+    const uint64_t dq[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(num_heads), static_cast<uint64_t>(q_rows)};
+    const uint64_t sq[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(num_heads) * DH * 2};
+    const uint32_t box[3] = {64, 1, kBlockM};
+    const uint32_t box_kv[3] = {64, 1, kBlockN};
+    int rc = encode_tensor_map(&tm_q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, query, dq, sq, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    const uint64_t dk[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(num_kv_heads),
+                            static_cast<uint64_t>(kv_rows)};
+    const uint64_t sk[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(num_kv_heads) * DH * 2};
+    rc = encode_tensor_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, k_src, dk, sk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    rc = encode_tensor_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, v_src, dk, sk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+
+    a.q_tiles = static_cast<int32_t>(q_tiles_per_seq);
+    // K and V of everything this call may read against half of a 126 MB L2
+    a.seq_major = static_cast<uint64_t>(kv_rows) * num_kv_heads * DH * 4 > (64ull << 20) ? 1 : 0;
+    a.num_heads = num_heads;
+    a.group = num_heads / num_kv_heads;
+    a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
+
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             T::kSmemBytes);
+        if (e != cudaSuccess) {
+            fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(prefill_tcgen05_kernel): %s\n", cudaGetErrorString(e));
+            return PPLB200_DEVICE_RUNTIME_ERROR;
+        }
+        attr_set = true;
+    }
+    const int64_t ctas = q_tiles_per_seq * a.prefill_batches * num_heads;
+    if (ctas > 0x7fffffff) {
+        return PPLB200_UNSUPPORTED;
+    }
+    const dim3 grid(static_cast<unsigned>(ctas));
+    {
+        KernelTimer timer(PPLB200_KERNEL_PREFILL, stream);
+        prefill_tcgen05_kernel<DH><<<grid, kThreads, T::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+    }
+    return check_launch("prefill_tcgen05_kernel");
+}
+
 template <int DH>
 static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan,
                              const void* query, const void* cur_k, const void* cur_v, const int64_t* seqstarts,
                              const int64_t* cachestarts, const int64_t* start_pos, const void* cache, const void* scale,
                              void* region, uint32_t* status, void* attn_output, cudaStream_t stream) {
-    using T = PTraits<DH>;
     const void* k_src = cur_k;
     const void* v_src = cur_v;
     int64_t kv_rows = p.total_tokens;
@@ -787,68 +873,53 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
         stage_starts = ss;
     }
 
-    // tensor maps: {Dh, heads, rows} with a box of one head's [tile rows][64 halves], 128-byte swizzle
-    CUtensorMap tm_q, tm_k, tm_v;
-    {
-        const uint64_t dq[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(p.num_heads),
-                                static_cast<uint64_t>(p.total_tokens)};
-        const uint64_t sq[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(p.num_heads) * DH * 2};
-        const uint32_t box[3] = {64, 1, kBlockM};
-        const uint32_t box_kv[3] = {64, 1, kBlockN};
-        rc = encode_tensor_map(&tm_q, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, query, dq, sq, box, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc != PPLB200_SUCCESS) {
-            return rc;
-        }
-        const uint64_t dk[3] = {static_cast<uint64_t>(DH), static_cast<uint64_t>(p.num_kv_heads),
-                                static_cast<uint64_t>(kv_rows)};
-        const uint64_t sk[2] = {static_cast<uint64_t>(DH) * 2, static_cast<uint64_t>(p.num_kv_heads) * DH * 2};
-        rc = encode_tensor_map(&tm_k, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, k_src, dk, sk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc != PPLB200_SUCCESS) {
-            return rc;
-        }
-        rc = encode_tensor_map(&tm_v, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, v_src, dk, sk, box_kv, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc != PPLB200_SUCCESS) {
-            return rc;
-        }
-    }
-
-    PrefillArgs a;
+    PrefillArgs a = {};
     a.out = static_cast<__half*>(attn_output);
     a.seqstarts = seqstarts;
     a.start_pos = start_pos;
     a.stage_starts = stage_starts;
+    a.kvstarts = nullptr;
     a.status = status;
     a.max_seqlen = p.max_seqlen;
+    a.max_kvlen = p.max_kvlen;
     a.decoding_batches = static_cast<int32_t>(p.decoding_batches);
     a.prefill_batches = static_cast<int32_t>(plan.prefill_batches);
-    a.q_tiles = static_cast<int32_t>(plan.q_tiles_per_seq);
-    // K and V of everything this call may read against half of a 126 MB L2
-    a.seq_major = static_cast<uint64_t>(kv_rows) * p.num_kv_heads * DH * 4 > (64ull << 20) ? 1 : 0;
-    a.num_heads = p.num_heads;
-    a.group = p.num_heads / p.num_kv_heads;
-    a.cache_prefill = p.enable_cache_prefill ? 1 : 0;
-    a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
+    a.kv_mode = p.enable_cache_prefill ? 1 : 0;
+    a.is_causal = 1;
+    return launch_attention_core<DH>(query, k_src, v_src, p.total_tokens, kv_rows, p.num_heads, p.num_kv_heads,
+                                     plan.q_tiles_per_seq, a, stream);
+}
 
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             T::kSmemBytes);
-        if (e != cudaSuccess) {
-            fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(prefill_tcgen05_kernel): %s\n", cudaGetErrorString(e));
-            return PPLB200_DEVICE_RUNTIME_ERROR;
-        }
-        attr_set = true;
+// The un-cached operator: every sequence of the batch through the same kernel, K/V from their own tensors.
+int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int64_t batch, int64_t max_seqlen,
+               int64_t max_kvlen, int64_t total_q, int64_t total_kv, const void* query, const void* key,
+               const void* value, const int64_t* seqstarts, const int64_t* kvstarts, uint32_t* status_word,
+               void* attn_output, cudaStream_t stream) {
+    if (batch <= 0 || max_seqlen <= 0 || total_q <= 0) {
+        return PPLB200_SUCCESS;
     }
-    const int64_t ctas = plan.q_tiles_per_seq * plan.prefill_batches * p.num_heads;
-    if (ctas > 0x7fffffff) {
-        return PPLB200_UNSUPPORTED;
+    PrefillArgs a = {};
+    a.out = static_cast<__half*>(attn_output);
+    a.seqstarts = seqstarts;
+    a.start_pos = nullptr;
+    a.stage_starts = nullptr;
+    a.kvstarts = kvstarts;
+    a.status = status_word;
+    a.max_seqlen = max_seqlen;
+    a.max_kvlen = max_kvlen;
+    a.decoding_batches = 0;
+    a.prefill_batches = static_cast<int32_t>(batch);
+    a.kv_mode = 2;
+    a.is_causal = is_causal ? 1 : 0;
+    const int64_t q_tiles = (max_seqlen + kBlockM - 1) / kBlockM;
+    const int64_t kv_rows = total_kv > 0 ? total_kv : 1;  // a tensor map needs a non-empty extent
+    if (head_dim == 128) {
+        return launch_attention_core<128>(query, key, value, total_q, kv_rows, num_heads, num_kv_heads, q_tiles, a, stream);
     }
-    const dim3 grid(static_cast<unsigned>(ctas));
-    {
-        KernelTimer timer(PPLB200_KERNEL_PREFILL, stream);
-        prefill_tcgen05_kernel<DH><<<grid, kThreads, T::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+    if (head_dim == 64) {
+        return launch_attention_core<64>(query, key, value, total_q, kv_rows, num_heads, num_kv_heads, q_tiles, a, stream);
     }
-    return check_launch("prefill_tcgen05_kernel");
+    return PPLB200_UNSUPPORTED;
 }
 
 int launch_prefill(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan, const void* query,

@@ -211,6 +211,106 @@ RetCode DynamicBatchingMultiHeadCacheAttentionKernel::DoExecute(KernelExecContex
 }
 
 // =================================================================================================
+// MultiHeadAttention (no cache)
+// =================================================================================================
+RetCode DynamicBatchingMultiHeadAttentionOp::DoInit(const OptKernelOptions& options) {
+    const RetCode rc = GenericLoadParam<ppl::nn::opmx::MultiHeadAttentionParam>(options, &param_);
+    if (rc != RC_SUCCESS) {
+        LOG(ERROR) << "GenericLoadParam failed: " << GetRetCodeStr(rc);
+        return rc;
+    }
+    infer_type_and_format_func_ = GenericInferTypeAndFormat;
+    infer_dims_func_ = GenericInferDims;  // attn_output has query's shape
+    return RC_SUCCESS;
+}
+
+KernelImpl* DynamicBatchingMultiHeadAttentionOp::CreateKernelImpl() const {
+    return CreateKernelImplWithParam<DynamicBatchingMultiHeadAttentionKernel>(param_.get());
+}
+
+RetCode DynamicBatchingMultiHeadAttentionKernel::DoExecute(KernelExecContext* ctx) {
+    // inputs by index: 0 query, 1 key, 2 value, 3 seqstarts, 4 kvstarts, 5 decoding_batches, 6 max_seqlen,
+    // 7 max_kvlen, 8 attn_mask (optional); output 0 attn_output
+    // (src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/multi_head_attention_kernel.cc:27-37)
+    static const char* const kNames[8] = {"query",    "key",        "value",     "seqstarts", "kvstarts", "decoding_batches",
+                                          "max_seqlen", "max_kvlen"};
+    Slots s(ctx);
+    TensorImpl* in[9];
+    for (uint32_t i = 0; i < 9; ++i) {
+        in[i] = s.In(i);
+        if (i < 8 && !s.Need(in[i], "Input", kNames[i])) {
+            return s.rc;
+        }
+    }
+    TensorImpl* attn_output = s.Out(0);
+    if (!s.Need(attn_output, "Output", "attn_output")) {
+        return s.rc;
+    }
+    TensorImpl *query = in[0], *key = in[1], *value = in[2], *seqstarts = in[3], *kvstarts = in[4], *attn_mask = in[8];
+
+    RetCode rc = Reshape(ctx);
+    if (rc != RC_SUCCESS) {
+        LOG(ERROR) << "Reshape kernel[" << GetName() << "] failed: " << GetRetCodeStr(rc);
+        return rc;
+    }
+    if (param_->is_alibi) {
+        LOG(ERROR) << "currently only support is_alibi == false";
+        return RC_UNSUPPORTED;
+    }
+    if (attn_mask && attn_mask->GetShape()->CalcElementsExcludingPadding() > 0) {
+        LOG(ERROR) << "attn_mask is not supported";  // an empty mask counts as absent
+        return RC_UNSUPPORTED;
+    }
+    if (query->GetShape()->GetDataType() != DATATYPE_FLOAT16) {
+        LOG(ERROR) << "currently only support fp16";
+        return RC_UNSUPPORTED;
+    }
+    for (TensorImpl* t : {query, key, value, seqstarts, kvstarts}) {
+        if ((rc = RequireOnDevice(t, GetCudaDevice())) != RC_SUCCESS) {
+            return rc;
+        }
+    }
+    if ((rc = ReallocOn(attn_output, GetCudaDevice())) != RC_SUCCESS) {
+        return rc;
+    }
+
+    int64_t decoding_batches = 0, max_seqlen = 0, max_kvlen = 0;
+    if ((rc = ReadScalar(in[5], &decoding_batches, "decoding_batches")) != RC_SUCCESS) return rc;
+    if ((rc = ReadScalar(in[6], &max_seqlen, "max_seqlen")) != RC_SUCCESS) return rc;
+    if ((rc = ReadScalar(in[7], &max_kvlen, "max_kvlen")) != RC_SUCCESS) return rc;
+
+    pplb200_mha_params p;
+    memset(&p, 0, sizeof(p));
+    p.num_heads = param_->num_heads;
+    p.num_kv_heads = param_->num_kv_heads;
+    p.head_dim = param_->head_dim;
+    p.is_causal = param_->is_causal ? 1 : 0;
+    p.batch = seqstarts->GetShape()->GetDim(0) - 1;  // here the batch does come from seqstarts
+    p.decoding_batches = decoding_batches;
+    p.max_seqlen = max_seqlen;
+    p.max_kvlen = max_kvlen;
+    p.total_tokens = query->GetShape()->GetDim(0);
+    p.total_kv_tokens = key->GetShape()->GetDim(0);
+
+    uint64_t workspace_bytes = 0;
+    if ((rc = FromStatus(pplb200_mha_workspace_size(&p, &workspace_bytes))) != RC_SUCCESS) {
+        return rc;
+    }
+    BufferDesc tmp;
+    rc = GetCudaDevice()->AllocTmpBuffer(workspace_bytes, &tmp);
+    if (rc != RC_SUCCESS) {
+        LOG(ERROR) << "alloc tmp buffer size[" << workspace_bytes << "] for kernel[" << GetName()
+                   << "] failed: " << GetRetCodeStr(rc);
+        return rc;
+    }
+    Destructor tmp_guard([this, &tmp]() { GetCudaDevice()->FreeTmpBuffer(&tmp); });
+
+    return FromStatus(pplb200_mha_forward(&p, query->GetBufferPtr(), key->GetBufferPtr(), value->GetBufferPtr(),
+                                          seqstarts->GetBufferPtr<int64_t>(), kvstarts->GetBufferPtr<int64_t>(), tmp.addr,
+                                          workspace_bytes, attn_output->GetBufferPtr(), GetStream()));
+}
+
+// =================================================================================================
 // KeyValueCache
 // =================================================================================================
 RetCode DynamicBatchingKeyValueCacheOp::DoInit(const OptKernelOptions& options) {
@@ -372,6 +472,9 @@ void RegisterB200OpImpls() {
                   CreateOp<opmx::DynamicBatchingMultiHeadCacheAttentionOp>);
     mgr->Remove(domain, "KeyValueCache");
     mgr->Register(domain, "KeyValueCache", utils::VersionRange(1, 1), CreateOp<opmx::DynamicBatchingKeyValueCacheOp>);
+    mgr->Remove(domain, "MultiHeadAttention");
+    mgr->Register(domain, "MultiHeadAttention", utils::VersionRange(1, 1),
+                  CreateOp<opmx::DynamicBatchingMultiHeadAttentionOp>);
 }
 
 }}}}  // namespace ppl::nn::llm::cuda

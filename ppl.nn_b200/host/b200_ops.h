@@ -5,6 +5,8 @@
 //       src/ppl/nn/engines/llm_cuda/{ops,kernels}/opmx/dynamic_batching/multi_head_cache_attention_*
 //   DynamicBatchingKeyValueCacheOp / ...Kernel
 //       src/ppl/nn/engines/llm_cuda/{ops,kernels}/opmx/dynamic_batching/key_value_cache_*
+//   DynamicBatchingMultiHeadAttentionOp / ...Kernel (attention over the call's own key/value, no cache)
+//       src/ppl/nn/engines/llm_cuda/{ops,kernels}/opmx/dynamic_batching/multi_head_attention_*
 #pragma once
 
 #include "llm_cuda.h"
@@ -49,6 +51,26 @@ public:
 private:
     ppl::common::RetCode DoInit(const OptKernelOptions&) override;
     std::shared_ptr<ppl::nn::opmx::KeyValueCacheParam> param_;
+};
+
+class DynamicBatchingMultiHeadAttentionKernel final : public LlmCudaKernel {
+public:
+    explicit DynamicBatchingMultiHeadAttentionKernel(const ir::Node* node) : LlmCudaKernel(node) {}
+    void SetParam(const ppl::nn::opmx::MultiHeadAttentionParam* p) { param_ = p; }
+
+private:
+    ppl::common::RetCode DoExecute(KernelExecContext*) override;
+    const ppl::nn::opmx::MultiHeadAttentionParam* param_ = nullptr;
+};
+
+class DynamicBatchingMultiHeadAttentionOp final : public LlmCudaOptKernel {
+public:
+    explicit DynamicBatchingMultiHeadAttentionOp(const ir::Node* node) : LlmCudaOptKernel(node) {}
+    KernelImpl* CreateKernelImpl() const override;
+
+private:
+    ppl::common::RetCode DoInit(const OptKernelOptions&) override;
+    std::shared_ptr<ppl::nn::opmx::MultiHeadAttentionParam> param_;
 };
 
 }}}}}  // namespace ppl::nn::llm::cuda::opmx

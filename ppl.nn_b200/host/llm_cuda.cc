@@ -65,6 +65,16 @@ RetCode ParseMultiHeadCacheAttentionParam(const AttrMap& attrs, MultiHeadCacheAt
     return RC_SUCCESS;
 }
 
+RetCode ParseMultiHeadAttentionParam(const AttrMap& attrs, MultiHeadAttentionParam* p) {
+    RetCode rc;
+    if ((rc = Required(attrs, "num_heads", &p->num_heads)) != RC_SUCCESS) return rc;
+    if ((rc = Required(attrs, "head_dim", &p->head_dim)) != RC_SUCCESS) return rc;
+    Optional(attrs, "num_kv_heads", &p->num_kv_heads, p->num_heads);
+    Optional(attrs, "is_causal", &p->is_causal, true);
+    Optional(attrs, "is_alibi", &p->is_alibi, false);
+    return RC_SUCCESS;
+}
+
 }  // namespace opmx
 
 namespace llm { namespace cuda {

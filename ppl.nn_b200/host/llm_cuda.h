@@ -6,8 +6,8 @@
 //   OptKernelCreatorManager       src/ppl/nn/engines/llm_cuda/opt_kernel_creator_manager.h:27-29,
 //                                 src/ppl/nn/utils/op_info_manager.h:30-110
 // and the two parameter structs with their ONNX attribute parsers
-//   src/ppl/nn/params/opmx/{key_value_cache,multi_head_cache_attention}_param.h
-//   src/ppl/nn/models/onnx/parsers/opmx/parse_{key_value_cache,multi_head_cache_attention}_param.cc
+//   src/ppl/nn/params/opmx/{key_value_cache,multi_head_cache_attention,multi_head_attention}_param.h
+//   src/ppl/nn/models/onnx/parsers/opmx/parse_{key_value_cache,multi_head_cache_attention,multi_head_attention}_param.cc
 #pragma once
 
 #include <cuda_runtime.h>
@@ -51,6 +51,16 @@ struct MultiHeadCacheAttentionParam final : public ir::TypedAttr<MultiHeadCacheA
     int32_t page_size = 128;
 };
 
+// src/ppl/nn/params/opmx/multi_head_attention_param.h; parser
+// src/ppl/nn/models/onnx/parsers/opmx/parse_multi_head_attention_param.cc
+struct MultiHeadAttentionParam final : public ir::TypedAttr<MultiHeadAttentionParam> {
+    int32_t num_heads = 0;
+    int32_t num_kv_heads = 0;
+    int32_t head_dim = 0;
+    bool is_causal = true;
+    bool is_alibi = false;
+};
+
 // Attributes of a node as name -> integer (all attributes of these two operators are ints).
 using AttrMap = std::map<std::string, int64_t>;
 
@@ -58,6 +68,7 @@ using AttrMap = std::map<std::string, int64_t>;
 // RC_NOT_FOUND, everything else falls back to its default.
 ppl::common::RetCode ParseKeyValueCacheParam(const AttrMap& attrs, KeyValueCacheParam* param);
 ppl::common::RetCode ParseMultiHeadCacheAttentionParam(const AttrMap& attrs, MultiHeadCacheAttentionParam* param);
+ppl::common::RetCode ParseMultiHeadAttentionParam(const AttrMap& attrs, MultiHeadAttentionParam* param);
 
 }  // namespace opmx
 
@@ -229,8 +240,8 @@ private:
     std::map<std::string, std::map<std::string, Versions>> info_;
 };
 
-// Registers this library's two operators under the names the engine serves
-// (src/ppl/nn/engines/llm_cuda/register_ops.cc:201,206), replacing whatever is registered for them.
+// Registers this library's operators under the names the engine serves
+// (src/ppl/nn/engines/llm_cuda/register_ops.cc), replacing whatever is registered for them.
 void RegisterB200OpImpls();
 
 }}  // namespace llm::cuda

@@ -51,6 +51,20 @@ class MultiHeadCacheAttentionParam:
 
 
 @dataclass
+class MultiHeadAttentionParam:
+    """src/ppl/nn/params/opmx/multi_head_attention_param.h."""
+    num_heads: int
+    head_dim: int
+    num_kv_heads: int = -1  # parser default: num_heads
+    is_causal: bool = True
+    is_alibi: bool = False
+
+    def __post_init__(self):
+        if self.num_kv_heads < 0:
+            self.num_kv_heads = self.num_heads
+
+
+@dataclass
 class EngineConfig:
     """The knobs of src/ppl/nn/engines/llm_cuda/engine_config.h:30-35 that reach this path."""
     enable_cache_prefill: bool = False
@@ -236,3 +250,43 @@ class KeyValueCache(_Base):
                     self.lib.kv_gather_dequant(p, _ptr(kvstarts), _ptr(cachestarts), _ptr(cache), _ptr(scale),
                                                total_kv, _ptr(key), _ptr(value), s))
         return key, value
+
+
+class MultiHeadAttention(_Base):
+    """opmx.dynamic_batching.MultiHeadAttention: attention over this call's own key/value tensors, no cache
+    (src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/multi_head_attention_kernel.cc:24-128)."""
+
+    def __init__(self, param: MultiHeadAttentionParam):
+        super().__init__()
+        self.param = param
+        self._workspace: torch.Tensor | None = None
+
+    def forward(self, query, key, value, seqstarts, kvstarts, decoding_batches: int, max_seqlen: int, max_kvlen: int,
+                attn_mask=None, attn_output: torch.Tensor | None = None) -> torch.Tensor:
+        a = self.param
+        _require_cuda(query=query, key=key, value=value, seqstarts=seqstarts, kvstarts=kvstarts)
+        if a.is_alibi:
+            raise OpError("RC_UNSUPPORTED", "currently only support is_alibi == false")
+        if attn_mask is not None and attn_mask.numel() > 0:
+            raise OpError("RC_UNSUPPORTED", "attn_mask is not supported")
+        p = capi.MhaParams()
+        p.num_heads, p.num_kv_heads, p.head_dim, p.is_causal = a.num_heads, a.num_kv_heads, a.head_dim, int(a.is_causal)
+        p.batch = seqstarts.shape[0] - 1
+        p.decoding_batches = int(decoding_batches)
+        p.max_seqlen, p.max_kvlen = int(max_seqlen), int(max_kvlen)
+        p.total_tokens, p.total_kv_tokens = query.shape[0], key.shape[0]
+        if attn_output is None:
+            attn_output = torch.empty_like(query)
+        if self._workspace is None or self._workspace.device != query.device:
+            self._workspace = torch.empty(256, dtype=torch.uint8, device=query.device)
+        rc = self.lib.mha_forward(p, _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts), _ptr(kvstarts),
+                                  _ptr(self._workspace), self._workspace.numel(), _ptr(attn_output), _stream())
+        self._raise("pplb200_mha_forward", rc)
+        return attn_output
+
+    def device_status(self) -> int:
+        if self._workspace is None:
+            return 0
+        rc, status = self.lib.mhca_device_status(_ptr(self._workspace), _stream())
+        self._raise("pplb200_mhca_device_status", rc)
+        return status

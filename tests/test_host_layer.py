@@ -38,11 +38,12 @@ def test_host_header_symbols_are_exported(built_lib, host):
 
 
 def test_registry_serves_the_reference_op_names(host):
-    # register_ops.cc:201,206: ("opmx.dynamic_batching", "KeyValueCache" / "MultiHeadCacheAttention", 1, 1)
+    # register_ops.cc: ("opmx.dynamic_batching", "KeyValueCache" / "MultiHeadCacheAttention" / "MultiHeadAttention", 1, 1)
     assert host.registry_has("MultiHeadCacheAttention", 1)
     assert host.registry_has("KeyValueCache", 1)
+    assert host.registry_has("MultiHeadAttention", 1)
     assert not host.registry_has("MultiHeadCacheAttention", 2)
-    assert not host.registry_has("MultiHeadAttention", 1)
+    assert not host.registry_has("RotaryPositionEmbedding", 1)
     assert not host.registry_has("MultiHeadCacheAttention", 1, domain="opmx")
 
 
