@@ -200,6 +200,57 @@ int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const vo
                         void* attn_output, void* stream);
 
 /*
+ * RotaryPositionEmbedding for ragged batches (opmx.dynamic_batching.RotaryPositionEmbedding).  Replaces
+ * ppl::kernel::llm::cuda::pmx::dynamic_batching_rotary_position_embedding as called from
+ * src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/rotary_position_embedding_kernel.cc:107-129
+ * (attributes: src/ppl/nn/params/opmx/rotary_position_embedding_param.h).
+ *   query [total_tokens, num_heads, head_dim], key [total_tokens, num_kv_heads, head_dim], fp16;
+ *   the token at index i of sequence b has position start_pos[b] + i.
+ *   Channel pairs (2j, 2j+1), j < rotary_dim/2 (rotary_dim 0 = head_dim), are rotated by
+ *   pos_eff * theta_eff^(-2j/rotary_dim); the other channels pass through.  scaling_type 0 none,
+ *   1 linear (pos / scaling_factor), 2 dynamic (theta grows once start_pos + seqlen exceeds
+ *   max_position_embeddings).  bypass_key != 0: the key passes through unrotated.
+ *   rotated_query / rotated_key may alias query / key (the reference hands the input buffers over when it can).
+ * `workspace`: pplb200_rope_workspace_size() bytes of device memory (the inverse-frequency table).
+ */
+typedef struct pplb200_rope_params {
+    int32_t num_heads;
+    int32_t num_kv_heads;
+    int32_t head_dim;   /* 64 or 128 */
+    int32_t rotary_dim; /* even, <= head_dim; 0 = head_dim */
+    int32_t bypass_key;
+    int32_t scaling_type; /* 0 none, 1 linear, 2 dynamic */
+    int32_t max_position_embeddings;
+    int32_t reserved;
+    float theta;
+    float scaling_factor;
+    int64_t batch;
+    int64_t max_seqlen;
+    int64_t total_tokens;
+} pplb200_rope_params;
+
+int pplb200_rope_workspace_size(const pplb200_rope_params* p, uint64_t* bytes);
+
+int pplb200_rope_forward(const pplb200_rope_params* p, const void* query, const void* key, const int64_t* seqstarts,
+                         const int64_t* start_pos, void* workspace, uint64_t workspace_bytes, void* rotated_query,
+                         void* rotated_key, void* stream);
+
+/*
+ * The rotary embedding and the KeyValueCache write side in one kernel: rotates the query into
+ * `rotated_query`, rotates the key, rounds it to fp16 (written to `rotated_key` unless that is null),
+ * quantises it and `value` and appends both to the cache.  The cache rows are bit-identical to
+ * pplb200_rope_forward followed by pplb200_kv_append_i8g8; a following pplb200_mhca_forward is called with
+ * phase_mask = PPLB200_PHASE_DECODE | PPLB200_PHASE_PREFILL.  No counterpart in the reference, whose
+ * graph runs the two operators separately; `rotated_key` may only be null when the step has no prefill
+ * sequence reading it.  `attn` supplies the cache geometry (layer, layout, strides, paging).
+ */
+int pplb200_rope_kv_append_i8g8(const pplb200_rope_params* p, const pplb200_attn_params* attn, const void* query,
+                                const void* key, const void* value, const int64_t* seqstarts,
+                                const int64_t* cachestarts, const int64_t* start_pos, void* workspace,
+                                uint64_t workspace_bytes, void* rotated_query, void* rotated_key, void* cache,
+                                void* scale, void* stream);
+
+/*
  * Reads the device-side status word that the kernels of the last pplb200_mhca_forward on this
  * workspace left behind (0 = clean; non-zero = a bounded wait gave up, see PPLB200_DEV_*).
  * Synchronises `stream`.  Has no counterpart in the reference; it exists because every wait

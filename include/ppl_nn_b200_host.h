@@ -43,8 +43,9 @@ int pplb200_host_registry_has(const char* domain, const char* type, uint64_t ver
 void pplb200_host_registry_remove(const char* domain, const char* type);
 int pplb200_host_registry_register_again(const char* domain, const char* type, uint64_t first, uint64_t last);
 
-/* Creates node + attribute object + Op (Init) + Kernel.  attr_names/attr_values: the node's integer
- * attributes.  On failure returns null and stores the RetCode in *rc. */
+/* Creates node + attribute object + Op (Init) + Kernel.  attr_names/attr_values: the node's attributes
+ * as integers; a float attribute (theta, scaling_factor) is passed as the bit pattern of the float in the
+ * low 32 bits, the string attribute scaling_type as 0 (""), 1 ("linear") or 2 ("dynamic").  On failure returns null and stores the RetCode in *rc. */
 void* pplb200_host_op_create(void* engine, const char* domain, const char* type, uint64_t version,
                              const char* const* attr_names, const int64_t* attr_values, int num_attrs, int* rc);
 void pplb200_host_op_destroy(void* op);

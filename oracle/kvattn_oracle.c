@@ -430,6 +430,80 @@ int orc_mha(const orc_desc* d, const uint16_t* query, const uint16_t* key, const
     return failed;
 }
 
+/* RotaryPositionEmbedding for ragged batches (contract: src/ppl/nn/engines/llm_cuda/kernels/opmx/
+ * dynamic_batching/rotary_position_embedding_kernel.cc:24-132, attributes params/opmx/
+ * rotary_position_embedding_param.h; the arithmetic is not in the reference tree, so the convention below
+ * is this repository's): channel pairs (2j, 2j+1), j < rotary_dim/2, of every head are rotated by
+ * pos_eff * inv_freq[j], inv_freq[j] = (float)pow(theta_eff, -2j/rotary_dim) in double; pos = start_pos[b] + i;
+ * scaling_type 0: pos_eff = pos; 1 (linear): pos_eff = (float)pos / scaling_factor; 2 (dynamic): with
+ * L = start_pos[b] + seqlen[b] > max_position_embeddings,
+ * theta_eff = theta * pow(scaling_factor * L / max_pos - (scaling_factor - 1), rotary_dim / (rotary_dim - 2)).
+ * float throughout after that: angle = pos_eff * inv_freq[j]; products and sums rounded one by one (no fma). */
+static void rope_rows(const uint16_t* in, uint16_t* out, int64_t heads, int64_t Dh, int64_t half_rot, float pos_eff,
+                      const float* inv_freq, int rotate) {
+    for (int64_t h = 0; h < heads; ++h) {
+        const uint16_t* x = in + h * Dh;
+        uint16_t* y = out + h * Dh;
+        for (int64_t e = 0; e < Dh; ++e) {
+            y[e] = x[e];
+        }
+        if (!rotate) {
+            continue;
+        }
+        for (int64_t j = 0; j < half_rot; ++j) {
+            const volatile float angle = pos_eff * inv_freq[j];
+            const float sn = sinf(angle), cs = cosf(angle);
+            const float x0 = orc_half_to_float(x[2 * j]), x1 = orc_half_to_float(x[2 * j + 1]);
+            const volatile float p0 = x0 * cs, p1 = x1 * sn, p2 = x0 * sn, p3 = x1 * cs;
+            y[2 * j] = orc_float_to_half(p0 - p1);
+            y[2 * j + 1] = orc_float_to_half(p2 + p3);
+        }
+    }
+}
+
+int orc_rope(int64_t num_heads, int64_t num_kv_heads, int64_t head_dim, int64_t rotary_dim, int bypass_key,
+             int scaling_type, int64_t max_position_embeddings, float theta, float scaling_factor, int64_t batch,
+             const uint16_t* query, const uint16_t* key, const int64_t* seqstarts, const int64_t* start_pos,
+             uint16_t* rotated_query, uint16_t* rotated_key) {
+    const int64_t rot = rotary_dim == 0 ? head_dim : rotary_dim;
+    if (rot < 2 || rot > head_dim || (rot & 1) || scaling_type < 0 || scaling_type > 2) {
+        return 1;
+    }
+    const int64_t half_rot = rot / 2;
+    float* inv_freq = (float*)malloc(sizeof(float) * (size_t)half_rot);
+    if (!inv_freq) {
+        return 1;
+    }
+    for (int64_t b = 0; b < batch; ++b) {
+        const int64_t seqlen = seqstarts[b + 1] - seqstarts[b];
+        double theta_eff = (double)theta;
+        if (scaling_type == 2) {
+            const double len = (double)(start_pos[b] + seqlen);
+            if (len > (double)max_position_embeddings) {
+                theta_eff = (double)theta * pow((double)scaling_factor * len / (double)max_position_embeddings -
+                                                    ((double)scaling_factor - 1.0),
+                                                (double)rot / ((double)rot - 2.0));
+            }
+        }
+        for (int64_t j = 0; j < half_rot; ++j) {
+            inv_freq[j] = (float)pow(theta_eff, -2.0 * (double)j / (double)rot);
+        }
+        for (int64_t i = 0; i < seqlen; ++i) {
+            const int64_t tok = seqstarts[b] + i;
+            float pos_eff = (float)(start_pos[b] + i);
+            if (scaling_type == 1) {
+                pos_eff = pos_eff / scaling_factor;
+            }
+            rope_rows(query + tok * num_heads * head_dim, rotated_query + tok * num_heads * head_dim, num_heads, head_dim,
+                      half_rot, pos_eff, inv_freq, 1);
+            rope_rows(key + tok * num_kv_heads * head_dim, rotated_key + tok * num_kv_heads * head_dim, num_kv_heads,
+                      head_dim, half_rot, pos_eff, inv_freq, !bypass_key);
+        }
+    }
+    free(inv_freq);
+    return 0;
+}
+
 int orc_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

@@ -78,6 +78,9 @@ class COracle:
         L.orc_attention.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 9 + [ctypes.c_int64, ctypes.c_int64]
         L.orc_mhca.restype = ctypes.c_int
         L.orc_mhca.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 9
+        L.orc_rope.restype = ctypes.c_int
+        L.orc_rope.argtypes = [ctypes.c_int64] * 4 + [ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_float,
+                               ctypes.c_float, ctypes.c_int64] + [vp] * 6
         L.orc_mha.restype = ctypes.c_int
         L.orc_mha.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 6
         L.orc_num_threads.restype = ctypes.c_int
@@ -163,6 +166,18 @@ class COracle:
             raise RuntimeError(f"orc_mha failed: {rc}")
         return out
 
+    def rope(self, query, key, seqstarts, start_pos, *, theta=10000.0, rotary_dim=0, bypass_key=False,
+             scaling_type=0, scaling_factor=1.0, max_position_embeddings=2048):
+        """RotaryPositionEmbedding: (rotated_query, rotated_key); scaling_type 0 none, 1 linear, 2 dynamic."""
+        rq, rk = np.empty_like(query), np.empty_like(key)
+        rc = self.lib.orc_rope(query.shape[1], key.shape[1], query.shape[2], int(rotary_dim), int(bool(bypass_key)),
+                               int(scaling_type), int(max_position_embeddings), ctypes.c_float(theta),
+                               ctypes.c_float(scaling_factor), len(start_pos), _ptr(query), _ptr(key), _ptr(seqstarts),
+                               _ptr(start_pos), _ptr(rq), _ptr(rk))
+        if rc != 0:
+            raise RuntimeError(f"orc_rope failed: {rc}")
+        return rq, rk
+
 
 # ------------------------------------------------------------------ numpy twin ---------
 
@@ -210,4 +225,31 @@ def np_mha(query, key, value, seqstarts, kvstarts, num_kv_heads: int, is_causal:
             for h in range(Hq):
                 kvh = h // group
                 out[s0 + i, h] = np_attention_one(q32[s0 + i, h], k32[k0:k0 + n, kvh], v32[k0:k0 + n, kvh]).astype(np.float16)
+    return out
+
+
+def np_rope(x, seqstarts, start_pos, *, theta=10000.0, rotary_dim=0, scaling_type=0, scaling_factor=1.0,
+            max_position_embeddings=2048) -> np.ndarray:
+    """numpy twin of orc_rope for one tensor [T, H, Dh] (fp16 in and out)."""
+    T, H, Dh = x.shape
+    rot = Dh if rotary_dim == 0 else rotary_dim
+    out = np.array(x, dtype=np.float16, copy=True)
+    j = np.arange(rot // 2, dtype=np.float64)
+    for b in range(len(start_pos)):
+        s0, s1 = int(seqstarts[b]), int(seqstarts[b + 1])
+        th = float(np.float32(theta))
+        L = int(start_pos[b]) + (s1 - s0)
+        if scaling_type == 2 and L > max_position_embeddings:
+            f = float(np.float32(scaling_factor))
+            th = th * (f * L / max_position_embeddings - (f - 1.0)) ** (rot / (rot - 2.0))
+        inv = np.power(th, -2.0 * j / rot).astype(np.float32)
+        pos = (np.arange(s1 - s0, dtype=np.int64) + int(start_pos[b])).astype(np.float32)
+        if scaling_type == 1:
+            pos = pos / np.float32(scaling_factor)
+        ang = (pos[:, None] * inv[None, :]).astype(np.float32)
+        sn, cs = np.sin(ang)[:, None, :], np.cos(ang)[:, None, :]
+        x0 = x[s0:s1, :, 0:rot:2].astype(np.float32)
+        x1 = x[s0:s1, :, 1:rot:2].astype(np.float32)
+        out[s0:s1, :, 0:rot:2] = ((x0 * cs).astype(np.float32) - (x1 * sn).astype(np.float32)).astype(np.float16)
+        out[s0:s1, :, 1:rot:2] = ((x0 * sn).astype(np.float32) + (x1 * cs).astype(np.float32)).astype(np.float16)
     return out

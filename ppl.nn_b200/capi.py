@@ -44,6 +44,9 @@ EXPORTS = (
     "pplb200_mhca_device_status",
     "pplb200_mha_workspace_size",
     "pplb200_mha_forward",
+    "pplb200_rope_workspace_size",
+    "pplb200_rope_forward",
+    "pplb200_rope_kv_append_i8g8",
     "pplb200_status_str",
     "pplb200_device_ready",
     "pplb200_launch_count",
@@ -85,6 +88,18 @@ class MhaParams(ctypes.Structure):
         ("is_causal", ctypes.c_int32),
         ("batch", ctypes.c_int64), ("decoding_batches", ctypes.c_int64), ("max_seqlen", ctypes.c_int64),
         ("max_kvlen", ctypes.c_int64), ("total_tokens", ctypes.c_int64), ("total_kv_tokens", ctypes.c_int64),
+    ]
+
+
+class RopeParams(ctypes.Structure):
+    """Mirror of ``pplb200_rope_params``."""
+
+    _fields_ = [
+        ("num_heads", ctypes.c_int32), ("num_kv_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32),
+        ("rotary_dim", ctypes.c_int32), ("bypass_key", ctypes.c_int32), ("scaling_type", ctypes.c_int32),
+        ("max_position_embeddings", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("theta", ctypes.c_float), ("scaling_factor", ctypes.c_float),
+        ("batch", ctypes.c_int64), ("max_seqlen", ctypes.c_int64), ("total_tokens", ctypes.c_int64),
     ]
 
 
@@ -130,6 +145,14 @@ class Library:
         d.pplb200_mha_workspace_size.argtypes = [mp, ctypes.POINTER(ctypes.c_uint64)]
         d.pplb200_mha_forward.restype = ctypes.c_int
         d.pplb200_mha_forward.argtypes = [mp, vp, vp, vp, i64p, i64p, vp, ctypes.c_uint64, vp, vp]
+        rp = ctypes.POINTER(RopeParams)
+        d.pplb200_rope_workspace_size.restype = ctypes.c_int
+        d.pplb200_rope_workspace_size.argtypes = [rp, ctypes.POINTER(ctypes.c_uint64)]
+        d.pplb200_rope_forward.restype = ctypes.c_int
+        d.pplb200_rope_forward.argtypes = [rp, vp, vp, i64p, i64p, vp, ctypes.c_uint64, vp, vp, vp]
+        d.pplb200_rope_kv_append_i8g8.restype = ctypes.c_int
+        d.pplb200_rope_kv_append_i8g8.argtypes = [rp, pp, vp, vp, vp, i64p, i64p, i64p, vp, ctypes.c_uint64, vp, vp,
+                                                  vp, vp, vp]
         d.pplb200_status_str.restype = ctypes.c_char_p
         d.pplb200_status_str.argtypes = [ctypes.c_int]
         d.pplb200_device_ready.restype = ctypes.c_int
@@ -201,6 +224,21 @@ class Library:
     def mha_forward(self, p, q, k, v, seqstarts, kvstarts, workspace, workspace_bytes, out, stream) -> int:
         return self.dll.pplb200_mha_forward(ctypes.byref(p), q, k, v, seqstarts, kvstarts, workspace,
                                             int(workspace_bytes), out, stream)
+
+    def rope_workspace_size(self, p) -> tuple[int, int]:
+        n = ctypes.c_uint64(0)
+        rc = self.dll.pplb200_rope_workspace_size(ctypes.byref(p), ctypes.byref(n))
+        return rc, int(n.value)
+
+    def rope_forward(self, p, q, k, seqstarts, start_pos, workspace, workspace_bytes, rq, rk, stream) -> int:
+        return self.dll.pplb200_rope_forward(ctypes.byref(p), q, k, seqstarts, start_pos, workspace,
+                                             int(workspace_bytes), rq, rk, stream)
+
+    def rope_kv_append(self, p, attn, q, k, v, seqstarts, cachestarts, start_pos, workspace, workspace_bytes, rq, rk,
+                       cache, scale, stream) -> int:
+        return self.dll.pplb200_rope_kv_append_i8g8(ctypes.byref(p), ctypes.byref(attn), q, k, v, seqstarts,
+                                                    cachestarts, start_pos, workspace, int(workspace_bytes), rq, rk,
+                                                    cache, scale, stream)
 
     def static_scratch_bytes(self) -> int:
         return int(self.dll.pplb200_static_scratch_bytes())

@@ -419,6 +419,114 @@ int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const vo
                       stream);
 }
 
+static int validate_rope(const pplb200_rope_params* p) {
+    if (!p) {
+        return fail(PPLB200_NOT_FOUND, "params is null");
+    }
+    if (p->head_dim != 64 && p->head_dim != 128) {
+        return fail(PPLB200_UNSUPPORTED, "head_dim must be 64 or 128");
+    }
+    const int rot = p->rotary_dim == 0 ? p->head_dim : p->rotary_dim;
+    if (rot < 2 || rot > p->head_dim || (rot & 1)) {
+        return fail(PPLB200_INVALID_VALUE, "rotary_dim must be even and within head_dim");
+    }
+    if (p->num_heads <= 0 || p->num_kv_heads <= 0) {
+        return fail(PPLB200_INVALID_VALUE, "head counts must be positive");
+    }
+    if (p->scaling_type < 0 || p->scaling_type > 2) {
+        return fail(PPLB200_INVALID_VALUE, "invalid scaling type");
+    }
+    if (!(p->theta > 0.0f) || (p->scaling_type != 0 && !(p->scaling_factor > 0.0f))) {
+        return fail(PPLB200_INVALID_VALUE, "theta and scaling_factor must be positive");
+    }
+    if (p->scaling_type == 2 && (p->max_position_embeddings <= 0 || rot <= 2)) {
+        return fail(PPLB200_INVALID_VALUE, "dynamic scaling needs max_position_embeddings > 0 and rotary_dim > 2");
+    }
+    if (p->batch < 0 || p->total_tokens < 0 || p->batch > 0x7fffffff) {
+        return fail(PPLB200_INVALID_VALUE, "negative size");
+    }
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_rope_workspace_size(const pplb200_rope_params* p, uint64_t* bytes) {
+    const int rc = validate_rope(p);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!bytes) {
+        return fail(PPLB200_NOT_FOUND, "null argument");
+    }
+    *bytes = rope_workspace_bytes(*p);
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_rope_forward(const pplb200_rope_params* p, const void* query, const void* key, const int64_t* seqstarts,
+                         const int64_t* start_pos, void* workspace, uint64_t workspace_bytes, void* rotated_query,
+                         void* rotated_key, void* stream) {
+    int rc = validate_rope(p);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!query || !key || !seqstarts || !start_pos || !rotated_query || !rotated_key) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    if (p->batch == 0 || p->total_tokens == 0) {
+        return PPLB200_SUCCESS;
+    }
+    DeviceInfo di;
+    rc = require_device(&di);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!workspace) {
+        return fail(PPLB200_NOT_FOUND, "workspace is null");
+    }
+    if (workspace_bytes < rope_workspace_bytes(*p)) {
+        return fail(PPLB200_OUT_OF_MEMORY, "workspace is smaller than pplb200_rope_workspace_size()");
+    }
+    return launch_rope(*p, nullptr, nullptr, query, key, nullptr, seqstarts, start_pos, nullptr, workspace,
+                       rotated_query, rotated_key, nullptr, nullptr, di.sm_count, static_cast<cudaStream_t>(stream));
+}
+
+int pplb200_rope_kv_append_i8g8(const pplb200_rope_params* p, const pplb200_attn_params* attn, const void* query,
+                                const void* key, const void* value, const int64_t* seqstarts,
+                                const int64_t* cachestarts, const int64_t* start_pos, void* workspace,
+                                uint64_t workspace_bytes, void* rotated_query, void* rotated_key, void* cache,
+                                void* scale, void* stream) {
+    int rc = validate_rope(p);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    rc = validate(attn);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (attn->num_heads != p->num_heads || attn->num_kv_heads != p->num_kv_heads || attn->head_dim != p->head_dim ||
+        attn->batch != p->batch || attn->total_tokens != p->total_tokens) {
+        return fail(PPLB200_INVALID_VALUE, "the two parameter blocks disagree on heads, head_dim, batch or tokens");
+    }
+    if (!query || !key || !value || !seqstarts || !cachestarts || !start_pos || !rotated_query || !cache || !scale) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    if (p->batch == 0 || p->total_tokens == 0) {
+        return PPLB200_SUCCESS;
+    }
+    DeviceInfo di;
+    rc = require_device(&di);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    if (!workspace) {
+        return fail(PPLB200_NOT_FOUND, "workspace is null");
+    }
+    if (workspace_bytes < rope_workspace_bytes(*p)) {
+        return fail(PPLB200_OUT_OF_MEMORY, "workspace is smaller than pplb200_rope_workspace_size()");
+    }
+    const CacheGeom geom = make_geom(*attn);
+    return launch_rope(*p, attn, &geom, query, key, value, seqstarts, start_pos, cachestarts, workspace, rotated_query,
+                       rotated_key, cache, scale, di.sm_count, static_cast<cudaStream_t>(stream));
+}
+
 int pplb200_mhca_device_status(const void* workspace, void* stream, uint32_t* status) {
     if (!workspace || !status) {
         return PPLB200_NOT_FOUND;

@@ -110,4 +110,11 @@ int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int
                const void* value, const int64_t* seqstarts, const int64_t* kvstarts, uint32_t* status_word,
                void* attn_output, cudaStream_t stream);
 
+// Rotary position embedding, alone (append == nullptr) or fused with the cache append.
+uint64_t rope_workspace_bytes(const pplb200_rope_params& p);
+int launch_rope(const pplb200_rope_params& p, const pplb200_attn_params* append, const CacheGeom* geom,
+                const void* query, const void* key, const void* value, const int64_t* seqstarts,
+                const int64_t* start_pos, const int64_t* cachestarts, void* workspace, void* rotated_query,
+                void* rotated_key, void* cache, void* scale, int sm_count, cudaStream_t stream);
+
 }  // namespace pplb200

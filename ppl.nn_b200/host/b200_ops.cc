@@ -311,6 +311,110 @@ RetCode DynamicBatchingMultiHeadAttentionKernel::DoExecute(KernelExecContext* ct
 }
 
 // =================================================================================================
+// RotaryPositionEmbedding
+// =================================================================================================
+RetCode DynamicBatchingRotaryPositionEmbeddingOp::DoInit(const OptKernelOptions& options) {
+    const RetCode rc = GenericLoadParam<ppl::nn::opmx::RotaryPositionEmbeddingParam>(options, &param_);
+    if (rc != RC_SUCCESS) {
+        LOG(ERROR) << "GenericLoadParam failed: " << GetRetCodeStr(rc);
+        return rc;
+    }
+    infer_type_and_format_func_ = GenericInferTypeAndFormat;
+    // rotated_query takes query's dims, rotated_key takes key's
+    // (src/ppl/nn/oputils/opmx/reshape_rotary_position_embedding.cc:26-35)
+    infer_dims_func_ = [](InputOutputInfo* info) -> RetCode {
+        for (uint32_t i = 0; i < 2 && i < info->GetOutputCount(); ++i) {
+            auto in = info->GetInput<TensorImpl>(i);
+            auto out = info->GetOutput<TensorImpl>(i);
+            if (in && out) {
+                out->GetShape()->Reshape(in->GetShape()->GetDims(), in->GetShape()->GetDimCount());
+            }
+        }
+        return RC_SUCCESS;
+    };
+    return RC_SUCCESS;
+}
+
+KernelImpl* DynamicBatchingRotaryPositionEmbeddingOp::CreateKernelImpl() const {
+    return CreateKernelImplWithParam<DynamicBatchingRotaryPositionEmbeddingKernel>(param_.get());
+}
+
+RetCode DynamicBatchingRotaryPositionEmbeddingKernel::DoExecute(KernelExecContext* ctx) {
+    // inputs by index: 0 query, 1 key, 2 seqstarts, 3 start_pos, 4 max_seqlen; outputs 0 rotated_query,
+    // 1 rotated_key (src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/rotary_position_embedding_kernel.cc:27-34)
+    static const char* const kNames[5] = {"query", "key", "seqstarts", "start_pos", "max_seqlen"};
+    Slots s(ctx);
+    TensorImpl* in[5];
+    for (uint32_t i = 0; i < 5; ++i) {
+        in[i] = s.In(i);
+        if (!s.Need(in[i], "Input", kNames[i])) {
+            return s.rc;
+        }
+    }
+    TensorImpl* rotated_query = s.Out(0);
+    TensorImpl* rotated_key = s.Out(1);
+    if (!s.Need(rotated_query, "Output", "rotated_query") || !s.Need(rotated_key, "Output", "rotated_key")) {
+        return s.rc;
+    }
+    TensorImpl *query = in[0], *key = in[1], *seqstarts = in[2], *start_pos = in[3];
+
+    RetCode rc = Reshape(ctx);
+    if (rc != RC_SUCCESS) {
+        LOG(ERROR) << "Reshape kernel[" << GetName() << "] failed: " << GetRetCodeStr(rc);
+        return rc;
+    }
+    if (query->GetShape()->GetDataType() != DATATYPE_FLOAT16) {
+        LOG(ERROR) << "currently only support fp16";
+        return RC_UNSUPPORTED;
+    }
+    for (TensorImpl* t : {query, key, seqstarts, start_pos}) {
+        if ((rc = RequireOnDevice(t, GetCudaDevice())) != RC_SUCCESS) {
+            return rc;
+        }
+    }
+    // The reference hands the input buffers over to the outputs when it is their last consumer
+    // (:55-75); here the outputs always get buffers of their own.
+    if ((rc = ReallocOn(rotated_query, GetCudaDevice())) != RC_SUCCESS) return rc;
+    if ((rc = ReallocOn(rotated_key, GetCudaDevice())) != RC_SUCCESS) return rc;
+
+    int64_t max_seqlen = 0;
+    if ((rc = ReadScalar(in[4], &max_seqlen, "max_seqlen")) != RC_SUCCESS) return rc;
+
+    pplb200_rope_params p;
+    memset(&p, 0, sizeof(p));
+    p.num_heads = static_cast<int32_t>(query->GetShape()->GetDim(1));
+    p.num_kv_heads = static_cast<int32_t>(key->GetShape()->GetDim(1));
+    p.head_dim = static_cast<int32_t>(query->GetShape()->GetDim(2));
+    p.rotary_dim = param_->rotary_dim;
+    p.bypass_key = param_->bypass_key;
+    // The reference's mapping of the scaling type tests with != where == is meant (:94-103), which sends
+    // every type to its neighbour; the attribute's own meaning is used here.
+    p.scaling_type = param_->scaling_type;
+    p.max_position_embeddings = param_->max_position_embeddings;
+    p.theta = param_->theta;
+    p.scaling_factor = param_->scaling_factor;
+    p.batch = start_pos->GetShape()->GetDim(0);
+    p.max_seqlen = max_seqlen;
+    p.total_tokens = query->GetShape()->GetDim(0);
+
+    uint64_t workspace_bytes = 0;
+    if ((rc = FromStatus(pplb200_rope_workspace_size(&p, &workspace_bytes))) != RC_SUCCESS) {
+        return rc;
+    }
+    BufferDesc tmp;
+    rc = GetCudaDevice()->AllocTmpBuffer(workspace_bytes, &tmp);
+    if (rc != RC_SUCCESS) {
+        LOG(ERROR) << "alloc tmp buffer size[" << workspace_bytes << "] for kernel[" << GetName()
+                   << "] failed: " << GetRetCodeStr(rc);
+        return rc;
+    }
+    Destructor tmp_guard([this, &tmp]() { GetCudaDevice()->FreeTmpBuffer(&tmp); });
+    return FromStatus(pplb200_rope_forward(&p, query->GetBufferPtr(), key->GetBufferPtr(), seqstarts->GetBufferPtr<int64_t>(),
+                                           start_pos->GetBufferPtr<int64_t>(), tmp.addr, workspace_bytes,
+                                           rotated_query->GetBufferPtr(), rotated_key->GetBufferPtr(), GetStream()));
+}
+
+// =================================================================================================
 // KeyValueCache
 // =================================================================================================
 RetCode DynamicBatchingKeyValueCacheOp::DoInit(const OptKernelOptions& options) {
@@ -472,6 +576,9 @@ void RegisterB200OpImpls() {
                   CreateOp<opmx::DynamicBatchingMultiHeadCacheAttentionOp>);
     mgr->Remove(domain, "KeyValueCache");
     mgr->Register(domain, "KeyValueCache", utils::VersionRange(1, 1), CreateOp<opmx::DynamicBatchingKeyValueCacheOp>);
+    mgr->Remove(domain, "RotaryPositionEmbedding");
+    mgr->Register(domain, "RotaryPositionEmbedding", utils::VersionRange(1, 1),
+                  CreateOp<opmx::DynamicBatchingRotaryPositionEmbeddingOp>);
     mgr->Remove(domain, "MultiHeadAttention");
     mgr->Register(domain, "MultiHeadAttention", utils::VersionRange(1, 1),
                   CreateOp<opmx::DynamicBatchingMultiHeadAttentionOp>);

@@ -73,4 +73,26 @@ private:
     std::shared_ptr<ppl::nn::opmx::MultiHeadAttentionParam> param_;
 };
 
+// DynamicBatchingRotaryPositionEmbeddingOp / ...Kernel
+//     src/ppl/nn/engines/llm_cuda/{ops,kernels}/opmx/dynamic_batching/rotary_position_embedding_*
+class DynamicBatchingRotaryPositionEmbeddingKernel final : public LlmCudaKernel {
+public:
+    explicit DynamicBatchingRotaryPositionEmbeddingKernel(const ir::Node* node) : LlmCudaKernel(node) {}
+    void SetParam(const ppl::nn::opmx::RotaryPositionEmbeddingParam* p) { param_ = p; }
+
+private:
+    ppl::common::RetCode DoExecute(KernelExecContext*) override;
+    const ppl::nn::opmx::RotaryPositionEmbeddingParam* param_ = nullptr;
+};
+
+class DynamicBatchingRotaryPositionEmbeddingOp final : public LlmCudaOptKernel {
+public:
+    explicit DynamicBatchingRotaryPositionEmbeddingOp(const ir::Node* node) : LlmCudaOptKernel(node) {}
+    KernelImpl* CreateKernelImpl() const override;
+
+private:
+    ppl::common::RetCode DoInit(const OptKernelOptions&) override;
+    std::shared_ptr<ppl::nn::opmx::RotaryPositionEmbeddingParam> param_;
+};
+
 }}}}}  // namespace ppl::nn::llm::cuda::opmx

@@ -152,6 +152,10 @@ void* pplb200_host_op_create(void* engine, const char* domain, const char* type,
         auto p = std::make_shared<ppl::nn::opmx::KeyValueCacheParam>();
         rc = ppl::nn::opmx::ParseKeyValueCacheParam(attrs, p.get());
         op->graph.data->attrs[op->node->GetId()] = p;
+    } else if (t == "RotaryPositionEmbedding") {
+        auto p = std::make_shared<ppl::nn::opmx::RotaryPositionEmbeddingParam>();
+        rc = ppl::nn::opmx::ParseRotaryPositionEmbeddingParam(attrs, p.get());
+        op->graph.data->attrs[op->node->GetId()] = p;
     } else if (t == "MultiHeadAttention") {
         auto p = std::make_shared<ppl::nn::opmx::MultiHeadAttentionParam>();
         rc = ppl::nn::opmx::ParseMultiHeadAttentionParam(attrs, p.get());

@@ -1,6 +1,8 @@
 // Devices, kernel/operator bases, attribute parsers and the operator registry of the host layer.
 #include "llm_cuda.h"
 
+#include <string.h>
+
 #include <stdlib.h>
 
 using namespace ppl::common;
@@ -72,6 +74,32 @@ RetCode ParseMultiHeadAttentionParam(const AttrMap& attrs, MultiHeadAttentionPar
     Optional(attrs, "num_kv_heads", &p->num_kv_heads, p->num_heads);
     Optional(attrs, "is_causal", &p->is_causal, true);
     Optional(attrs, "is_alibi", &p->is_alibi, false);
+    return RC_SUCCESS;
+}
+
+static float FloatFromBits(int64_t v) {
+    const uint32_t u = static_cast<uint32_t>(v);
+    float f;
+    memcpy(&f, &u, sizeof(f));
+    return f;
+}
+
+RetCode ParseRotaryPositionEmbeddingParam(const AttrMap& attrs, RotaryPositionEmbeddingParam* p) {
+    int64_t v = 0;
+    if (!Lookup(attrs, "theta", &v)) {  // parse_rotary_position_embedding_param.cc:13-16
+        LOG(ERROR) << "attribute \"theta\" is required.";
+        return RC_NOT_FOUND;
+    }
+    p->theta = FloatFromBits(v);
+    Optional(attrs, "bypass_key", &p->bypass_key, 0);
+    Optional(attrs, "rotary_dim", &p->rotary_dim, 0);
+    p->scaling_factor = Lookup(attrs, "scaling_factor", &v) ? FloatFromBits(v) : 1.0f;
+    Optional(attrs, "max_position_embeddings", &p->max_position_embeddings, 2048);
+    Optional(attrs, "scaling_type", &p->scaling_type, 0);
+    if (p->scaling_type < 0 || p->scaling_type > 2) {
+        LOG(ERROR) << "unsupported scaling_type: " << p->scaling_type;
+        return RC_UNSUPPORTED;
+    }
     return RC_SUCCESS;
 }
 

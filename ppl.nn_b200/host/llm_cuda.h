@@ -61,7 +61,20 @@ struct MultiHeadAttentionParam final : public ir::TypedAttr<MultiHeadAttentionPa
     bool is_alibi = false;
 };
 
-// Attributes of a node as name -> integer (all attributes of these two operators are ints).
+// src/ppl/nn/params/opmx/rotary_position_embedding_param.h; parser
+// src/ppl/nn/models/onnx/parsers/opmx/parse_rotary_position_embedding_param.cc
+struct RotaryPositionEmbeddingParam final : public ir::TypedAttr<RotaryPositionEmbeddingParam> {
+    enum { SCALING_TYPE_NONE = 0, SCALING_TYPE_LINEAR = 1, SCALING_TYPE_DYNAMIC = 2 };
+    int32_t bypass_key = 0;
+    int32_t rotary_dim = 0;
+    float theta = 10000.0f;
+    int32_t max_position_embeddings = 2048;
+    int32_t scaling_type = SCALING_TYPE_NONE;
+    float scaling_factor = 1.0f;
+};
+
+// Attributes of a node as name -> integer.  A float attribute (theta, scaling_factor) travels as the bit
+// pattern of the float in the low 32 bits; the string attribute scaling_type as 0 "", 1 "linear", 2 "dynamic".
 using AttrMap = std::map<std::string, int64_t>;
 
 // Same required attributes and defaults as the ONNX parsers: a missing required attribute is
@@ -69,6 +82,7 @@ using AttrMap = std::map<std::string, int64_t>;
 ppl::common::RetCode ParseKeyValueCacheParam(const AttrMap& attrs, KeyValueCacheParam* param);
 ppl::common::RetCode ParseMultiHeadCacheAttentionParam(const AttrMap& attrs, MultiHeadCacheAttentionParam* param);
 ppl::common::RetCode ParseMultiHeadAttentionParam(const AttrMap& attrs, MultiHeadAttentionParam* param);
+ppl::common::RetCode ParseRotaryPositionEmbeddingParam(const AttrMap& attrs, RotaryPositionEmbeddingParam* param);
 
 }  // namespace opmx
 

@@ -65,6 +65,17 @@ class MultiHeadAttentionParam:
 
 
 @dataclass
+class RotaryPositionEmbeddingParam:
+    """src/ppl/nn/params/opmx/rotary_position_embedding_param.h; scaling_type "" | "linear" | "dynamic"."""
+    theta: float = 10000.0
+    bypass_key: int = 0
+    rotary_dim: int = 0
+    max_position_embeddings: int = 2048
+    scaling_type: str = ""
+    scaling_factor: float = 1.0
+
+
+@dataclass
 class EngineConfig:
     """The knobs of src/ppl/nn/engines/llm_cuda/engine_config.h:30-35 that reach this path."""
     enable_cache_prefill: bool = False
@@ -290,3 +301,69 @@ class MultiHeadAttention(_Base):
         rc, status = self.lib.mhca_device_status(_ptr(self._workspace), _stream())
         self._raise("pplb200_mhca_device_status", rc)
         return status
+
+
+class RotaryPositionEmbedding(_Base):
+    """opmx.dynamic_batching.RotaryPositionEmbedding
+    (src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/rotary_position_embedding_kernel.cc:24-132),
+    and ``forward_fused``: the same rotation fused with the quantise-and-append of the KV cache."""
+
+    _SCALING = {"": 0, "linear": 1, "dynamic": 2}
+
+    def __init__(self, param: RotaryPositionEmbeddingParam):
+        super().__init__()
+        if param.scaling_type not in self._SCALING:
+            raise OpError("RC_UNSUPPORTED", f"unsupported scaling_type: {param.scaling_type}")
+        self.param = param
+        self._workspace: torch.Tensor | None = None
+
+    def _params(self, query, key, start_pos, max_seqlen) -> capi.RopeParams:
+        a = self.param
+        p = capi.RopeParams()
+        p.num_heads, p.num_kv_heads, p.head_dim = query.shape[1], key.shape[1], query.shape[2]
+        p.rotary_dim, p.bypass_key = a.rotary_dim, int(a.bypass_key)
+        p.scaling_type = self._SCALING[a.scaling_type]
+        p.max_position_embeddings = a.max_position_embeddings
+        p.theta, p.scaling_factor = a.theta, a.scaling_factor
+        p.batch, p.max_seqlen, p.total_tokens = start_pos.shape[0], int(max_seqlen), query.shape[0]
+        return p
+
+    def _ws(self, p, device) -> torch.Tensor:
+        rc, nbytes = self.lib.rope_workspace_size(p)
+        self._raise("pplb200_rope_workspace_size", rc)
+        if self._workspace is None or self._workspace.numel() < nbytes or self._workspace.device != device:
+            self._workspace = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+        return self._workspace
+
+    def forward(self, query, key, seqstarts, start_pos, max_seqlen: int, rotated_query=None, rotated_key=None):
+        _require_cuda(query=query, key=key, seqstarts=seqstarts, start_pos=start_pos)
+        if query.dtype != torch.float16:
+            raise OpError("RC_UNSUPPORTED", "currently only support fp16")
+        p = self._params(query, key, start_pos, max_seqlen)
+        ws = self._ws(p, query.device)
+        rotated_query = torch.empty_like(query) if rotated_query is None else rotated_query
+        rotated_key = torch.empty_like(key) if rotated_key is None else rotated_key
+        rc = self.lib.rope_forward(p, _ptr(query), _ptr(key), _ptr(seqstarts), _ptr(start_pos), _ptr(ws), ws.numel(),
+                                   _ptr(rotated_query), _ptr(rotated_key), _stream())
+        self._raise("pplb200_rope_forward", rc)
+        return rotated_query, rotated_key
+
+    def forward_fused(self, attn: "MultiHeadCacheAttention", query, key, value, seqstarts, cachestarts, start_pos,
+                      max_seqlen: int, cache, scale, want_rotated_key: bool = True):
+        """Rotate, then quantise-and-append in the same kernel.  Returns (rotated_query, rotated_key or None);
+        follow with ``attn.forward(..., phase_mask=PHASE_DECODE | PHASE_PREFILL)``."""
+        _require_cuda(query=query, key=key, value=value, seqstarts=seqstarts, cachestarts=cachestarts,
+                      start_pos=start_pos, cache=cache, scale=scale)
+        p = self._params(query, key, start_pos, max_seqlen)
+        ws = self._ws(p, query.device)
+        ap = attn.make_params(batch=start_pos.shape[0], decoding_batches=0, max_seqlen=int(max_seqlen),
+                              max_kvlen=0, total_tokens=query.shape[0],
+                              max_tokens=_max_tokens(cache, attn.param.cache_layout),
+                              cachestart_stride_b=cachestarts.shape[1] if cachestarts.dim() == 2 else 0)
+        rotated_query = torch.empty_like(query)
+        rotated_key = torch.empty_like(key) if want_rotated_key else None
+        rc = self.lib.rope_kv_append(p, ap, _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts), _ptr(cachestarts),
+                                     _ptr(start_pos), _ptr(ws), ws.numel(), _ptr(rotated_query), _ptr(rotated_key),
+                                     _ptr(cache), _ptr(scale), _stream())
+        self._raise("pplb200_rope_kv_append_i8g8", rc)
+        return rotated_query, rotated_key

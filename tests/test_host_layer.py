@@ -43,7 +43,8 @@ def test_registry_serves_the_reference_op_names(host):
     assert host.registry_has("KeyValueCache", 1)
     assert host.registry_has("MultiHeadAttention", 1)
     assert not host.registry_has("MultiHeadCacheAttention", 2)
-    assert not host.registry_has("RotaryPositionEmbedding", 1)
+    assert host.registry_has("RotaryPositionEmbedding", 1)
+    assert not host.registry_has("ColumnParallelLinear", 1)
     assert not host.registry_has("MultiHeadCacheAttention", 1, domain="opmx")
 
 
@@ -78,7 +79,7 @@ def test_kvcache_required_attributes(host, engine, missing):
 
 def test_unknown_op_is_not_found(host, engine):
     with pytest.raises(host.RetCodeError) as e:
-        host.Op(engine, "RotaryPositionEmbedding", dict(num_layer=1, layer_idx=0))
+        host.Op(engine, "ColumnParallelLinear", dict(num_layer=1, layer_idx=0))
     assert e.value.name == "RC_NOT_FOUND"
 
 
