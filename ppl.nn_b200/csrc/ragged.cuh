@@ -35,8 +35,8 @@ struct WarpItems {
     int32_t step_chunk;
     int32_t chunks_per_token;
 
-    __device__ __forceinline__ WarpItems(int32_t groups_per_token) {
-        chunks_per_token = (groups_per_token + 32 * kChunks - 1) / (32 * kChunks);  // items per token
+    __device__ __forceinline__ explicit WarpItems(int32_t groups_per_token, int32_t chunks_per_item = kChunks) {
+        chunks_per_token = (groups_per_token + 32 * chunks_per_item - 1) / (32 * chunks_per_item);  // items per token
         const int64_t warp_id = (blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x) >> 5;
         const int64_t warps = (static_cast<int64_t>(gridDim.x) * blockDim.x) >> 5;
         tok = warp_id / chunks_per_token;

@@ -58,27 +58,41 @@ __global__ void rope_table_kernel(const int64_t* __restrict__ seqstarts, const i
     }
 }
 
-// Rotates the (up to 4) pairs of one group of 8 channels; `grp` = index of the group inside the head.
-__device__ __forceinline__ uint4 rotate_group(uint4 in, int grp, float pos_eff, const float* __restrict__ inv_freq,
-                                              int half_rot) {
-    const __half2* h2 = reinterpret_cast<const __half2*>(&in);
-    uint4 out = in;
-    __half2* o2 = reinterpret_cast<__half2*>(&out);
+constexpr int kRopeChunks = 8;  // chunks of 32 groups per warp item: the sines and cosines are shared by all of them
+
+// A lane always works on the same group of channels of whatever head it is looking at (32 is a multiple
+// of the groups per head), so the four (sin, cos) pairs of its channels are computed once per token.
+struct LaneRotation {
+    float sn[4], cs[4];
+    bool on[4];
+    __device__ __forceinline__ void init(int grp, float pos_eff, const float* __restrict__ inv_freq, int half_rot) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int j = grp * 4 + i;  // pair index inside the head
-        if (j < half_rot) {
-            const float angle = __fmul_rn(pos_eff, inv_freq[j]);
-            float sn, cs;
-            sincosf(angle, &sn, &cs);
-            const float2 x = __half22float2(h2[i]);
-            const float a = __fsub_rn(__fmul_rn(x.x, cs), __fmul_rn(x.y, sn));
-            const float b = __fadd_rn(__fmul_rn(x.x, sn), __fmul_rn(x.y, cs));
-            o2[i] = __floats2half2_rn(a, b);
+        for (int i = 0; i < 4; ++i) {
+            const int j = grp * 4 + i;  // pair index inside the head
+            on[i] = j < half_rot;
+            sn[i] = 0.0f;
+            cs[i] = 1.0f;
+            if (on[i]) {
+                sincosf(__fmul_rn(pos_eff, inv_freq[j]), &sn[i], &cs[i]);
+            }
         }
     }
-    return out;
-}
+    __device__ __forceinline__ uint4 apply(uint4 in) const {
+        const __half2* h2 = reinterpret_cast<const __half2*>(&in);
+        uint4 out = in;
+        __half2* o2 = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if (on[i]) {
+                const float2 x = __half22float2(h2[i]);
+                const float a = __fsub_rn(__fmul_rn(x.x, cs[i]), __fmul_rn(x.y, sn[i]));
+                const float b = __fadd_rn(__fmul_rn(x.x, sn[i]), __fmul_rn(x.y, cs[i]));
+                o2[i] = __floats2half2_rn(a, b);
+            }
+        }
+        return out;
+    }
+};
 
 struct RopeArgs {
     const __half* query;
@@ -114,11 +128,12 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
     const int32_t q_groups = a.num_heads << group_shift;
     const int32_t k_groups = a.num_kv_heads << group_shift;
     const int32_t groups_per_token = q_groups + k_groups + (FUSED ? k_groups : 0);
-    for (WarpItems it(groups_per_token); it.tok < a.total_tokens; it.next()) {
-        uint4 in[kChunks];
+    const int grp = lane & ((1 << group_shift) - 1);  // the same for every chunk: 32 is a multiple of the groups per head
+    for (WarpItems it(groups_per_token, kRopeChunks); it.tok < a.total_tokens; it.next()) {
+        uint4 in[kRopeChunks];
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+        for (int c = 0; c < kRopeChunks; ++c) {
+            const int32_t g = (it.chunk * kRopeChunks + c) * 32 + lane;
             in[c] = make_uint4(0u, 0u, 0u, 0u);
             if (g < groups_per_token) {
                 const __half* src;
@@ -143,15 +158,16 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
         if (FUSED) {
             row = cache_row(a.geom, a.cachestarts, b, pos);
         }
+        LaneRotation rotn;
+        rotn.init(grp, pos_eff, inv_freq, a.rope.half_rot);
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+        for (int c = 0; c < kRopeChunks; ++c) {
+            const int32_t g = (it.chunk * kRopeChunks + c) * 32 + lane;
             if (g >= groups_per_token) {
                 continue;
             }
-            const int grp = g & ((1 << group_shift) - 1);
             if (g < q_groups) {
-                const uint4 r = rotate_group(in[c], grp, pos_eff, inv_freq, a.rope.half_rot);
+                const uint4 r = rotn.apply(in[c]);
                 *reinterpret_cast<uint4*>(a.rotated_query + (it.tok * q_groups + g) * 8) = r;
                 continue;
             }
@@ -160,7 +176,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
             uint4 r = in[c];
             if (is_key) {
                 if (!a.bypass_key) {
-                    r = rotate_group(in[c], grp, pos_eff, inv_freq, a.rope.half_rot);
+                    r = rotn.apply(in[c]);
                 }
                 if (a.rotated_key && (a.rotated_key != a.key || !a.bypass_key)) {
                     *reinterpret_cast<uint4*>(a.rotated_key + (it.tok * k_groups + gk) * 8) = r;
@@ -179,7 +195,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
 }
 
 int grid_for_items(int64_t tokens, int32_t groups_per_token, int sm_count) {
-    const int64_t items_per_token = (groups_per_token + 32 * kChunks - 1) / (32 * kChunks);
+    const int64_t items_per_token = (groups_per_token + 32 * kRopeChunks - 1) / (32 * kRopeChunks);
     int64_t blocks = (tokens * items_per_token * 32 + 255) / 256;
     const int64_t cap = static_cast<int64_t>(sm_count) * 16;
     blocks = blocks > cap ? cap : blocks;

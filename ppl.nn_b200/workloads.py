@@ -50,6 +50,8 @@ SPECS = {
                                seed=2),
     # the prefill half of the mixed step alone (for the tensor-core roofline of the prefill kernel)
     "cfg3_prefill_only": Spec("cfg3_prefill_only", 32, 8, 128, 0, 1, 1, n_prefill=8, pf_lo=512, pf_hi=2048, seed=2),
+    # the same layer with 16 prompts of 4096 tokens: the steady state of the prefill kernel (not a BASELINE config)
+    "prefill_16x4096": Spec("prefill_16x4096", 32, 8, 128, 0, 1, 1, n_prefill=16, pf_lo=4096, pf_hi=4096, seed=5),
     # LLaMA-2-70B attention layer, large-batch decode
     "cfg4_llama70b_decode": Spec("cfg4_llama70b_decode", 64, 8, 128, 512, 64, 8192, "loguniform", seed=3),
     # Long-context split-k stress
