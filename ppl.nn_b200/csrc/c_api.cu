@@ -221,6 +221,9 @@ int pplb200_kv_append_i8g8(const pplb200_attn_params* p, const void* current_key
     if (!scale) {
         return fail(PPLB200_UNSUPPORTED, "only a quantised cache is supported but scale is null");
     }
+    if (p->batch == 0 || p->total_tokens == 0) {
+        return PPLB200_SUCCESS;  // nothing to append, whatever the pointers are
+    }
     if (!current_key || !current_value || !seqstarts || !cachestarts || !start_pos || !cache) {
         return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
     }
@@ -300,12 +303,13 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     if (!scale) {
         return fail(PPLB200_UNSUPPORTED, "only a quantised cache is supported but scale is null");
     }
+    // an empty batch is a no-op whatever the pointers are (empty tensors have none)
+    if (p->batch == 0 || p->total_tokens == 0) {
+        return PPLB200_SUCCESS;
+    }
     if (!query || !current_key || !current_value || !seqstarts || !kvstarts || !cachestarts || !start_pos || !cache ||
         !attn_output) {
         return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
-    }
-    if (p->batch == 0 || p->total_tokens == 0) {
-        return PPLB200_SUCCESS;
     }
     DeviceInfo di;
     rc = require_device(&di);
@@ -391,11 +395,12 @@ int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const vo
     if (p->total_tokens > 0x7fffffff || p->total_kv_tokens > 0x7fffffff) {
         return fail(PPLB200_UNSUPPORTED, "more than 2^31 rows");
     }
-    if (!query || !key || !value || !seqstarts || !kvstarts || !attn_output) {
-        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
-    }
+    // an empty batch is a no-op whatever the pointers are (empty tensors have none)
     if (p->batch == 0 || p->total_tokens == 0) {
         return PPLB200_SUCCESS;
+    }
+    if (!query || !key || !value || !seqstarts || !kvstarts || !attn_output) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
     }
     DeviceInfo di;
     int rc = require_device(&di);
@@ -467,11 +472,12 @@ int pplb200_rope_forward(const pplb200_rope_params* p, const void* query, const 
     if (rc != PPLB200_SUCCESS) {
         return rc;
     }
-    if (!query || !key || !seqstarts || !start_pos || !rotated_query || !rotated_key) {
-        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
-    }
+    // an empty batch is a no-op whatever the pointers are (empty tensors have none)
     if (p->batch == 0 || p->total_tokens == 0) {
         return PPLB200_SUCCESS;
+    }
+    if (!query || !key || !seqstarts || !start_pos || !rotated_query || !rotated_key) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
     }
     DeviceInfo di;
     rc = require_device(&di);
@@ -505,11 +511,12 @@ int pplb200_rope_kv_append_i8g8(const pplb200_rope_params* p, const pplb200_attn
         attn->batch != p->batch || attn->total_tokens != p->total_tokens) {
         return fail(PPLB200_INVALID_VALUE, "the two parameter blocks disagree on heads, head_dim, batch or tokens");
     }
-    if (!query || !key || !value || !seqstarts || !cachestarts || !start_pos || !rotated_query || !cache || !scale) {
-        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
-    }
+    // an empty batch is a no-op whatever the pointers are (empty tensors have none)
     if (p->batch == 0 || p->total_tokens == 0) {
         return PPLB200_SUCCESS;
+    }
+    if (!query || !key || !value || !seqstarts || !cachestarts || !start_pos || !rotated_query || !cache || !scale) {
+        return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
     }
     DeviceInfo di;
     rc = require_device(&di);

@@ -1,0 +1,71 @@
+"""Edge cases of the ragged batch on the GPU, against the oracle: empty sequences inside a batch, an empty
+batch, a single one-token sequence, and lengths beyond the max_seqlen / max_kvlen the caller announced."""
+import numpy as np
+import pytest
+
+from test_gpu_parity import _case_with_index, _spec, _t, run_case, torch_dev  # noqa: F401  (fixtures and helpers)
+
+pytestmark = pytest.mark.gpu
+
+
+def test_empty_prefill_sequences_inside_the_batch(orc, torch_dev, pkg):
+    """seqstarts with repeated entries: sequences of zero new tokens between real ones."""
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=8, num_kv_heads=2, head_dim=128, n_decode=2, kv_dist="list", kv_list=(17, 64),
+                 n_prefill=5, seed=41)
+    hc = workloads.host_case(spec)
+    idx = workloads.make_index([17, 64], [0, 5, 0, 130, 0])
+    hc = _case_with_index(hc, idx, spec)
+    run_case(orc, torch_dev, hc)
+
+
+def test_single_token_single_sequence(orc, torch_dev, pkg):
+    from ppl_nn_b200 import workloads
+    for lens in (([1], []), ([], [1])):
+        spec = _spec(num_heads=8, num_kv_heads=8, head_dim=64, n_decode=len(lens[0]), kv_dist="list",
+                     kv_list=tuple(lens[0]), n_prefill=len(lens[1]), seed=42)
+        hc = workloads.host_case(spec)
+        hc = _case_with_index(hc, workloads.make_index(*lens), spec)
+        run_case(orc, torch_dev, hc)
+
+
+def test_empty_batch_is_a_no_op(torch_dev, pkg):
+    import torch
+    from ppl_nn_b200 import ops
+    dev = torch_dev
+    op = ops.MultiHeadCacheAttention(ops.MultiHeadCacheAttentionParam(num_heads=8, num_kv_heads=2, head_dim=128,
+                                                                     num_layer=1, layer_idx=0, quant_bit=8))
+    z = lambda *shape, dt=torch.float16: torch.zeros(shape, dtype=dt, device=dev)
+    cache, scale = z(16, 1, 2, 2, 128, dt=torch.int8), z(16, 1, 2, 2, 16)
+    cache.fill_(7)
+    out = op.forward(z(0, 8, 128), z(0, 2, 128), z(0, 2, 128), z(1, dt=torch.int64), z(1, dt=torch.int64),
+                     z(0, dt=torch.int64), z(0, dt=torch.int64), 0, 0, 0, cache, scale)
+    torch.cuda.synchronize()
+    assert out.shape == (0, 8, 128) and bool((cache == 7).all())
+
+
+def test_lengths_beyond_the_announced_maximum_are_clamped_and_reported(orc, torch_dev, pkg, built_lib):
+    """max_kvlen / max_seqlen are host scalars the caller passes; a sequence that is longer is cut there and
+    the device status word says so (PPLB200_DEV_LENGTH_CLAMPED = 4), nothing is read out of bounds."""
+    import torch
+    from ppl_nn_b200 import ops, workloads
+    dev = torch_dev
+    spec = _spec(num_heads=8, num_kv_heads=2, head_dim=128, n_decode=2, kv_dist="list", kv_list=(100, 300),
+                 n_prefill=1, seed=43)
+    hc = workloads.host_case(spec)
+    idx = workloads.make_index([100, 300], [200])
+    hc = _case_with_index(hc, idx, spec)
+    err, op = run_case(orc, torch_dev, hc)          # the honest call first: clean status, parity
+    assert op.device_status() == 0
+    Hq, Hkv, Dh = 8, 2, 128
+    cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, Hkv, Dh)
+    cache = torch.zeros(cshape, dtype=torch.int8, device=dev)
+    scale = torch.zeros(sshape, dtype=torch.float16, device=dev)
+    args = (_t(hc.query, dev), _t(hc.current_key, dev), _t(hc.current_value, dev), _t(idx.seqstarts, dev),
+            _t(idx.kvstarts, dev), _t(idx.cachestarts, dev), _t(idx.start_pos, dev), idx.decoding_batches)
+    out = op.forward(*args, idx.max_seqlen, 128, cache, scale)      # max_kvlen too small for the second sequence
+    assert op.device_status() & 4
+    assert bool(torch.isfinite(out.float()).all())
+    out = op.forward(*args, 64, idx.max_kvlen, cache, scale)        # max_seqlen too small for the prefill sequence
+    assert op.device_status() & 4
+    assert bool(torch.isfinite(out[:idx.seqstarts[2] + 64].float()).all())

@@ -74,7 +74,8 @@ def run_case(orc, dev, hc, *, layout=0, num_layer=1, layer_idx=0, split_k=1, cac
     assert np.isfinite(got).all()
     err = np.abs(got - want.astype(np.float32))
     if check_attention:
-        per_seq = [float(err[idx.seqstarts[b]:idx.seqstarts[b + 1]].max()) for b in range(idx.batch)]
+        per_seq = [float(err[idx.seqstarts[b]:idx.seqstarts[b + 1]].max()) if idx.seqstarts[b + 1] > idx.seqstarts[b]
+                   else 0.0 for b in range(idx.batch)]
         worst = int(np.argmax(per_seq))
         assert err.max() <= MAX_ABS, (f"max-abs {err.max():.3e}; worst sequence {worst} kvlen "
                                       f"{int(idx.kvlens[worst])} seqlen {int(idx.seqlens[worst])}")
