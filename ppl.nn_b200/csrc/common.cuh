@@ -240,15 +240,19 @@ __device__ __forceinline__ void quant_group8(const uint4 in, uint2& codes, __hal
         constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
         const float r = __frcp_rn(s);
         uint32_t ub[8];
+        bool all_safe = true;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float qf = __fmul_rn(v[i], r);
             const float u = __fadd_rn(qf, kMagic);
             const float t = __fsub_rn(u, kMagic);  // rint(qf) for |qf| < 2^22
             // |qf| <= 127.4 also means that no clamp is needed; false for NaN
-            const bool safe = fabsf(qf) <= 127.4f && fabsf(__fsub_rn(qf, t)) < 0.499f;
+            all_safe = all_safe && fabsf(qf) <= 127.4f && fabsf(__fsub_rn(qf, t)) < 0.4999f;
             ub[i] = __float_as_uint(u);  // low mantissa byte = the code in two's complement
-            if (!safe) {
+        }
+        if (!all_safe) {  // rare (about one group in a thousand): redo the group with true divisions
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
                 ub[i] = static_cast<uint32_t>(quant_code_exact(v[i], s));
             }
         }

@@ -21,22 +21,29 @@ kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict
     const int group_shift = head_dim == 128 ? 4 : 3;
     const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
     const int32_t groups_per_token = 2 * groups_per_tensor_row;
+    const int32_t row_elems = num_kv_heads * head_dim;  // one token row of K (or V)
     for (WarpItems it(groups_per_token); it.tok < total_tokens; it.next()) {
-        // the payload loads go out before the lookups, which then overlap with them
+        // the payload loads go out before the lookups, which then overlap with them; the 64-bit part of every
+        // address is formed once per token, the rest is 32-bit arithmetic on the group index
+        const __half* k_tok = cur_k + it.tok * row_elems;
+        const __half* v_tok = cur_v + it.tok * row_elems;
         uint4 in[kChunks];
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
             const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
             in[c] = make_uint4(0u, 0u, 0u, 0u);
             if (g < groups_per_token) {
-                int kv, head, grp;
-                split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
-                const __half* src = (kv ? cur_v : cur_k) + (it.tok * num_kv_heads + head) * head_dim + grp * 8;
-                in[c] = *reinterpret_cast<const uint4*>(src);
+                // groups of a token row are laid out exactly like its channels: group r2 = channels 8 r2 ..
+                const bool is_v = g >= groups_per_tensor_row;
+                const int32_t r2 = g - (is_v ? groups_per_tensor_row : 0);
+                in[c] = *reinterpret_cast<const uint4*>((is_v ? v_tok : k_tok) + r2 * 8);
             }
         }
         const int32_t b = warp_find_segment(seqstarts, batch, it.tok, lane);
         const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (it.tok - seqstarts[b]));
+        const int64_t row_off = row * geom.stride_s + geom.layer_idx * geom.stride_l;
+        int8_t* c_row = cache + row_off;
+        __half* s_row = scale + (row_off >> 3);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c) {
             const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
@@ -46,9 +53,9 @@ kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict
             if (g < groups_per_token) {
                 int kv, head, grp;
                 split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
-                const int64_t off = cache_offset(geom, row, kv, head);
-                *reinterpret_cast<uint2*>(cache + off + grp * 8) = codes;
-                scale[(off >> 3) + grp] = s16;
+                const int64_t off = kv * geom.stride_kv + head * geom.stride_h + grp * 8;
+                *reinterpret_cast<uint2*>(c_row + off) = codes;
+                s_row[off >> 3] = s16;
             }
         }
     }
