@@ -236,7 +236,9 @@ int pplb200_rope_forward(const pplb200_rope_params* p, const void* query, const 
                          void* rotated_key, void* stream);
 
 /*
- * The rotary embedding and the KeyValueCache write side in one kernel: rotates the query into
+ * The rotary embedding and the KeyValueCache write side in one call (one kernel for the small batches of
+ * decode steps; rotation and append kernels back to back for batches of 1024 tokens and more when
+ * `rotated_key` is given, which is faster there): rotates the query into
  * `rotated_query`, rotates the key, rounds it to fp16 (written to `rotated_key` unless that is null),
  * quantises it and `value` and appends both to the cache.  The cache rows are bit-identical to
  * pplb200_rope_forward followed by pplb200_kv_append_i8g8; a following pplb200_mhca_forward is called with
