@@ -511,8 +511,9 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 // O += P(j-1) V(j-1)
                 const int jp = j - 1;
                 const int s = jp % kVStages;
-                ok = wait_or_abort(&bars.p_full[jp & 1], (jp >> 1) & 1, abort_flag, a.status, kDevMmaTimeout) &&
-                     wait_or_abort(&bars.v_full[s], (jp / kVStages) & 1, abort_flag, a.status, kDevTmaTimeout);
+                // V landed long ago; testing it first keeps it off the path from "P is ready" to the issue
+                ok = wait_or_abort(&bars.v_full[s], (jp / kVStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
+                     wait_or_abort(&bars.p_full[jp & 1], (jp >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                 if (!ok) {
                     break;
                 }
@@ -545,6 +546,15 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         float m_ref = kNegBig, l_sum = 0.0f;
         bool ok = true;
         for (int j = 0; ok && j < n_kv; ++j) {
+            // This tile's P buffer is free once the P V of the tile before the previous one has completed.  That
+            // happened long before the scores of this tile arrive, so the test comes first and costs nothing
+            // on the path from "S is ready" to the exponentials.
+            if (j >= 2) {
+                ok = wait_or_abort(&bars.pv_done[j & 1], ((j - 2) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                if (!ok) {
+                    break;
+                }
+            }
             ok = wait_or_abort(&bars.s_full, j & 1, abort_flag, a.status, kDevMmaTimeout);
             if (!ok) {
                 break;
@@ -614,14 +624,6 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     }
                     tmem_wait_st();
                 }
-            }
-            // this tile's P buffer is free once the P V of the tile before the previous one has completed
-            if (j >= 2) {
-                ok = wait_or_abort(&bars.pv_done[j & 1], ((j - 2) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
-                if (!ok) {
-                    break;
-                }
-                tc_fence_after();
             }
             // P = exp2(s * scale - m_ref) as packed fp16 into TMEM: column c of the buffer = kv columns 2c, 2c+1
             // a row that sees no kv position at all gets zero weights (exp2(-inf)), hence a zero output row
