@@ -860,7 +860,13 @@ static int map_order_kind(const CacheMapOrder& od) {
 template <int DH, int ORDER>
 static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t grid, cudaStream_t stream) {
     using T = Traits<DH>;
-    static bool attr_set = false;  // per template instance; setting it twice is harmless
+    // the attribute belongs to the (kernel, device) pair: remembered per template instance and device
+    static bool attr_set_on[kMaxDevices] = {};
+    int dev_id = 0;
+    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= kMaxDevices) {
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    bool& attr_set = attr_set_on[dev_id];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(decode_splitk_kernel<DH, ORDER>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);

@@ -11,6 +11,8 @@ namespace pplb200 {
 
 struct CacheGeom;
 
+constexpr int kMaxDevices = 64;  // devices per process that per-device launch state is kept for
+
 // cudaGetLastError() after a launch -> PPLB200_SUCCESS / PPLB200_DEVICE_RUNTIME_ERROR (logged to
 // stderr with the kernel name), and bumps the launch counter.  Mirrors what ppl.nn does after every
 // kernel (src/ppl/nn/engines/llm_cuda/kernel.cc:179-185).

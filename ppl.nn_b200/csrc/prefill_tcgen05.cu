@@ -814,7 +814,13 @@ static int launch_attention_core(const void* query, const void* k_src, const voi
     a.group = num_heads / num_kv_heads;
     a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
 
-    static bool attr_set = false;
+    // the attribute belongs to the (kernel, device) pair: remembered per template instance and device
+    static bool attr_set_on[kMaxDevices] = {};
+    int dev_id = 0;
+    if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= kMaxDevices) {
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    bool& attr_set = attr_set_on[dev_id];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              T::kSmemBytes);

@@ -69,3 +69,21 @@ def test_lengths_beyond_the_announced_maximum_are_clamped_and_reported(orc, torc
     out = op.forward(*args, 64, idx.max_kvlen, cache, scale)        # max_seqlen too small for the prefill sequence
     assert op.device_status() & 4
     assert bool(torch.isfinite(out[:idx.seqstarts[2] + 64].float()).all())
+
+
+def test_second_device_in_the_same_process(orc, torch_dev, pkg):
+    """Per-device launch state (function attributes, device properties): a process that has used GPU 0 runs the
+    same kernels on GPU 1.  Needs two GPUs."""
+    import torch
+    from ppl_nn_b200 import workloads
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    hc = workloads.host_case(workloads.SPECS["cfg1_tiny"])
+    run_case(orc, torch.device("cuda:0"), hc)
+    spec = _spec(num_heads=8, num_kv_heads=2, head_dim=128, n_decode=2, kv_dist="list", kv_list=(40, 300), n_prefill=1,
+                 seed=44)
+    hc2 = _case_with_index(workloads.host_case(spec), workloads.make_index([40, 300], [150]), spec)
+    with torch.cuda.device(1):
+        run_case(orc, torch.device("cuda:1"), hc)
+        run_case(orc, torch.device("cuda:1"), hc2)
+    torch.cuda.set_device(0)
