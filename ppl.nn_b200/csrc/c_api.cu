@@ -120,8 +120,8 @@ static int validate(const pplb200_attn_params* p) {
         return fail(PPLB200_INVALID_VALUE, "layer_idx out of range");
     }
     if (p->batch < 0 || p->decoding_batches < 0 || p->decoding_batches > p->batch || p->total_tokens < 0 ||
-        p->batch > 0x7fffffff) {
-        return fail(PPLB200_INVALID_VALUE, "batch / decoding_batches / total_tokens out of range");
+        p->batch > 0x7fffffff || p->total_tokens > 0x7fffffff || p->max_seqlen < 0 || p->max_kvlen < 0) {
+        return fail(PPLB200_INVALID_VALUE, "batch / decoding_batches / total_tokens / max lengths out of range");
     }
     if (p->max_tokens <= 0 || p->max_tokens > 0x7fffffff) {
         return fail(PPLB200_INVALID_VALUE, "max_tokens (cache rows) out of range");
