@@ -561,13 +561,15 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 float s1 = sacc[1] * a.scale_log2;  // token g,   head 2t+1
                 float s2 = sacc[2] * a.scale_log2;  // token g+8, head 2t
                 float s3 = sacc[3] * a.scale_log2;  // token g+8, head 2t+1
-                if (g >= nvalid) {
-                    s0 = kNegBig;
-                    s1 = kNegBig;
-                }
-                if (g + 8 >= nvalid) {
-                    s2 = kNegBig;
-                    s3 = kNegBig;
+                if (nvalid < kTileTok) {  // only the last tile of a sequence has rows past its end
+                    if (g >= nvalid) {
+                        s0 = kNegBig;
+                        s1 = kNegBig;
+                    }
+                    if (g + 8 >= nvalid) {
+                        s2 = kNegBig;
+                        s3 = kNegBig;
+                    }
                 }
                 {
                     float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
