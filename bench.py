@@ -155,35 +155,48 @@ class ClockSampler:
 # ------------------------------------------------------------------------------------------------
 # CPU arm: the oracle port on the host cores
 # ------------------------------------------------------------------------------------------------
-def cpu_time_sample(spec, num_seqs: int, target_seconds: float = 12.0):
+def cpu_time_sample(spec, num_seqs: int, target_seconds: float = 12.0, steps: int | None = None, warmup: int = 1):
     """Time the CPU restatement on the first `num_seqs` decode sequences of `spec` (same seeded
     lengths).  Cache contents are random valid codes/scales: the arithmetic does not depend on
-    them.  Returns (tokens_per_s, cores, seconds_per_step, steps, sample_text)."""
+    them.  With `steps` the run is exactly `warmup` + `steps` passes and the sample shrinks (fewer
+    sequences) until that fits about a minute and a half; without it the number of passes is chosen to
+    fill `target_seconds`.  Returns (tokens_per_s, cores, seconds_per_step, steps, sample_text)."""
     from ppl_nn_b200 import workloads
     om = entry.load_oracle()
     orc = om.COracle()
-    kv, _ = workloads.draw_lengths(spec)
-    kv = kv[:num_seqs]
-    idx = workloads.make_index(kv, [])
+    kv_all, _ = workloads.draw_lengths(spec)
     rng = np.random.default_rng(99)
     Hq, Hkv, Dh = spec.num_heads, spec.num_kv_heads, spec.head_dim
-    cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, Hkv, Dh)
-    cache = rng.integers(-127, 128, size=cshape, dtype=np.int8)
-    scale = rng.uniform(0.01, 0.05, size=sshape).astype(np.float16)
-    T = idx.total_tokens
-    q = rng.standard_normal((T, Hq, Dh), dtype=np.float32).astype(np.float16)
-    ck = rng.standard_normal((T, Hkv, Dh), dtype=np.float32).astype(np.float16)
-    cv = rng.standard_normal((T, Hkv, Dh), dtype=np.float32).astype(np.float16)
-    d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=idx.batch, decoding_batches=idx.batch,
-                 max_tokens=idx.max_tokens)
 
-    def step():
-        return orc.mhca(d, q, ck, cv, idx.seqstarts, idx.cachestarts, idx.start_pos, cache, scale)
+    def make(n):
+        kv = kv_all[:n]
+        idx = workloads.make_index(kv, [])
+        cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, Hkv, Dh)
+        cache = rng.integers(-127, 128, size=cshape, dtype=np.int8)
+        scale = rng.uniform(0.01, 0.05, size=sshape).astype(np.float16)
+        T = idx.total_tokens
+        q = rng.standard_normal((T, Hq, Dh), dtype=np.float32).astype(np.float16)
+        ck = rng.standard_normal((T, Hkv, Dh), dtype=np.float32).astype(np.float16)
+        cv = rng.standard_normal((T, Hkv, Dh), dtype=np.float32).astype(np.float16)
+        d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=idx.batch, decoding_batches=idx.batch,
+                     max_tokens=idx.max_tokens)
+        return kv, idx, (lambda: orc.mhca(d, q, ck, cv, idx.seqstarts, idx.cachestarts, idx.start_pos, cache, scale))
 
+    kv, idx, step = make(num_seqs)
     t0 = time.perf_counter()
-    step()  # warm-up, also tells us how long a step is
+    step()  # first pass: warms up, and tells us how long a step is
     one = time.perf_counter() - t0
-    steps = max(1, min(50, int(target_seconds / max(one, 1e-4))))
+    if steps is None:
+        steps = max(1, min(50, int(target_seconds / max(one, 1e-4))))
+    else:
+        budget = 90.0
+        done = 1
+        if one * (steps + warmup) > budget and num_seqs > 4:
+            num_seqs = max(4, int(num_seqs * budget / (one * (steps + warmup))))
+            kv, idx, step = make(num_seqs)
+            done = 0
+        for _ in range(max(warmup - done, 0)):
+            step()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
@@ -206,10 +219,10 @@ def run_reference_arm(args, rank: int):
     # one "step" of this arm = one pass over the bounded sample; K steps after W warm-ups
     om = entry.load_oracle()
     om.build()
-    tok_s, cores, per_step, steps, sample = cpu_time_sample(spec, nseq, target_seconds=max(2.0, 0.5 * args.steps))
+    tok_s, cores, per_step, steps, sample = cpu_time_sample(spec, nseq, steps=args.steps, warmup=max(args.warmup, 1))
     line = {
         "impl": "reference", "metric": METRIC, "value": tok_s, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": 1, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
+        "steps": steps, "warmup": max(args.warmup, 1), "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp16 in/out, int8 cache, fp32 accumulate", "data": "synthetic",
         "config": {"workload": spec.name, "sample": sample},
         "cpu_baseline": {"value": tok_s, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
