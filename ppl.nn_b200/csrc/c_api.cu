@@ -1,5 +1,6 @@
 // extern "C" layer: argument validation, workspace layout and kernel sequencing for the two operators.
-// Nothing here allocates device memory or synchronises (except pplb200_mhca_device_status).
+// Nothing here allocates device memory or synchronises, except pplb200_mhca_device_status (waits for the
+// stream) and pplb200_profile_read (waits for the recorded events).
 #include <cuda_runtime.h>
 #include <stdio.h>
 
@@ -28,7 +29,7 @@ int check_launch(const char* kernel_name) {
 // ---- optional per-kernel event timing ------------------------------------------------------------
 struct ProfileState {
     std::mutex mu;
-    bool enabled = false;
+    std::atomic<bool> enabled{false};
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending[PPLB200_KERNEL_FAMILIES];
 };
 static ProfileState& profile_state() {
@@ -38,12 +39,17 @@ static ProfileState& profile_state() {
 
 KernelTimer::KernelTimer(int family, cudaStream_t stream) : stream_(stream), stop_(nullptr) {
     ProfileState& ps = profile_state();
-    if (!ps.enabled) {
+    if (!ps.enabled.load(std::memory_order_relaxed)) {
         return;
     }
     cudaEvent_t start = nullptr;
-    if (cudaEventCreate(&start) != cudaSuccess || cudaEventCreate(&stop_) != cudaSuccess) {
+    if (cudaEventCreate(&start) != cudaSuccess) {
         (void)cudaGetLastError();
+        return;
+    }
+    if (cudaEventCreate(&stop_) != cudaSuccess) {
+        (void)cudaGetLastError();
+        cudaEventDestroy(start);
         stop_ = nullptr;
         return;
     }
@@ -447,8 +453,8 @@ static int validate_rope(const pplb200_rope_params* p) {
     if (p->scaling_type == 2 && (p->max_position_embeddings <= 0 || rot <= 2)) {
         return fail(PPLB200_INVALID_VALUE, "dynamic scaling needs max_position_embeddings > 0 and rotary_dim > 2");
     }
-    if (p->batch < 0 || p->total_tokens < 0 || p->batch > 0x7fffffff) {
-        return fail(PPLB200_INVALID_VALUE, "negative size");
+    if (p->batch < 0 || p->total_tokens < 0 || p->batch > 0x7fffffff || p->total_tokens > 0x7fffffff) {
+        return fail(PPLB200_INVALID_VALUE, "batch / total_tokens out of range");
     }
     return PPLB200_SUCCESS;
 }
@@ -594,8 +600,7 @@ uint64_t pplb200_launch_count(void) {
 
 int pplb200_profile_enable(int enable) {
     ProfileState& ps = profile_state();
-    std::lock_guard<std::mutex> lock(ps.mu);
-    ps.enabled = enable != 0;
+    ps.enabled.store(enable != 0, std::memory_order_relaxed);
     return PPLB200_SUCCESS;
 }
 

@@ -57,6 +57,26 @@ RetCode RequireOnDevice(const TensorImpl* t, const Device* dev) {
     return RC_SUCCESS;
 }
 
+// The kernels index [tokens, heads, head_dim] tensors with the attribute values, so a tensor of another
+// shape would be read out of bounds; the reference leaves this to its kernel library.
+RetCode RequireTokenTensor(const TensorImpl* t, int64_t tokens, int64_t heads, int64_t head_dim) {
+    const TensorShape& s = *t->GetShape();
+    if (s.GetDimCount() != 3 || (tokens >= 0 && s.GetDim(0) != tokens) || s.GetDim(1) != heads || s.GetDim(2) != head_dim) {
+        LOG(ERROR) << "tensor[" << t->GetName() << "] must be [tokens, " << heads << ", " << head_dim << "]";
+        return RC_INVALID_VALUE;
+    }
+    return RC_SUCCESS;
+}
+
+RetCode RequireIndexTensor(const TensorImpl* t, int64_t min_rows) {
+    const TensorShape& s = *t->GetShape();
+    if (s.GetDataType() != DATATYPE_INT64 || s.GetDimCount() < 1 || s.GetDim(0) < min_rows) {
+        LOG(ERROR) << "tensor[" << t->GetName() << "] must be int64 with at least " << min_rows << " rows";
+        return RC_INVALID_VALUE;
+    }
+    return RC_SUCCESS;
+}
+
 RetCode ReallocOn(TensorImpl* t, Device* dev) {
     t->SetDevice(dev);
     const RetCode rc = t->ReallocBuffer();
@@ -137,6 +157,23 @@ RetCode DynamicBatchingMultiHeadCacheAttentionKernel::DoExecute(KernelExecContex
         return RC_UNSUPPORTED;
     }
 
+    {
+        const int64_t tokens = query->GetShape()->GetDimCount() > 0 ? query->GetShape()->GetDim(0) : 0;
+        const int64_t batch = start_pos->GetShape()->GetDimCount() > 0 ? start_pos->GetShape()->GetDim(0) : 0;
+        if ((rc = RequireTokenTensor(query, -1, param_->num_heads, param_->head_dim)) != RC_SUCCESS ||
+            (rc = RequireTokenTensor(current_key, tokens, param_->num_kv_heads, param_->head_dim)) != RC_SUCCESS ||
+            (rc = RequireTokenTensor(current_value, tokens, param_->num_kv_heads, param_->head_dim)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(start_pos, 0)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(seqstarts, batch + 1)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(kvstarts, batch + 1)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(cachestarts, batch)) != RC_SUCCESS) {
+            return rc;
+        }
+        if (cache->GetShape()->GetDimCount() != 5 || scale->GetShape()->GetDimCount() != 5) {
+            LOG(ERROR) << "cache and scale must be 5-d tensors";
+            return RC_INVALID_VALUE;
+        }
+    }
     for (TensorImpl* t : {query, current_key, current_value, seqstarts, kvstarts, cachestarts, start_pos, cache, scale}) {
         if ((rc = RequireOnDevice(t, GetCudaDevice())) != RC_SUCCESS) {
             return rc;
@@ -265,6 +302,16 @@ RetCode DynamicBatchingMultiHeadAttentionKernel::DoExecute(KernelExecContext* ct
         LOG(ERROR) << "currently only support fp16";
         return RC_UNSUPPORTED;
     }
+    {
+        const int64_t kv_tokens = key->GetShape()->GetDimCount() > 0 ? key->GetShape()->GetDim(0) : 0;
+        if ((rc = RequireTokenTensor(query, -1, param_->num_heads, param_->head_dim)) != RC_SUCCESS ||
+            (rc = RequireTokenTensor(key, -1, param_->num_kv_heads, param_->head_dim)) != RC_SUCCESS ||
+            (rc = RequireTokenTensor(value, kv_tokens, param_->num_kv_heads, param_->head_dim)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(seqstarts, 1)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(kvstarts, seqstarts->GetShape()->GetDim(0))) != RC_SUCCESS) {
+            return rc;
+        }
+    }
     for (TensorImpl* t : {query, key, value, seqstarts, kvstarts}) {
         if ((rc = RequireOnDevice(t, GetCudaDevice())) != RC_SUCCESS) {
             return rc;
@@ -366,6 +413,18 @@ RetCode DynamicBatchingRotaryPositionEmbeddingKernel::DoExecute(KernelExecContex
     if (query->GetShape()->GetDataType() != DATATYPE_FLOAT16) {
         LOG(ERROR) << "currently only support fp16";
         return RC_UNSUPPORTED;
+    }
+    {
+        const TensorShape& qs = *query->GetShape();
+        const TensorShape& ks = *key->GetShape();
+        if (qs.GetDimCount() != 3 || ks.GetDimCount() != 3 || ks.GetDim(0) != qs.GetDim(0) || ks.GetDim(2) != qs.GetDim(2)) {
+            LOG(ERROR) << "query and key must be [tokens, heads, head_dim] with the same tokens and head_dim";
+            return RC_INVALID_VALUE;
+        }
+        if ((rc = RequireIndexTensor(start_pos, 0)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(seqstarts, start_pos->GetShape()->GetDim(0) + 1)) != RC_SUCCESS) {
+            return rc;
+        }
     }
     for (TensorImpl* t : {query, key, seqstarts, start_pos}) {
         if ((rc = RequireOnDevice(t, GetCudaDevice())) != RC_SUCCESS) {
@@ -502,6 +561,25 @@ RetCode DynamicBatchingKeyValueCacheKernel::DoExecute(KernelExecContext* ctx) {
         LOG(ERROR) << "currently only support num_repeat == 1";
         return RC_UNSUPPORTED;
     }
+    {
+        const TensorShape& cs = *current_key->GetShape();
+        if (cs.GetDimCount() != 3) {
+            LOG(ERROR) << "current_key must be [tokens, num_kv_heads, head_dim]";
+            return RC_INVALID_VALUE;
+        }
+        const int64_t batch = start_pos->GetShape()->GetDimCount() > 0 ? start_pos->GetShape()->GetDim(0) : 0;
+        if ((rc = RequireTokenTensor(current_value, cs.GetDim(0), cs.GetDim(1), cs.GetDim(2))) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(start_pos, 0)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(seqstarts, batch + 1)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(kvstarts, batch + 1)) != RC_SUCCESS ||
+            (rc = RequireIndexTensor(cachestarts, batch)) != RC_SUCCESS) {
+            return rc;
+        }
+        if (cache->GetShape()->GetDimCount() != 5 || scale->GetShape()->GetDimCount() != 5) {
+            LOG(ERROR) << "cache and scale must be 5-d tensors";
+            return RC_INVALID_VALUE;
+        }
+    }
     for (TensorImpl* t : {current_key, current_value, seqstarts, kvstarts, cachestarts, start_pos, cache, scale}) {
         if ((rc = RequireOnDevice(t, GetCudaDevice())) != RC_SUCCESS) {
             return rc;
@@ -513,10 +591,6 @@ RetCode DynamicBatchingKeyValueCacheKernel::DoExecute(KernelExecContext* ctx) {
     if (ks.GetDataType() != DATATYPE_FLOAT16) {
         LOG(ERROR) << "currently only support fp16";
         return RC_UNSUPPORTED;
-    }
-    if (ks.GetDimCount() != 3) {
-        LOG(ERROR) << "current_key must be [tokens, num_kv_heads, head_dim]";
-        return RC_INVALID_VALUE;
     }
 
     pplb200_attn_params p;

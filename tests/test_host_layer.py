@@ -158,6 +158,27 @@ def test_mhca_guards(host, engine, attrs, kw, expect):
     assert rc == expect
 
 
+@pytest.mark.parametrize("which,shape,dtype", [
+    (0, (4, 8, 64), np.float16),      # query with another head_dim than the attribute
+    (0, (4, 1024), np.float16),       # query flattened to 2-d
+    (1, (4, 4, 128), np.float16),     # current_key with another head count
+    (2, (3, 2, 128), np.float16),     # current_value with fewer tokens than query
+    (3, (4,), np.int64),              # seqstarts shorter than batch + 1
+    (4, (5,), np.int32),              # kvstarts not int64
+    (5, (3,), np.int64),              # cachestarts shorter than batch
+    (10, (64 * 2, 2, 2, 128), np.int8),  # cache not 5-d
+])
+def test_mhca_rejects_tensors_the_kernels_would_overrun(host, engine, which, shape, dtype):
+    op = host.Op(engine, "MultiHeadCacheAttention", MHCA_ATTRS)
+    ins, outs, keep = _mhca_inputs(host)
+    t, _ = host.describe(np.zeros(shape, dtype=dtype))
+    t.on_host = 0
+    t.data = 4096
+    ins[which] = t
+    rc, _ = op.run_raw(ins, outs)
+    assert rc == "RC_INVALID_VALUE"
+
+
 def test_mhca_empty_attn_mask_counts_as_absent_and_output_takes_query_shape(host, engine):
     import torch
     if torch.cuda.is_available():
