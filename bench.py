@@ -244,6 +244,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
     ap.add_argument("--layout", type=int, default=0, choices=[0, 3])
+    ap.add_argument("--page-size", type=int, default=0, help="paged cache (cache_mode 1) with pages of this many tokens")
     ap.add_argument("--seq-scale", type=float, default=1.0, help="fraction of the sequences (profiling captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -280,12 +281,13 @@ def main():
     spec = workloads.SPECS[args.workload]
     if args.seq_scale != 1.0:
         spec = workloads.scaled(spec, seqs=args.seq_scale)
-    dc = workloads.device_case(spec, dev, rank=rank, world=world, layout=args.layout)
+    dc = workloads.device_case(spec, dev, rank=rank, world=world, layout=args.layout, page_size=args.page_size)
     idx = dc.index
     nd = idx.decoding_batches
+    paging = dict(cache_mode=1, page_size=args.page_size) if args.page_size else {}
     op = ops.MultiHeadCacheAttention(
         ops.MultiHeadCacheAttentionParam(num_heads=dc.num_heads, num_kv_heads=dc.num_kv_heads, head_dim=spec.head_dim,
-                                         num_layer=1, layer_idx=0, quant_bit=8, cache_layout=args.layout))
+                                         num_layer=1, layer_idx=0, quant_bit=8, cache_layout=args.layout, **paging))
     out = torch.empty_like(dc.query)
     fwd_args = (dc.query, dc.current_key, dc.current_value, dc.seqstarts, dc.kvstarts, dc.cachestarts, dc.start_pos,
                 nd, idx.max_seqlen, idx.max_kvlen, dc.cache, dc.scale)
@@ -400,7 +402,7 @@ def main():
         eng = hostapi.Engine(local_rank, torch.cuda.current_stream().cuda_stream)
         hop = hostapi.Op(eng, "MultiHeadCacheAttention",
                          dict(num_heads=dc.num_heads, num_kv_heads=dc.num_kv_heads, head_dim=spec.head_dim, num_layer=1,
-                              layer_idx=0, quant_bit=8, quant_group=8, cache_layout=args.layout))
+                              layer_idx=0, quant_bit=8, quant_group=8, cache_layout=args.layout, **paging))
         hin = [hostapi.describe(x)[0] for x in
                (devbuf["query"], devbuf["current_key"], devbuf["current_value"], devbuf["seqstarts"],
                 devbuf["kvstarts"], devbuf["cachestarts"], devbuf["start_pos"])]
@@ -462,7 +464,7 @@ def main():
             "config": {"workload": spec.name, "num_heads": spec.num_heads, "num_kv_heads": spec.num_kv_heads,
                        "head_dim": spec.head_dim, "decode_sequences": nd, "kv_tokens": int(idx.kvlens[:nd].sum()),
                        "prefill_sequences": idx.batch - nd, "prefill_tokens": int(idx.seqlens[nd:].sum()),
-                       "cache_layout": args.layout, "sharding": f"kv-heads/{world}",
+                       "cache_layout": args.layout, "page_size": args.page_size, "sharding": f"kv-heads/{world}",
                        "l2": "no flush: the per-GPU cache working set is far larger than the 126 MB L2"
                              if algo_bytes > 4 * 126e6 else
                              "no flush: the step is compute-bound prefill" if nd == 0 else

@@ -12,10 +12,12 @@
 //     end in the middle of a segment; such pieces go to the workspace as fp32 partials (at most two
 //     per range) and a second-pass kernel merges them.  Pieces that cover a whole segment are written
 //     as fp16 output directly.
-//   * The heads are dealt round-robin into `head_lanes` (4, 2 or 1) classes; the 4 warps of a CTA take
+//   * The heads are dealt round-robin into `head_lanes` (8, 4, 2 or 1) classes; the 8 warps of a CTA take
 //     the same range of different classes, i.e. adjacent heads of the same token rows, so that in the
-//     token-major cache layout the CTA streams 4 x 128 contiguous bytes per row (with fewer classes
-//     the remaining warps take the next range of the same class).
+//     token-major cache layout the CTA streams 8 x 128 contiguous bytes per row (with fewer classes
+//     the remaining warps take the next ranges of the same class).  Where it pays (see
+//     want_lockstep) the warps that share a range also meet at a named barrier after every tile, which
+//     keeps their requests to neighbouring addresses together in time.
 //   * Every warp is an independent worker with its own 2-stage pipeline.  Per tile (5 KB at head_dim
 //     128) one lane issues two bulk-tensor (TMA) copies, K codes and V codes, and all lanes together
 //     copy the two small scale tiles with one 16-byte cp.async each (a TMA copy costs the warp tens
@@ -33,6 +35,7 @@
 // Every wait on an mbarrier is bounded; on a timeout the warp records a status code, stops
 // waiting and finishes (with wrong numbers, flagged) instead of hanging.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <cub/block/block_scan.cuh>
 
@@ -46,19 +49,18 @@ namespace {
 
 // Tuning knobs (compile-time).  Measured on B200 with the LLaMA-2-7B decode workload: throughput in the
 // token-major cache layout grows with the number of resident warps (each warp's row sequence is served
-// by few DRAM banks at a time), not with the depth of its pipeline, so 16 warps x 2 stages beat
-// 12 x 3 and 8 x 4 at equal bytes in flight; 126 registers per thread is what 16 warps allow.
+// by few DRAM banks at a time), not with the depth of its pipeline, so 16 warps x 2 stages per SM beat
+// 12 x 3 and 8 x 4 at equal bytes in flight; 128 registers per thread is what 16 warps allow.  The 16
+// warps are 2 CTAs of 8: eight head lanes per CTA read 1 KB of every token row together, 3-10 % faster
+// than 4 CTAs of 4 on every workload and cache layout tried, and within 2 % of 1 CTA of 16.
 #ifndef PPLB200_DECODE_WARPS
-#define PPLB200_DECODE_WARPS 4
+#define PPLB200_DECODE_WARPS 8
 #endif
 #ifndef PPLB200_DECODE_STAGES
 #define PPLB200_DECODE_STAGES 2
 #endif
 #ifndef PPLB200_DECODE_CTAS
-#define PPLB200_DECODE_CTAS 4
-#endif
-#ifndef PPLB200_DECODE_LOCKSTEP
-#define PPLB200_DECODE_LOCKSTEP 0
+#define PPLB200_DECODE_CTAS 2
 #endif
 
 constexpr int kTileTok = 16;
@@ -112,6 +114,7 @@ struct DecodeArgs {
     int32_t head_lanes;   // head classes = warps of a CTA that share a range
     int32_t class_heads;  // virtual heads per class: num_vheads / head_lanes
     int32_t layer_idx;
+    int32_t lockstep;     // 1: the warps that share a range synchronise after every tile
     CacheMapOrder order;
     const __half* scale;  // the scale tensor (copied with cp.async, addressed with the cache strides / 8)
     int64_t max_tokens;
@@ -362,6 +365,7 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
     const bool paged = a.geom.cache_mode != 0;
     const int octets = a.octets;
     const int head_lanes = a.head_lanes;
+    const bool lockstep = a.lockstep != 0;
     const int layer = a.layer_idx;
 
     auto load_seq = [&](Cursor& c) {  // per-sequence fields
@@ -661,9 +665,9 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                     }
                 }
 
-#if PPLB200_DECODE_LOCKSTEP
-                __syncthreads();
-#endif
+                if (lockstep) {  // the warps that share this range (same tile count) meet after every tile
+                    asm volatile("bar.sync %0, %1;" ::"r"(1 + sub), "r"(head_lanes * 32) : "memory");
+                }
                 __syncwarp();  // every lane has read this stage: it may be refilled
                 if (++c_stage == kStages) {
                     c_stage = 0;
@@ -886,6 +890,26 @@ static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t
     return check_launch("decode_splitk_kernel");
 }
 
+// Whether the warps that share a range run in lockstep (a barrier per tile).  Measured on B200, 8 head
+// lanes: with a multi-layer token-major cache or the head-major layout the lockstep raises the decode
+// bandwidth by 5-7 % (6.25 -> 6.57 TB/s with 8 layers, 6.25 -> 6.69 TB/s head-major, LLaMA-2-7B decode
+// workload); where the token rows of the layer lie back to back (one layer, token-major) it costs 3-4 %.
+// PPLB200_DECODE_LOCKSTEP=0|1 in the environment overrides the rule (tuning only).
+static bool want_lockstep(const pplb200_attn_params& p, const DecodePlan& plan) {
+    if (plan.head_lanes <= 1) {
+        return false;
+    }
+    static const int forced = [] {
+        const char* e = getenv("PPLB200_DECODE_LOCKSTEP");
+        return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1;
+    }();
+    if (forced >= 0) {
+        return forced == 1;
+    }
+    const bool rows_back_to_back = p.cache_stride_s == 2 * static_cast<int64_t>(p.num_kv_heads) * p.head_dim;
+    return !rows_back_to_back;
+}
+
 template <int DH>
 static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan,
                             const void* query, const int64_t* seqstarts, const int64_t* cachestarts,
@@ -931,6 +955,7 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.head_lanes = plan.head_lanes;
     a.class_heads = static_cast<int32_t>(plan.class_heads);
     a.layer_idx = p.layer_idx;
+    a.lockstep = want_lockstep(p, plan) ? 1 : 0;
     a.order = order;
     a.scale = static_cast<const __half*>(scale);
     a.max_tokens = p.max_tokens;

@@ -53,10 +53,16 @@ def _check_sample(orc, dc, spec, out, seqs):
     cache = np.zeros(cshape, dtype=np.int8)
     scale = np.zeros(sshape, dtype=np.float16)
     gpu_cache_rows, gpu_scale_rows = [], []
+    def rows(t, r0, n):
+        """Rows r0 .. r0+n of the op's layer as (n, 1, 2, H, X), whatever the layout and layer count."""
+        if dc.layout == 0:  # (MaxT, L, 2, H, X)
+            return t[r0:r0 + n, dc.layer_idx][:, None].cpu().numpy()
+        return t[dc.layer_idx, :, :, r0:r0 + n].permute(2, 0, 1, 3)[:, None].contiguous().cpu().numpy()  # (L, 2, H, MaxT, X)
+
     for i, b in enumerate(seqs):
         r0, n = int(idx.cachestarts[b]), int(kvl[i])
-        c = dc.cache[r0:r0 + n].cpu().numpy()
-        s = dc.scale[r0:r0 + n].cpu().numpy()
+        c = rows(dc.cache, r0, n)
+        s = rows(dc.scale, r0, n)
         cache[sub.cachestarts[i]:sub.cachestarts[i] + n] = c
         scale[sub.cachestarts[i]:sub.cachestarts[i] + n] = s
         gpu_cache_rows.append(c)
@@ -112,6 +118,27 @@ def test_full_size_sampled_sequences_match_the_oracle(orc, dev, pkg, name, k_dec
         diff = (other - ref).abs()
         assert float(diff.max()) <= MAX_ABS and float(diff.mean()) <= MEAN_ABS, (name, mode)
     del dc, out
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("layout", [0, 3])
+def test_cache_offsets_beyond_4_gib(orc, dev, pkg, layout):
+    """The last layer of a 32-layer cache of 80 k token rows: 5.2 GB of codes, so the rows of that layer lie
+    beyond 2^32 bytes in either layout (layout 0: row stride 64 KiB; layout 3: layer stride 164 MB).  Sampled
+    sequences against the oracle, and no other layer of the cache may have been written."""
+    import torch
+    from ppl_nn_b200 import workloads
+    spec = workloads.Spec("wide_cache", 32, 8, 128, 48, 1024, 2304, seed=9)
+    L = 32
+    dc = workloads.device_case(spec, dev, layout=layout, num_layer=L, layer_idx=L - 1)
+    assert dc.cache.numel() > (1 << 32)
+    op = _op(dc, spec)
+    out = _forward(op, dc)
+    assert op.device_status() == 0
+    _check_sample(orc, dc, spec, out, _sample(dc.index, np.random.default_rng(3), 3))
+    other = dc.cache[:, :L - 1] if layout == 0 else dc.cache[:L - 1]
+    assert not bool(other.any())
+    del dc, out, other
     torch.cuda.empty_cache()
 
 
