@@ -51,8 +51,8 @@ FALLBACK_HBM_GBS = 6650.0
 
 # DRAM bytes moved by decode_splitk_kernel per algorithmic byte, from the ncu capture summarised in
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes of the captured
-# launch): 692.57 MB + 3.97 MB for 690.86 MB (profiles/decode_splitk_kernel_cfg2_eighth.md).
-DECODE_TRAFFIC_PER_ALGO_BYTE = 1.0082
+# launch): 692.67 MB + 5.64 MB for 690.86 MB (profiles/decode_splitk_kernel_cfg2_eighth.md).
+DECODE_TRAFFIC_PER_ALGO_BYTE = 1.0108
 
 
 def measured_peak_gbs():
