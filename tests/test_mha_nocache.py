@@ -179,3 +179,38 @@ def test_gpu_host_operator(orc, dev, pkg, host):
     assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
     op.close()
     eng.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("causal", [True, False])
+def test_gpu_agrees_with_torch_sdpa_fp32_at_size(dev, pkg, causal):
+    """A second, independent reference at a size the CPU oracle does not reach in seconds: 3 sequences of
+    up to 2 304 tokens, GQA 32/8 x 128, against torch's scaled_dot_product_attention in fp32 on the same GPU."""
+    import torch
+    from ppl_nn_b200 import ops
+    Hq, Hkv, Dh = 32, 8, 128
+    seqlens = [2304, 1000, 129]
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    T = sum(seqlens)
+    q = torch.randn((T, Hq, Dh), generator=g, device=dev).to(torch.float16)
+    k = torch.randn((T, Hkv, Dh), generator=g, device=dev).to(torch.float16)
+    v = torch.randn((T, Hkv, Dh), generator=g, device=dev).to(torch.float16)
+    ss = torch.tensor([0] + list(np.cumsum(seqlens)), dtype=torch.int64, device=dev)
+    op = ops.MultiHeadAttention(ops.MultiHeadAttentionParam(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, is_causal=causal))
+    got = op.forward(q, k, v, ss, ss.clone(), 0, max(seqlens), max(seqlens)).float()
+    assert op.device_status() == 0
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        for b, n in enumerate(seqlens):
+            s0 = int(ss[b])
+            qq = q[s0:s0 + n].float().transpose(0, 1)[None]
+            kk = k[s0:s0 + n].float().repeat_interleave(Hq // Hkv, dim=1).transpose(0, 1)[None]
+            vv = v[s0:s0 + n].float().repeat_interleave(Hq // Hkv, dim=1).transpose(0, 1)[None]
+            with torch.nn.attention.sdpa_kernel(torch.nn.attention.SDPBackend.MATH):
+                ref = torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, is_causal=causal)[0].transpose(0, 1)
+            err = (got[s0:s0 + n] - ref).abs()
+            assert float(err.max()) <= MAX_ABS and float(err.mean()) <= MEAN_ABS, (b, float(err.max()), float(err.mean()))
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev

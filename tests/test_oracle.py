@@ -208,3 +208,54 @@ def test_prefill_is_causal_and_gqa_maps_heads(pkg, orc, oracle_mod):
                          cache, scale)
     assert np.abs(out2.astype(np.float32) - out.astype(np.float32)).max() < 0.05  # quantisation noise only
     assert not np.array_equal(out2, out)
+
+
+# ---- an implementation the oracle shares no code with: torch's scaled_dot_product_attention -----------
+def _sdpa(q, k, v, causal_offset=None):
+    """q [Tq, H, Dh], k/v [Tk, H, Dh] (float32 torch) -> [Tq, H, Dh]; causal_offset: row i sees kv <= i + offset."""
+    import torch
+    mask = None
+    if causal_offset is not None:
+        i = torch.arange(q.shape[0])[:, None]
+        j = torch.arange(k.shape[0])[None, :]
+        mask = j <= i + causal_offset
+    o = torch.nn.functional.scaled_dot_product_attention(q.transpose(0, 1)[None].double(), k.transpose(0, 1)[None].double(),
+                                                         v.transpose(0, 1)[None].double(), attn_mask=mask)
+    return o[0].transpose(0, 1).float()
+
+
+def test_decode_attention_agrees_with_torch_sdpa(pkg, orc, oracle_mod):
+    """The oracle's decode over the INT8 cache against torch SDPA (float64) over the dequantised rows."""
+    import torch
+    hc, d, cache, scale, out = _tiny_case(pkg, orc)
+    idx = hc.index
+    deq = torch.from_numpy(oracle_mod.np_dequant(cache, scale).astype(np.float32))  # (MaxT, 1, 2, H, Dh)
+    for b in range(idx.batch):
+        n = int(idx.kvlens[b])
+        r0 = int(idx.cachestarts[b])
+        q = torch.from_numpy(hc.query[idx.seqstarts[b]:idx.seqstarts[b] + 1].astype(np.float32))
+        ref = _sdpa(q, deq[r0:r0 + n, 0, 0], deq[r0:r0 + n, 0, 1]).numpy()
+        got = out[idx.seqstarts[b]:idx.seqstarts[b] + 1].astype(np.float32)
+        np.testing.assert_allclose(got, ref, atol=1e-3, rtol=1e-3)  # the oracle rounds its output to fp16
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_uncached_attention_agrees_with_torch_sdpa(orc, causal):
+    """orc_mha (GQA 4/2 heads, kv longer than q, mask aligned to the end) against torch SDPA (float64)."""
+    import torch
+    rng = np.random.default_rng(21)
+    seqlens, kvlens, Hq, Hkv, Dh = [6, 1, 17], [6, 40, 29], 4, 2, 64
+    ss = np.concatenate([[0], np.cumsum(seqlens)]).astype(np.int64)
+    ks = np.concatenate([[0], np.cumsum(kvlens)]).astype(np.int64)
+    q = rng.standard_normal((int(ss[-1]), Hq, Dh)).astype(np.float16)
+    k = rng.standard_normal((int(ks[-1]), Hkv, Dh)).astype(np.float16)
+    v = rng.standard_normal((int(ks[-1]), Hkv, Dh)).astype(np.float16)
+    d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=len(seqlens), is_causal=int(causal))
+    got = orc.mha(d, q, k, v, ss, ks).astype(np.float32)
+    rep = Hq // Hkv
+    for b in range(len(seqlens)):
+        qq = torch.from_numpy(q[ss[b]:ss[b + 1]].astype(np.float32))
+        kk = torch.from_numpy(k[ks[b]:ks[b + 1]].astype(np.float32)).repeat_interleave(rep, dim=1)
+        vv = torch.from_numpy(v[ks[b]:ks[b + 1]].astype(np.float32)).repeat_interleave(rep, dim=1)
+        ref = _sdpa(qq, kk, vv, causal_offset=(kvlens[b] - seqlens[b]) if causal else None).numpy()
+        np.testing.assert_allclose(got[ss[b]:ss[b + 1]], ref, atol=1e-3, rtol=1e-3)
