@@ -277,7 +277,10 @@ __device__ __forceinline__ int64_t cache_row(const CacheGeom& g, const int64_t* 
     if (g.cache_mode == 0) {
         return cachestarts[b] + pos;
     }
-    return cachestarts[b * g.cachestart_stride_b + pos / g.page_size] + pos % g.page_size;
+    // positions and page sizes are below 2^31 (checked on the host), so the division is a 32-bit one
+    const uint32_t p = static_cast<uint32_t>(pos);
+    const uint32_t page = p / static_cast<uint32_t>(g.page_size);
+    return cachestarts[b * g.cachestart_stride_b + page] + (p - page * static_cast<uint32_t>(g.page_size));
 }
 
 __device__ __forceinline__ int64_t cache_offset(const CacheGeom& g, int64_t row, int kv, int head) {

@@ -363,6 +363,7 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
     const int32_t per_segment = a.hdr->per_segment;
     const int64_t total_tiles = a.hdr->total_tiles;
     const bool paged = a.geom.cache_mode != 0;
+    const int page_shift = (a.geom.page_size & (a.geom.page_size - 1)) == 0 ? 31 - __clz(a.geom.page_size) : -1;
     const int octets = a.octets;
     const int head_lanes = a.head_lanes;
     const bool lockstep = a.lockstep != 0;
@@ -438,7 +439,13 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
 
         auto issue_one = [&]() {
             const int tok = ic.tile * kTileTok;
-            const int row = paged ? static_cast<int>(cache_row(a.geom, a.cachestarts, ic.b, tok)) : ic.row_base + tok;
+            int row = ic.row_base + tok;
+            if (paged) {  // the page table row of the sequence gives the first cache row of every page
+                const uint32_t page = page_shift >= 0 ? static_cast<uint32_t>(tok) >> page_shift
+                                                      : static_cast<uint32_t>(tok) / static_cast<uint32_t>(a.geom.page_size);
+                row = static_cast<int>(a.cachestarts[ic.b * a.geom.cachestart_stride_b + page]) +
+                      (tok - static_cast<int>(page) * a.geom.page_size);
+            }
             const uint32_t st = wsm + i_stage * T::kStageBytes;
             const uint32_t bar = wbar + i_stage * 8;
             {
