@@ -75,6 +75,17 @@ def measured_peak_tflops():
     return 1590.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
 
 
+def measured_sustained_tflops():
+    """cuBLAS bf16 over a seconds-long loop under the power cap: the yardstick for a kernel inside a long step."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops_sustained"])
+        except Exception:
+            pass
+    return 1400.0
+
+
 # ------------------------------------------------------------------------------------------------
 # clocks: NVML samples taken while the timed region runs (read-only)
 # ------------------------------------------------------------------------------------------------
@@ -360,7 +371,8 @@ def main():
         ach = algo_flops / (times["prefill"] * 1e-3) / 1e12
         kernels["prefill_tcgen05_kernel"] = {
             "bound": "tensor", "kernel": "prefill_tcgen05_kernel", "achieved": ach, "peak": tpeak, "unit": "TFLOP/s",
-            "frac": ach / tpeak, "peak_source": tpeak_src, "algorithmic_flops_per_launch": algo_flops,
+            "frac": ach / tpeak, "peak_source": tpeak_src, "frac_of_sustained_peak": ach / measured_sustained_tflops(),
+            "algorithmic_flops_per_launch": algo_flops,
             "kernel_ms": times["prefill"], "launches_timed": pre_n, "per_gpu": True, "traffic": None}
     dominant = max(kernels.values(), key=lambda k: k["kernel_ms"]) if kernels else None
     roofline = dict(dominant) if dominant else None
