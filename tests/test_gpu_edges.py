@@ -87,3 +87,34 @@ def test_second_device_in_the_same_process(orc, torch_dev, pkg):
         run_case(orc, torch.device("cuda:1"), hc)
         run_case(orc, torch.device("cuda:1"), hc2)
     torch.cuda.set_device(0)
+
+
+def test_step_replays_from_a_cuda_graph(torch_dev, pkg):
+    """The operator's launches (append, plan, decode, merge, prefill) are all stream-ordered, so a captured
+    step replays with new contents in the same buffers and gives the eager result bit for bit."""
+    import torch
+    from ppl_nn_b200 import ops, workloads
+    spec = workloads.scaled(workloads.SPECS["cfg3_llama8b_mixed"], seqs=0.125, length=0.25)
+    dc = workloads.device_case(spec, torch_dev)
+    idx = dc.index
+    op = ops.MultiHeadCacheAttention(ops.MultiHeadCacheAttentionParam(
+        num_heads=dc.num_heads, num_kv_heads=dc.num_kv_heads, head_dim=spec.head_dim, num_layer=1, layer_idx=0, quant_bit=8))
+    args = (dc.query, dc.current_key, dc.current_value, dc.seqstarts, dc.kvstarts, dc.cachestarts, dc.start_pos,
+            idx.decoding_batches, idx.max_seqlen, idx.max_kvlen, dc.cache, dc.scale)
+    eager, replayed = torch.empty_like(dc.query), torch.empty_like(dc.query)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm-up off the default stream: workspace, kernel attributes, tensor maps
+        op.forward(*args, attn_output=replayed)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        op.forward(*args, attn_output=replayed)
+    for factor in (1.0, 0.5):
+        dc.query.mul_(factor)
+        op.forward(*args, attn_output=eager)
+        replayed.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert op.device_status() == 0
+        assert bool((eager.view(torch.int16) == replayed.view(torch.int16)).all())
