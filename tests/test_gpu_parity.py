@@ -224,6 +224,20 @@ def test_workspace_too_small_and_bad_params_are_rejected(torch_dev, built_lib, p
     assert built_lib.status_str(rc) == "RC_UNSUPPORTED"  # scale missing
 
 
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (4, 4), (12, 4), (16, 16)])
+@pytest.mark.parametrize("layout,num_layer,layer_idx", [(3, 1, 0), (0, 2, 1)])
+@pytest.mark.parametrize("split_k", [0, 1, 2])
+def test_strided_cache_rows_with_2_4_and_8_head_lanes(orc, torch_dev, pkg, hq, hkv, layout, num_layer, layer_idx, split_k):
+    """Caches whose token rows are strided (layout 3, or more than one layer) make the decode warps that
+    share a range meet at a barrier after every tile.  With 2 or 4 kv heads a CTA holds several such
+    groups, each on its own range, of different lengths when split-k is off."""
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=hq, num_kv_heads=hkv, head_dim=128, n_decode=80, kv_dist="list",
+                 kv_list=tuple(range(1, 400, 5)), seed=23)
+    run_case(orc, torch_dev, workloads.host_case(spec), layout=layout, num_layer=num_layer, layer_idx=layer_idx,
+             split_k=split_k)
+
+
 # ------------------------------------------------------------------------------------------------
 # prefill (tcgen05) and mixed batches
 # ------------------------------------------------------------------------------------------------
