@@ -45,6 +45,8 @@ constexpr int kThreads = 192;  // 6 warps
 constexpr int kKStages = 3;
 constexpr int kVStages = 2;
 constexpr int kCtasPerSm = 2;
+constexpr int kTileRing = 4;      // tile indices in flight between the producer and the other roles
+constexpr int kCounterWord = 16;  // the tile counter is this many 32-bit words after the status word
 constexpr float kNegBig = -1.0e30f;
 constexpr float kRescaleSlack = 8.0f;
 
@@ -71,10 +73,12 @@ struct PrefillArgs {
     const int64_t* stage_starts;  // kv_mode 1: first staging row of each prefill sequence
     const int64_t* kvstarts;      // kv_mode 2: first K/V row of each sequence (a tensor of its own)
     uint32_t* status;
+    int* tile_counter;  // next tile to hand out; zeroed before every launch
     int64_t max_seqlen;
     int32_t decoding_batches;
     int32_t prefill_batches;
-    int32_t q_tiles;    // query tiles per sequence the grid provides
+    int32_t q_tiles;    // query tiles per sequence in the tile index space
+    int32_t total_tiles;  // q_tiles * prefill_batches * num_heads
     int32_t seq_major;  // grid order
     int32_t num_heads;
     int32_t group;
@@ -86,6 +90,8 @@ struct PrefillArgs {
 
 struct Barriers {
     uint64_t q_full;
+    uint64_t q_empty;     // the last Q K^T of a tile has completed: Q may be overwritten with the next tile's
+    uint64_t o_free;      // the epilogue holds O in registers: the next tile may overwrite it
     uint64_t k_full[kKStages];
     uint64_t v_full[kVStages];
     uint64_t k_empty[kKStages];
@@ -94,6 +100,9 @@ struct Barriers {
     uint64_t s_free;
     uint64_t p_full[2];   // one per P buffer, so that a waiter can never be lapped
     uint64_t pv_done[2];  // P V of the tile that used P buffer 0 / 1 has completed
+    uint64_t tile_full[kTileRing];  // the producer has published a tile index in tile_ring[e]
+    uint64_t tile_free[kTileRing];  // the MMA warp and the softmax threads have read tile_ring[e]
+    int tile_ring[kTileRing];
     uint32_t tmem_slot;
     int abort_word;
 };
@@ -300,82 +309,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // ---- which tile ----
-    // Two grid orders, both with the heads of one query tile adjacent (they share K/V in L2):
-    //   tile-major      blockIdx.x = (qt_rev * prefill_batches + pb) * num_heads + head: the latest (longest)
-    //                   query tile of every sequence first, then the ones before them; best balance
-    //   sequence-major  blockIdx.x = (pb * q_tiles + qt_rev) * num_heads + head: the CTAs in flight work on
-    //                   one or two sequences, whose K/V then stay in L2
-    int qt_rev, pb, head;
-    if (a.seq_major) {
-        const int per_seq = a.q_tiles * a.num_heads;
-        pb = blockIdx.x / per_seq;
-        const int rem = blockIdx.x - pb * per_seq;
-        qt_rev = rem / a.num_heads;
-        head = rem - qt_rev * a.num_heads;
-    } else {
-        const int per_rev = a.prefill_batches * a.num_heads;
-        qt_rev = blockIdx.x / per_rev;
-        const int rem = blockIdx.x - qt_rev * per_rev;
-        pb = rem / a.num_heads;
-        head = rem - pb * a.num_heads;
-    }
-    const int b = a.decoding_batches + pb;
-    const int64_t seq0 = a.seqstarts[b];
-    int64_t seqlen = a.seqstarts[b + 1] - seq0;
-    if (seqlen > a.max_seqlen) {
-        seqlen = a.max_seqlen;
-        if (threadIdx.x == 0 && qt_rev == 0 && head == 0) {
-            atomicOr(a.status, kDevLengthClamped);
-        }
-    }
-    const int n_qt = static_cast<int>((seqlen + kBlockM - 1) / kBlockM);
-    if (qt_rev >= n_qt) {
-        return;  // uniform for the CTA, before any barrier or TMEM allocation
-    }
     if ((smem_u32(smem) & 1023u) != 0u) {
         if (threadIdx.x == 0) {
             atomicOr(a.status, kDevTmaTimeout);
         }
-        return;  // uniform as well
+        return;  // uniform for the CTA, before any barrier or TMEM allocation
     }
-    const int qt = n_qt - 1 - qt_rev;  // longest (latest) query tiles first
-    const int kvh = head / a.group;
-    const int64_t i0 = static_cast<int64_t>(qt) * kBlockM;
-    const int rows_valid = (seqlen - i0) < kBlockM ? static_cast<int>(seqlen - i0) : kBlockM;
-    // kv rows of the sequence, how many there are, and how many of them precede query row 0 (hist)
-    int64_t kv_row0 = seq0, kvlen = seqlen, hist = 0;
-    if (a.kv_mode == 1) {
-        hist = a.start_pos[b];
-        kvlen = hist + seqlen;
-        kv_row0 = a.stage_starts[pb];
-    } else if (a.kv_mode == 2) {
-        kv_row0 = a.kvstarts[b];
-        kvlen = a.kvstarts[b + 1] - kv_row0;
-        kvlen = kvlen > a.max_kvlen ? a.max_kvlen : kvlen;
-        hist = kvlen - seqlen;  // causal masks are aligned to the END of the kv range
-    }
-    int64_t kv_visible = a.is_causal ? hist + i0 + rows_valid : kvlen;  // kv positions the last valid row may see
-    kv_visible = kv_visible > kvlen ? kvlen : kv_visible;
-    const int n_kv = kv_visible > 0 ? static_cast<int>((kv_visible + kBlockN - 1) / kBlockN) : 0;
-    const int64_t q_row0 = seq0 + i0;
-    if (n_kv == 0) {
-        // nothing visible to any row of the tile: zeros (uniform for the CTA, before any barrier)
-        for (int idx = threadIdx.x; idx < rows_valid * (DH / 8); idx += kThreads) {
-            const int r = idx / (DH / 8), c = idx - r * (DH / 8);
-            *reinterpret_cast<uint4*>(a.out + ((q_row0 + r) * a.num_heads + head) * DH + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-        }
-        return;
-    }
-    // first kv position no row may see, and whether rows of this tile see nothing at all (causal, more
-    // query rows than kv rows)
-    const int64_t first_row_last = a.is_causal ? hist + i0 : kvlen - 1;  // last kv position visible to row 0 of the tile
-    const bool dead_rows = first_row_last < 0;
 
-    // ---- setup ----
+    // ---- setup (once per CTA; the CTA then works through tiles handed out by a global counter) ----
     if (threadIdx.x == 0) {
         bars.abort_word = 0;
         mbar_init(&bars.q_full, 1);
+        mbar_init(&bars.q_empty, 1);
         for (int s = 0; s < kKStages; ++s) {
             mbar_init(&bars.k_full[s], 1);
             mbar_init(&bars.k_empty[s], 1);
@@ -386,6 +331,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
         mbar_init(&bars.s_full, 1);
         mbar_init(&bars.s_free, 128);
+        mbar_init(&bars.o_free, 128);
+        for (int e = 0; e < kTileRing; ++e) {
+            mbar_init(&bars.tile_full[e], 1);
+            mbar_init(&bars.tile_free[e], 129);  // 128 softmax threads + one lane of the MMA warp
+        }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&bars.p_full[i], 128);
             mbar_init(&bars.pv_done[i], 1);
@@ -404,69 +354,202 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     tc_fence_after();
     const uint32_t tmem_base = bars.tmem_slot;
 
+    // ---- which tile ----
+    // Two orders of the tile index, both with the heads of one query tile adjacent (they share K/V in L2):
+    //   tile-major      t = (qt_rev * prefill_batches + pb) * num_heads + head: the latest (longest)
+    //                   query tile of every sequence first, then the ones before them; best balance
+    //   sequence-major  t = (pb * q_tiles + qt_rev) * num_heads + head: the CTAs in flight work on
+    //                   one or two sequences, whose K/V then stay in L2
+    // The producer warp draws tile indices from the global counter, drops those beyond their sequence's
+    // length and publishes the others through a small ring in shared memory; the MMA warp and the softmax
+    // threads read them there (index -1: no more tiles).  A tile that sees no kv position is zero-filled by
+    // the softmax threads and ignored by the other two roles.
+    struct Tile {
+        int head, kvh, n_kv, rows_valid;
+        int64_t q_row0, kv_row0, kvlen, first_row_last;
+        bool dead_rows;
+    };
+    auto decode_tile = [&](int t, Tile& ti) -> bool {
+        int qt_rev, pb;
+        if (a.seq_major) {
+            const int per_seq = a.q_tiles * a.num_heads;
+            pb = t / per_seq;
+            const int rem = t - pb * per_seq;
+            qt_rev = rem / a.num_heads;
+            ti.head = rem - qt_rev * a.num_heads;
+        } else {
+            const int per_rev = a.prefill_batches * a.num_heads;
+            qt_rev = t / per_rev;
+            const int rem = t - qt_rev * per_rev;
+            pb = rem / a.num_heads;
+            ti.head = rem - pb * a.num_heads;
+        }
+        const int b = a.decoding_batches + pb;
+        const int64_t seq0 = a.seqstarts[b];
+        int64_t seqlen = a.seqstarts[b + 1] - seq0;
+        if (seqlen > a.max_seqlen) {
+            seqlen = a.max_seqlen;
+            if (threadIdx.x == 64 && qt_rev == 0 && ti.head == 0) {
+                atomicOr(a.status, kDevLengthClamped);
+            }
+        }
+        const int n_qt = static_cast<int>((seqlen + kBlockM - 1) / kBlockM);
+        if (qt_rev >= n_qt) {
+            return false;
+        }
+        const int qt = n_qt - 1 - qt_rev;  // longest (latest) query tiles first
+        ti.kvh = ti.head / a.group;
+        const int64_t i0 = static_cast<int64_t>(qt) * kBlockM;
+        ti.rows_valid = (seqlen - i0) < kBlockM ? static_cast<int>(seqlen - i0) : kBlockM;
+        // kv rows of the sequence, how many there are, and how many of them precede query row 0 (hist)
+        int64_t kv_row0 = seq0, kvlen = seqlen, hist = 0;
+        if (a.kv_mode == 1) {
+            hist = a.start_pos[b];
+            kvlen = hist + seqlen;
+            kv_row0 = a.stage_starts[pb];
+        } else if (a.kv_mode == 2) {
+            kv_row0 = a.kvstarts[b];
+            kvlen = a.kvstarts[b + 1] - kv_row0;
+            kvlen = kvlen > a.max_kvlen ? a.max_kvlen : kvlen;
+            hist = kvlen - seqlen;  // causal masks are aligned to the END of the kv range
+        }
+        int64_t kv_visible = a.is_causal ? hist + i0 + ti.rows_valid : kvlen;  // kv positions the last valid row may see
+        kv_visible = kv_visible > kvlen ? kvlen : kv_visible;
+        ti.n_kv = kv_visible > 0 ? static_cast<int>((kv_visible + kBlockN - 1) / kBlockN) : 0;
+        ti.q_row0 = seq0 + i0;
+        ti.kv_row0 = kv_row0;
+        ti.kvlen = kvlen;
+        // last kv position visible to row 0 of the tile, and whether rows of this tile see nothing at all
+        // (causal, more query rows than kv rows)
+        ti.first_row_last = a.is_causal ? hist + i0 : kvlen - 1;
+        ti.dead_rows = ti.first_row_last < 0;
+        return true;
+    };
+    const int total_tiles = a.total_tiles;
+    // reader side of the ring: entry n of this CTA, or false after a timeout / abort
+    auto next_tile = [&](int n, int& t, bool one_lane_arrives) -> bool {
+        const int e = n % kTileRing;
+        if (!wait_or_abort(&bars.tile_full[e], (n / kTileRing) & 1, abort_flag, a.status, kDevTmaTimeout)) {
+            return false;
+        }
+        t = *reinterpret_cast<volatile int*>(&bars.tile_ring[e]);
+        if (one_lane_arrives) {
+            __syncwarp();  // every lane has read the entry
+            if (lane == 0) {
+                mbar_arrive(&bars.tile_free[e]);
+            }
+        } else {
+            mbar_arrive(&bars.tile_free[e]);
+        }
+        return true;
+    };
+
     if (warp == 0) {
         // =========================== TMA producer ===========================
         // The whole warp runs the loop (waits are warp-uniform); an elected lane issues the copies.  A K
         // stage is free again as soon as its Q K^T has completed, a V stage once its P V has; the copies are
-        // issued in the order in which those completions arrive: K(i), then V(i-1).
-        if (elect_one()) {
-            mbar_arrive_expect_tx(&bars.q_full, T::kQBytes);
-#pragma unroll
-            for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                tma_load_3d(sQ + cb * T::kQBlockBytes, &tm_q, &bars.q_full, cb * 64, head, static_cast<int>(q_row0));
-            }
-        }
-        __syncwarp();
+        // issued in the order in which those completions arrive: K(i), then V(i-1).  The stage rings and
+        // their phases run on across tiles; Q is reloaded once the last Q K^T of the previous tile is done.
         bool ok = true;
-        int k_issued = 0, v_issued = 0;
-        for (int i = 0; ok && i <= n_kv; ++i) {
-            if (i < n_kv) {
-                const int s = i % kKStages;
-                if (i >= kKStages) {
-                    ok = wait_or_abort(&bars.k_empty[s], ((i / kKStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
-                    if (!ok) {
-                        break;
-                    }
-                }
-                if (elect_one()) {
-                    const int row = static_cast<int>(kv_row0 + static_cast<int64_t>(i) * kBlockN);
-                    mbar_arrive_expect_tx(&bars.k_full[s], T::kKVBytes);
-#pragma unroll
-                    for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                        tma_load_3d(sK + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_k, &bars.k_full[s], cb * 64, kvh, row);
-                    }
-                }
-                __syncwarp();
-                k_issued = i + 1;
+        int tiles_done = 0, kc = 0, vc = 0;  // tiles with work so far; K and V copies issued so far
+        int published = 0;
+        while (ok) {
+            int t = 0;
+            if (lane == 0) {
+                t = atomicAdd(a.tile_counter, 1);
             }
-            if (i > 0) {
-                const int jv = i - 1;
-                const int s = jv % kVStages;
-                if (jv >= kVStages) {
-                    ok = wait_or_abort(&bars.v_empty[s], ((jv / kVStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+            t = __shfl_sync(0xffffffffu, t, 0);
+            const bool last = t >= total_tiles;
+            Tile ti;
+            if (!last && !decode_tile(t, ti)) {
+                continue;  // beyond the end of its sequence: nobody needs it
+            }
+            {
+                const int e = published % kTileRing;
+                if (published >= kTileRing) {
+                    ok = wait_or_abort(&bars.tile_free[e], ((published / kTileRing) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                     if (!ok) {
                         break;
                     }
                 }
-                if (elect_one()) {
-                    const int row = static_cast<int>(kv_row0 + static_cast<int64_t>(jv) * kBlockN);
-                    mbar_arrive_expect_tx(&bars.v_full[s], T::kKVBytes);
-#pragma unroll
-                    for (int cb = 0; cb < T::kColBlocks; ++cb) {
-                        tma_load_3d(sV + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_v, &bars.v_full[s], cb * 64, kvh, row);
-                    }
+                if (lane == 0) {
+                    bars.tile_ring[e] = last ? -1 : t;
+                    mbar_arrive(&bars.tile_full[e]);
                 }
                 __syncwarp();
-                v_issued = jv + 1;
+                ++published;
+            }
+            if (last) {
+                break;
+            }
+            if (ti.n_kv == 0) {
+                continue;
+            }
+            if (tiles_done > 0) {
+                ok = wait_or_abort(&bars.q_empty, (tiles_done - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                if (!ok) {
+                    break;
+                }
+            }
+            if (elect_one()) {
+                mbar_arrive_expect_tx(&bars.q_full, T::kQBytes);
+#pragma unroll
+                for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                    tma_load_3d(sQ + cb * T::kQBlockBytes, &tm_q, &bars.q_full, cb * 64, ti.head, static_cast<int>(ti.q_row0));
+                }
+            }
+            __syncwarp();
+            ++tiles_done;
+            for (int i = 0; ok && i <= ti.n_kv; ++i) {
+                if (i < ti.n_kv) {
+                    const int s = kc % kKStages;
+                    if (kc >= kKStages) {
+                        ok = wait_or_abort(&bars.k_empty[s], ((kc / kKStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                        if (!ok) {
+                            break;
+                        }
+                    }
+                    if (elect_one()) {
+                        const int row = static_cast<int>(ti.kv_row0 + static_cast<int64_t>(i) * kBlockN);
+                        mbar_arrive_expect_tx(&bars.k_full[s], T::kKVBytes);
+#pragma unroll
+                        for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                            tma_load_3d(sK + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_k, &bars.k_full[s], cb * 64, ti.kvh, row);
+                        }
+                    }
+                    __syncwarp();
+                    ++kc;
+                }
+                if (i > 0) {
+                    const int s = vc % kVStages;
+                    if (vc >= kVStages) {
+                        ok = wait_or_abort(&bars.v_empty[s], ((vc / kVStages) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                        if (!ok) {
+                            break;
+                        }
+                    }
+                    if (elect_one()) {
+                        const int row = static_cast<int>(ti.kv_row0 + static_cast<int64_t>(i - 1) * kBlockN);
+                        mbar_arrive_expect_tx(&bars.v_full[s], T::kKVBytes);
+#pragma unroll
+                        for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                            tma_load_3d(sV + s * T::kKVBytes + cb * T::kKVBlockBytes, &tm_v, &bars.v_full[s], cb * 64, ti.kvh, row);
+                        }
+                    }
+                    __syncwarp();
+                    ++vc;
+                }
             }
         }
         if (*abort_flag) {
             // drain: every copy this warp issued must have landed before the CTA may exit
-            mbar_wait_bounded(&bars.q_full, 0);
-            for (int j = k_issued > kKStages ? k_issued - kKStages : 0; j < k_issued; ++j) {
+            if (tiles_done > 0) {
+                mbar_wait_bounded(&bars.q_full, (tiles_done - 1) & 1);
+            }
+            for (int j = kc > kKStages ? kc - kKStages : 0; j < kc; ++j) {
                 mbar_wait_bounded(&bars.k_full[j % kKStages], (j / kKStages) & 1);
             }
-            for (int j = v_issued > kVStages ? v_issued - kVStages : 0; j < v_issued; ++j) {
+            for (int j = vc > kVStages ? vc - kVStages : 0; j < vc; ++j) {
                 mbar_wait_bounded(&bars.v_full[j % kVStages], (j / kVStages) & 1);
             }
         }
@@ -480,59 +563,82 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const uint32_t k_lo = desc_lo(smem_u32(sK), 16);
         const uint32_t v_lo = desc_lo(smem_u32(sV), T::kKVBlockBytes);  // MN-major: 64-channel blocks lbo apart
         const uint32_t d_s = tmem_base + T::kColS, d_o = tmem_base + T::kColO, a_p = tmem_base + T::kColP;
-        bool ok = wait_or_abort(&bars.q_full, 0, abort_flag, a.status, kDevTmaTimeout);
-        for (int j = 0; ok && j <= n_kv; ++j) {
-            if (j < n_kv) {
-                // S(j) = Q K(j)^T as soon as K(j) has landed and the softmax threads hold S(j-1) in registers
-                const int s = j % kKStages;
-                ok = wait_or_abort(&bars.k_full[s], (j / kKStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
-                     (j == 0 || wait_or_abort(&bars.s_free, (j - 1) & 1, abort_flag, a.status, kDevMmaTimeout));
-                if (!ok) {
-                    break;
-                }
-                tc_fence_after();
-                if (elect_one()) {
-                    const uint32_t ks_lo = k_lo + s * (T::kKVBytes >> 4);
+        bool ok = true;
+        int tiles_done = 0, kc = 0, vc = 0;  // tiles with work so far; Q K^T and P V issued so far (all tiles)
+        for (int n = 0; ok; ++n) {
+            int t;
+            if (!next_tile(n, t, true) || t < 0) {
+                break;
+            }
+            Tile ti;
+            if (!decode_tile(t, ti) || ti.n_kv == 0) {
+                continue;
+            }
+            ok = wait_or_abort(&bars.q_full, tiles_done & 1, abort_flag, a.status, kDevTmaTimeout);
+            for (int j = 0; ok && j <= ti.n_kv; ++j) {
+                if (j < ti.n_kv) {
+                    // S = Q K(j)^T as soon as K(j) has landed and the softmax threads hold the previous scores in
+                    // registers (the previous scores may be the last ones of the tile before)
+                    const int s = kc % kKStages;
+                    ok = wait_or_abort(&bars.k_full[s], (kc / kKStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
+                         (kc == 0 || wait_or_abort(&bars.s_free, (kc - 1) & 1, abort_flag, a.status, kDevMmaTimeout));
+                    if (!ok) {
+                        break;
+                    }
+                    tc_fence_after();
+                    if (elect_one()) {
+                        const uint32_t ks_lo = k_lo + s * (T::kKVBytes >> 4);
 #pragma unroll
-                    for (int cb = 0; cb < T::kColBlocks; ++cb) {
+                        for (int cb = 0; cb < T::kColBlocks; ++cb) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            tc_mma_f16(d_s, desc_join(q_lo + cb * (T::kQBlockBytes >> 4) + 2 * k, hi_sw128),
-                                       desc_join(ks_lo + cb * (T::kKVBlockBytes >> 4) + 2 * k, hi_sw128), idesc_qk,
-                                       (cb | k) ? 1u : 0u);
+                            for (int k = 0; k < 4; ++k) {
+                                tc_mma_f16(d_s, desc_join(q_lo + cb * (T::kQBlockBytes >> 4) + 2 * k, hi_sw128),
+                                           desc_join(ks_lo + cb * (T::kKVBlockBytes >> 4) + 2 * k, hi_sw128), idesc_qk,
+                                           (cb | k) ? 1u : 0u);
+                            }
+                        }
+                        tc_commit(&bars.s_full);
+                        tc_commit(&bars.k_empty[s]);
+                        if (j == ti.n_kv - 1) {
+                            tc_commit(&bars.q_empty);  // the tile's last read of Q
                         }
                     }
-                    tc_commit(&bars.s_full);
-                    tc_commit(&bars.k_empty[s]);
+                    __syncwarp();
+                    ++kc;
                 }
-                __syncwarp();
-            }
-            if (j > 0) {
-                // O += P(j-1) V(j-1)
-                const int jp = j - 1;
-                const int s = jp % kVStages;
-                // V landed long ago; testing it first keeps it off the path from "P is ready" to the issue
-                ok = wait_or_abort(&bars.v_full[s], (jp / kVStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
-                     wait_or_abort(&bars.p_full[jp & 1], (jp >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
-                if (!ok) {
-                    break;
-                }
-                tc_fence_after();
-                if (elect_one()) {
-                    const uint32_t vs_lo = v_lo + s * (T::kKVBytes >> 4);
-                    const uint32_t pa = a_p + (jp & 1) * T::kPCols;
-#pragma unroll
-                    for (int ks = 0; ks < kBlockN / 16; ++ks) {
-                        // P: kv index 16 ks = TMEM column 8 ks of the buffer (two halves per column);
-                        // V: MN-major, kv rows 16 ks .. 16 ks + 15 (2048 bytes) of every 64-channel block
-                        tc_mma_f16_ts(d_o, pa + 8 * ks, desc_join(vs_lo + ks * (2048 >> 4), hi_sw128), idesc_pv,
-                                      (jp | ks) ? 1u : 0u);
+                if (j > 0) {
+                    // O += P(j-1) V(j-1)
+                    const int jp = j - 1;
+                    const int s = vc % kVStages;
+                    // V landed long ago; testing it first keeps it off the path from "P is ready" to the issue
+                    ok = wait_or_abort(&bars.v_full[s], (vc / kVStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
+                         wait_or_abort(&bars.p_full[vc & 1], (vc >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                    if (ok && jp == 0 && tiles_done > 0) {
+                        // the first P V of a tile overwrites O: the previous tile's epilogue must have read it
+                        ok = wait_or_abort(&bars.o_free, (tiles_done - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                     }
-                    tc_commit(&bars.v_empty[s]);
-                    tc_commit(&bars.pv_done[jp & 1]);
+                    if (!ok) {
+                        break;
+                    }
+                    tc_fence_after();
+                    if (elect_one()) {
+                        const uint32_t vs_lo = v_lo + s * (T::kKVBytes >> 4);
+                        const uint32_t pa = a_p + (vc & 1) * T::kPCols;
+#pragma unroll
+                        for (int ks = 0; ks < kBlockN / 16; ++ks) {
+                            // P: kv index 16 ks = TMEM column 8 ks of the buffer (two halves per column);
+                            // V: MN-major, kv rows 16 ks .. 16 ks + 15 (2048 bytes) of every 64-channel block
+                            tc_mma_f16_ts(d_o, pa + 8 * ks, desc_join(vs_lo + ks * (2048 >> 4), hi_sw128), idesc_pv,
+                                          (jp | ks) ? 1u : 0u);
+                        }
+                        tc_commit(&bars.v_empty[s]);
+                        tc_commit(&bars.pv_done[vc & 1]);
+                    }
+                    __syncwarp();
+                    ++vc;
                 }
-                __syncwarp();
             }
+            ++tiles_done;
         }
     } else {
         // =========================== softmax / epilogue ===========================
@@ -543,130 +649,157 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const uint32_t t_o = tmem_base + t_lane + T::kColO;
         const uint32_t t_p = tmem_base + t_lane + T::kColP;
         const float sc = a.scale_log2;
-        float m_ref = kNegBig, l_sum = 0.0f;
         bool ok = true;
-        for (int j = 0; ok && j < n_kv; ++j) {
-            // This tile's P buffer is free once the P V of the tile before the previous one has completed.  That
-            // happened long before the scores of this tile arrive, so the test comes first and costs nothing
-            // on the path from "S is ready" to the exponentials.
-            if (j >= 2) {
-                ok = wait_or_abort(&bars.pv_done[j & 1], ((j - 2) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
-                if (!ok) {
-                    break;
-                }
-            }
-            ok = wait_or_abort(&bars.s_full, j & 1, abort_flag, a.status, kDevMmaTimeout);
-            if (!ok) {
+        int pc = 0;  // score tiles consumed = P tiles produced so far (all tiles of this CTA)
+        for (int n = 0; ok; ++n) {
+            int t;
+            if (!next_tile(n, t, false) || t < 0) {
                 break;
             }
-            tc_fence_after();
-            float sv[kBlockN];
-            {
-                uint32_t v0[32], v1[32];
-                tmem_ld32(t_s, v0);
-                tmem_ld32(t_s + 32, v1);
-                tmem_wait_ld();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    sv[e] = __uint_as_float(v0[e]);
-                    sv[32 + e] = __uint_as_float(v1[e]);
+            Tile ti;
+            if (!decode_tile(t, ti)) {
+                continue;
+            }
+            const int head = ti.head, rows_valid = ti.rows_valid, n_kv = ti.n_kv;
+            const int64_t q_row0 = ti.q_row0, kvlen = ti.kvlen, first_row_last = ti.first_row_last;
+            const bool dead_rows = ti.dead_rows;
+            if (n_kv == 0) {
+                // nothing visible to any row of the tile: zeros
+                for (int idx = threadIdx.x - 64; idx < rows_valid * (DH / 8); idx += 128) {
+                    const int rr = idx / (DH / 8), c = idx - rr * (DH / 8);
+                    *reinterpret_cast<uint4*>(a.out + ((q_row0 + rr) * a.num_heads + head) * DH + c * 8) = make_uint4(0u, 0u, 0u, 0u);
                 }
+                continue;
             }
-            // S is in registers: the MMA warp may overwrite the buffer with the next tile's scores
-            tc_fence_before();
-            mbar_arrive(&bars.s_free);
-            // columns of this tile that row r may see: col <= limit.  Only tiles that reach past the first
-            // row's horizon or past the end of the kv range need the mask (uniform for the CTA).  Unless the
-            // tile has rows that see nothing at all (handled below), column 0 of tile 0 is visible to every
-            // row, so m_ref is a real score from the first tile on.
-            const int64_t tile_hi = static_cast<int64_t>(j + 1) * kBlockN - 1;
-            if (tile_hi > first_row_last || tile_hi >= kvlen) {
-                int64_t lim64 = (a.is_causal ? first_row_last + r : kvlen - 1);
-                lim64 = lim64 > kvlen - 1 ? kvlen - 1 : lim64;
-                lim64 -= static_cast<int64_t>(j) * kBlockN;
-                const int limit = lim64 > kBlockN ? kBlockN : (lim64 < -1 ? -1 : static_cast<int>(lim64));
-#pragma unroll
-                for (int e = 0; e < kBlockN; ++e) {
-                    sv[e] = e <= limit ? sv[e] : kNegBig;
-                }
-            }
-            float mx0 = fmax3(sv[0], sv[1], sv[2]), mx1 = fmax3(sv[3], sv[4], sv[5]);
-#pragma unroll
-            for (int e = 6; e + 3 < kBlockN; e += 4) {
-                mx0 = fmax3(mx0, sv[e], sv[e + 1]);
-                mx1 = fmax3(mx1, sv[e + 2], sv[e + 3]);
-            }
-            float mx = fmax3(mx0, mx1, fmaxf(sv[kBlockN - 2], sv[kBlockN - 1]));
-            mx *= sc;  // sc > 0, so the maximum commutes with the scaling
-            const bool grow = mx > m_ref + kRescaleSlack;
-            if (__any_sync(0xffffffffu, grow)) {
-                const float m_new = grow ? mx : m_ref;
-                const float f = ex2_approx(m_ref - m_new);
-                m_ref = m_new;
-                l_sum *= f;
-                if (j > 0) {
-                    // O may be touched once the previous tile's P V has completed
-                    ok = wait_or_abort(&bars.pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+            float m_ref = kNegBig, l_sum = 0.0f;
+            for (int j = 0; ok && j < n_kv; ++j, ++pc) {
+                // This tile's P buffer is free once the P V of the tile before the previous one has completed.  That
+                // happened long before the scores of this tile arrive, so the test comes first and costs nothing
+                // on the path from "S is ready" to the exponentials.
+                if (pc >= 2) {
+                    ok = wait_or_abort(&bars.pv_done[pc & 1], ((pc - 2) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                     if (!ok) {
                         break;
                     }
-                    tc_fence_after();
+                }
+                ok = wait_or_abort(&bars.s_full, pc & 1, abort_flag, a.status, kDevMmaTimeout);
+                if (!ok) {
+                    break;
+                }
+                tc_fence_after();
+                float sv[kBlockN];
+                {
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(t_s, v0);
+                    tmem_ld32(t_s + 32, v1);
+                    tmem_wait_ld();
 #pragma unroll
-                    for (int c = 0; c < DH / 32; ++c) {
-                        uint32_t v[32];
-                        tmem_ld32(t_o + c * 32, v);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
-                        }
-                        tmem_st32(t_o + c * 32, v);
+                    for (int e = 0; e < 32; ++e) {
+                        sv[e] = __uint_as_float(v0[e]);
+                        sv[32 + e] = __uint_as_float(v1[e]);
                     }
-                    tmem_wait_st();
                 }
-            }
-            // P = exp2(s * scale - m_ref) as packed fp16 into TMEM: column c of the buffer = kv columns 2c, 2c+1
-            // a row that sees no kv position at all gets zero weights (exp2(-inf)), hence a zero output row
-            const float neg_m = (dead_rows && first_row_last + r < 0) ? -INFINITY : -m_ref;
-            const uint32_t t_pb = t_p + (j & 1) * T::kPCols;
+                // S is in registers: the MMA warp may overwrite the buffer with the next tile's scores
+                tc_fence_before();
+                mbar_arrive(&bars.s_free);
+                // columns of this tile that row r may see: col <= limit.  Only tiles that reach past the first
+                // row's horizon or past the end of the kv range need the mask (uniform for the CTA).  Unless the
+                // tile has rows that see nothing at all (handled below), column 0 of tile 0 is visible to every
+                // row, so m_ref is a real score from the first tile on.
+                const int64_t tile_hi = static_cast<int64_t>(j + 1) * kBlockN - 1;
+                if (tile_hi > first_row_last || tile_hi >= kvlen) {
+                    int64_t lim64 = (a.is_causal ? first_row_last + r : kvlen - 1);
+                    lim64 = lim64 > kvlen - 1 ? kvlen - 1 : lim64;
+                    lim64 -= static_cast<int64_t>(j) * kBlockN;
+                    const int limit = lim64 > kBlockN ? kBlockN : (lim64 < -1 ? -1 : static_cast<int>(lim64));
 #pragma unroll
-            for (int q = 0; q < kBlockN / 32; ++q) {
-                uint32_t pk[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const float p0 = ex2_approx(fmaf(sv[32 * q + 2 * e], sc, neg_m));
-                    const float p1 = ex2_approx(fmaf(sv[32 * q + 2 * e + 1], sc, neg_m));
-                    pk[e] = h2_as_u32(__floats2half2_rn(p0, p1));
-                    add_half2_to_float(l_sum, pk[e]);
+                    for (int e = 0; e < kBlockN; ++e) {
+                        sv[e] = e <= limit ? sv[e] : kNegBig;
+                    }
                 }
-                tmem_st16(t_pb + 16 * q, pk);
+                float mx0 = fmax3(sv[0], sv[1], sv[2]), mx1 = fmax3(sv[3], sv[4], sv[5]);
+#pragma unroll
+                for (int e = 6; e + 3 < kBlockN; e += 4) {
+                    mx0 = fmax3(mx0, sv[e], sv[e + 1]);
+                    mx1 = fmax3(mx1, sv[e + 2], sv[e + 3]);
+                }
+                float mx = fmax3(mx0, mx1, fmaxf(sv[kBlockN - 2], sv[kBlockN - 1]));
+                mx *= sc;  // sc > 0, so the maximum commutes with the scaling
+                const bool grow = mx > m_ref + kRescaleSlack;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float m_new = grow ? mx : m_ref;
+                    const float f = ex2_approx(m_ref - m_new);
+                    m_ref = m_new;
+                    l_sum *= f;
+                    if (j > 0) {
+                        // O may be touched once the previous tile's P V has completed
+                        ok = wait_or_abort(&bars.pv_done[(pc - 1) & 1], ((pc - 1) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+                        if (!ok) {
+                            break;
+                        }
+                        tc_fence_after();
+#pragma unroll
+                        for (int c = 0; c < DH / 32; ++c) {
+                            uint32_t v[32];
+                            tmem_ld32(t_o + c * 32, v);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) {
+                                v[e] = __float_as_uint(__uint_as_float(v[e]) * f);
+                            }
+                            tmem_st32(t_o + c * 32, v);
+                        }
+                        tmem_wait_st();
+                    }
+                }
+                // P = exp2(s * scale - m_ref) as packed fp16 into TMEM: column c of the buffer = kv columns 2c, 2c+1
+                // a row that sees no kv position at all gets zero weights (exp2(-inf)), hence a zero output row
+                const float neg_m = (dead_rows && first_row_last + r < 0) ? -INFINITY : -m_ref;
+                const uint32_t t_pb = t_p + (pc & 1) * T::kPCols;
+#pragma unroll
+                for (int q = 0; q < kBlockN / 32; ++q) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) {
+                        const float p0 = ex2_approx(fmaf(sv[32 * q + 2 * e], sc, neg_m));
+                        const float p1 = ex2_approx(fmaf(sv[32 * q + 2 * e + 1], sc, neg_m));
+                        pk[e] = h2_as_u32(__floats2half2_rn(p0, p1));
+                        add_half2_to_float(l_sum, pk[e]);
+                    }
+                    tmem_st16(t_pb + 16 * q, pk);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&bars.p_full[pc & 1]);
             }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&bars.p_full[j & 1]);
-        }
-        // ---- epilogue: O / l -> fp16 rows ----
-        if (ok) {
-            ok = wait_or_abort(&bars.pv_done[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
-        }
-        if (ok) {
-            tc_fence_after();
-            const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
-            __half* dst = a.out + ((q_row0 + r) * a.num_heads + head) * DH;
+            // ---- epilogue: O / l -> fp16 rows ----
+            if (ok) {
+                ok = wait_or_abort(&bars.pv_done[(pc - 1) & 1], ((pc - 1) >> 1) & 1, abort_flag, a.status, kDevMmaTimeout);
+            }
+            if (ok) {
+                tc_fence_after();
+                const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
+                __half* dst = a.out + ((q_row0 + r) * a.num_heads + head) * DH;
 #pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
-                uint32_t v[32];
-                tmem_ld32(t_o + c * 32, v);
-                tmem_wait_ld();
-                if (r < rows_valid) {
+                for (int c = 0; c < DH / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld32(t_o + c * 32, v);
+                    tmem_wait_ld();
+                    if (c == DH / 32 - 1) {
+                        // O is in registers: the MMA warp may start the next tile's accumulation
+                        tc_fence_before();
+                        mbar_arrive(&bars.o_free);
+                    }
+                    if (r < rows_valid) {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        uint4 o4;
-                        o4.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv));
-                        o4.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv));
-                        o4.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv));
-                        o4.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv));
-                        *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o4;
+                        for (int q = 0; q < 4; ++q) {
+                            uint4 o4;
+                            o4.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv));
+                            o4.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv));
+                            o4.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv));
+                            o4.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv));
+                            *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o4;
+                        }
                     }
                 }
             }
@@ -830,11 +963,24 @@ static int launch_attention_core(const void* query, const void* k_src, const voi
         }
         attr_set = true;
     }
-    const int64_t ctas = q_tiles_per_seq * a.prefill_batches * num_heads;
-    if (ctas > 0x7fffffff) {
+    const int64_t tiles = q_tiles_per_seq * a.prefill_batches * num_heads;
+    if (tiles > 0x7fffffff) {
         return PPLB200_UNSUPPORTED;
     }
-    const dim3 grid(static_cast<unsigned>(ctas));
+    a.total_tiles = static_cast<int32_t>(tiles);
+    a.tile_counter = reinterpret_cast<int*>(a.status + kCounterWord);
+    if (cudaMemsetAsync(a.tile_counter, 0, 4, stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    // persistent CTAs: two per SM, drawing tiles from the counter
+    int sm_count = 0;
+    if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev_id) != cudaSuccess || sm_count <= 0) {
+        (void)cudaGetLastError();
+        return PPLB200_DEVICE_RUNTIME_ERROR;
+    }
+    const int64_t resident = static_cast<int64_t>(sm_count) * kCtasPerSm;
+    const dim3 grid(static_cast<unsigned>(tiles < resident ? tiles : resident));
     {
         KernelTimer timer(PPLB200_KERNEL_PREFILL, stream);
         prefill_tcgen05_kernel<DH><<<grid, kThreads, T::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
