@@ -57,7 +57,7 @@ struct PTraits {
     static constexpr int kKVBlockBytes = kBlockN * 128;          // one [64 rows][64 halves] block of K or V
     static constexpr int kQBytes = kColBlocks * kQBlockBytes;
     static constexpr int kKVBytes = kColBlocks * kKVBlockBytes;  // one K (or V) tile
-    static constexpr int kBarrierBytes = 256;
+    static constexpr int kBarrierBytes = 512;
     // The same for every head size (the Dh = 128 figure), so that never more than two CTAs share an SM
     // and the two 256-column TMEM allocations always fit.
     static constexpr int kSmemBytes = 32768 + (kKStages + kVStages) * 16384 + kBarrierBytes;
@@ -88,6 +88,14 @@ struct PrefillArgs {
     float scale_log2;
 };
 
+// One unit of work: a 128-row query tile of one head, as decoded by the producer warp and handed to the
+// other roles through shared memory.  head < 0: no more tiles.
+struct Tile {
+    int head, kvh, n_kv, rows_valid;
+    int64_t q_row0, kv_row0, kvlen;
+    int64_t first_row_last;  // last kv position visible to row 0 of the tile (negative: rows that see nothing)
+};
+
 struct Barriers {
     uint64_t q_full;
     uint64_t q_empty;     // the last Q K^T of a tile has completed: Q may be overwritten with the next tile's
@@ -102,11 +110,11 @@ struct Barriers {
     uint64_t pv_done[2];  // P V of the tile that used P buffer 0 / 1 has completed
     uint64_t tile_full[kTileRing];  // the producer has published a tile index in tile_ring[e]
     uint64_t tile_free[kTileRing];  // the MMA warp and the softmax threads have read tile_ring[e]
-    int tile_ring[kTileRing];
+    Tile tile_ring[kTileRing];
     uint32_t tmem_slot;
     int abort_word;
 };
-static_assert(sizeof(Barriers) <= 256, "barrier block");
+static_assert(sizeof(Barriers) <= 512, "barrier block");
 
 // ---- tcgen05 wrappers ---------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t cols) {
@@ -201,6 +209,13 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+// 256-bit store (32-byte aligned address)
+__device__ __forceinline__ void st_global_v8(void* p, const uint32_t (&r)[8]) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -360,15 +375,10 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     //                   query tile of every sequence first, then the ones before them; best balance
     //   sequence-major  t = (pb * q_tiles + qt_rev) * num_heads + head: the CTAs in flight work on
     //                   one or two sequences, whose K/V then stay in L2
-    // The producer warp draws tile indices from the global counter, drops those beyond their sequence's
-    // length and publishes the others through a small ring in shared memory; the MMA warp and the softmax
-    // threads read them there (index -1: no more tiles).  A tile that sees no kv position is zero-filled by
+    // The producer warp draws tile indices from the global counter, decodes them, drops those beyond their
+    // sequence's length and publishes the others through a small ring in shared memory; the MMA warp and the
+    // softmax threads read them there (head -1: no more tiles).  A tile that sees no kv position is zero-filled by
     // the softmax threads and ignored by the other two roles.
-    struct Tile {
-        int head, kvh, n_kv, rows_valid;
-        int64_t q_row0, kv_row0, kvlen, first_row_last;
-        bool dead_rows;
-    };
     auto decode_tile = [&](int t, Tile& ti) -> bool {
         int qt_rev, pb;
         if (a.seq_major) {
@@ -389,7 +399,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         int64_t seqlen = a.seqstarts[b + 1] - seq0;
         if (seqlen > a.max_seqlen) {
             seqlen = a.max_seqlen;
-            if (threadIdx.x == 64 && qt_rev == 0 && ti.head == 0) {
+            if (lane == 0 && qt_rev == 0 && ti.head == 0) {  // only the producer warp decodes tiles
                 atomicOr(a.status, kDevLengthClamped);
             }
         }
@@ -422,17 +432,16 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // last kv position visible to row 0 of the tile, and whether rows of this tile see nothing at all
         // (causal, more query rows than kv rows)
         ti.first_row_last = a.is_causal ? hist + i0 : kvlen - 1;
-        ti.dead_rows = ti.first_row_last < 0;
         return true;
     };
     const int total_tiles = a.total_tiles;
     // reader side of the ring: entry n of this CTA, or false after a timeout / abort
-    auto next_tile = [&](int n, int& t, bool one_lane_arrives) -> bool {
+    auto next_tile = [&](int n, Tile& ti, bool one_lane_arrives) -> bool {
         const int e = n % kTileRing;
         if (!wait_or_abort(&bars.tile_full[e], (n / kTileRing) & 1, abort_flag, a.status, kDevTmaTimeout)) {
             return false;
         }
-        t = *reinterpret_cast<volatile int*>(&bars.tile_ring[e]);
+        ti = bars.tile_ring[e];
         if (one_lane_arrives) {
             __syncwarp();  // every lane has read the entry
             if (lane == 0) {
@@ -453,38 +462,46 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         bool ok = true;
         int tiles_done = 0, kc = 0, vc = 0;  // tiles with work so far; K and V copies issued so far
         int published = 0;
-        while (ok) {
-            int t = 0;
-            if (lane == 0) {
-                t = atomicAdd(a.tile_counter, 1);
-            }
-            t = __shfl_sync(0xffffffffu, t, 0);
-            const bool last = t >= total_tiles;
-            Tile ti;
-            if (!last && !decode_tile(t, ti)) {
-                continue;  // beyond the end of its sequence: nobody needs it
-            }
-            {
+        // Draws the next tile that somebody needs, publishes it (or the end marker) and returns whether there
+        // was one.  Costs an atomic and two dependent global loads, so it is called one tile ahead.
+        auto fetch = [&](Tile& out) -> bool {
+            for (;;) {
+                int t = 0;
+                if (lane == 0) {
+                    t = atomicAdd(a.tile_counter, 1);
+                }
+                t = __shfl_sync(0xffffffffu, t, 0);
+                const bool last = t >= total_tiles;
+                if (!last && !decode_tile(t, out)) {
+                    continue;  // beyond the end of its sequence: nobody needs it
+                }
+                if (last) {
+                    out.head = -1;
+                }
                 const int e = published % kTileRing;
                 if (published >= kTileRing) {
                     ok = wait_or_abort(&bars.tile_free[e], ((published / kTileRing) - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                     if (!ok) {
-                        break;
+                        return false;
                     }
                 }
                 if (lane == 0) {
-                    bars.tile_ring[e] = last ? -1 : t;
+                    bars.tile_ring[e] = out;
                     mbar_arrive(&bars.tile_full[e]);
                 }
                 __syncwarp();
                 ++published;
+                return !last;
             }
-            if (last) {
-                break;
-            }
-            if (ti.n_kv == 0) {
+        };
+        Tile ti, nxt;
+        bool have = fetch(ti);
+        while (ok && have) {
+            if (ti.n_kv == 0) {  // zero-filled by the softmax threads
+                have = fetch(ti);
                 continue;
             }
+            bool fetched = false, have_next = false;
             if (tiles_done > 0) {
                 ok = wait_or_abort(&bars.q_empty, (tiles_done - 1) & 1, abort_flag, a.status, kDevMmaTimeout);
                 if (!ok) {
@@ -501,6 +518,14 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             __syncwarp();
             ++tiles_done;
             for (int i = 0; ok && i <= ti.n_kv; ++i) {
+                if (i == kKStages) {
+                    // every stage of this tile's rings is on its way: now look up the next tile
+                    have_next = fetch(nxt);
+                    fetched = true;
+                    if (!ok) {
+                        break;
+                    }
+                }
                 if (i < ti.n_kv) {
                     const int s = kc % kKStages;
                     if (kc >= kKStages) {
@@ -540,6 +565,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     ++vc;
                 }
             }
+            if (ok && !fetched) {
+                have_next = fetch(nxt);
+            }
+            ti = nxt;
+            have = have_next;
         }
         if (*abort_flag) {
             // drain: every copy this warp issued must have landed before the CTA may exit
@@ -566,12 +596,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         bool ok = true;
         int tiles_done = 0, kc = 0, vc = 0;  // tiles with work so far; Q K^T and P V issued so far (all tiles)
         for (int n = 0; ok; ++n) {
-            int t;
-            if (!next_tile(n, t, true) || t < 0) {
+            Tile ti;
+            if (!next_tile(n, ti, true) || ti.head < 0) {
                 break;
             }
-            Tile ti;
-            if (!decode_tile(t, ti) || ti.n_kv == 0) {
+            if (ti.n_kv == 0) {
                 continue;
             }
             ok = wait_or_abort(&bars.q_full, tiles_done & 1, abort_flag, a.status, kDevTmaTimeout);
@@ -652,17 +681,13 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         bool ok = true;
         int pc = 0;  // score tiles consumed = P tiles produced so far (all tiles of this CTA)
         for (int n = 0; ok; ++n) {
-            int t;
-            if (!next_tile(n, t, false) || t < 0) {
-                break;
-            }
             Tile ti;
-            if (!decode_tile(t, ti)) {
-                continue;
+            if (!next_tile(n, ti, false) || ti.head < 0) {
+                break;
             }
             const int head = ti.head, rows_valid = ti.rows_valid, n_kv = ti.n_kv;
             const int64_t q_row0 = ti.q_row0, kvlen = ti.kvlen, first_row_last = ti.first_row_last;
-            const bool dead_rows = ti.dead_rows;
+            const bool dead_rows = first_row_last < 0;
             if (n_kv == 0) {
                 // nothing visible to any row of the tile: zeros
                 for (int idx = threadIdx.x - 64; idx < rows_valid * (DH / 8); idx += 128) {
@@ -781,24 +806,31 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 const float inv = l_sum > 0.0f ? 1.0f / l_sum : 0.0f;
                 __half* dst = a.out + ((q_row0 + r) * a.num_heads + head) * DH;
 #pragma unroll
-                for (int c = 0; c < DH / 32; ++c) {
-                    uint32_t v[32];
-                    tmem_ld32(t_o + c * 32, v);
+                for (int c = 0; c < DH / 64; ++c) {
+                    uint32_t v[2][32];  // 64 columns per round: two loads in flight
+                    tmem_ld32(t_o + c * 64, v[0]);
+                    tmem_ld32(t_o + c * 64 + 32, v[1]);
                     tmem_wait_ld();
-                    if (c == DH / 32 - 1) {
+                    if (c == DH / 64 - 1) {
                         // O is in registers: the MMA warp may start the next tile's accumulation
                         tc_fence_before();
                         mbar_arrive(&bars.o_free);
                     }
                     if (r < rows_valid) {
+                        // a thread owns a whole row, so a warp's store touches 32 rows: 32-byte stores fill whole
+                        // sectors and halve the number of scattered requests
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            uint4 o4;
-                            o4.x = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q]) * inv, __uint_as_float(v[8 * q + 1]) * inv));
-                            o4.y = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 2]) * inv, __uint_as_float(v[8 * q + 3]) * inv));
-                            o4.z = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 4]) * inv, __uint_as_float(v[8 * q + 5]) * inv));
-                            o4.w = h2_as_u32(__floats2half2_rn(__uint_as_float(v[8 * q + 6]) * inv, __uint_as_float(v[8 * q + 7]) * inv));
-                            *reinterpret_cast<uint4*>(dst + c * 32 + q * 8) = o4;
+                        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                            for (int q = 0; q < 2; ++q) {
+                                uint32_t o[8];
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    o[e] = h2_as_u32(__floats2half2_rn(__uint_as_float(v[h][16 * q + 2 * e]) * inv,
+                                                                       __uint_as_float(v[h][16 * q + 2 * e + 1]) * inv));
+                                }
+                                st_global_v8(dst + c * 64 + h * 32 + q * 16, o);
+                            }
                         }
                     }
                 }
@@ -940,6 +972,10 @@ static int launch_attention_core(const void* query, const void* k_src, const voi
         return rc;
     }
 
+    if ((reinterpret_cast<uintptr_t>(a.out) & 31u) != 0) {
+        fprintf(stderr, "[ppl_nn_b200] attn_output must be 32-byte aligned\n");
+        return PPLB200_INVALID_VALUE;
+    }
     a.q_tiles = static_cast<int32_t>(q_tiles_per_seq);
     // K and V of everything this call may read against half of a 126 MB L2
     a.seq_major = static_cast<uint64_t>(kv_rows) * num_kv_heads * DH * 4 > (64ull << 20) ? 1 : 0;
