@@ -2,10 +2,15 @@
 // dense contraction on the 5th-generation tensor cores: tcgen05.mma with TMEM accumulators, operands
 // staged in shared memory by TMA (no multicast), fp16 inputs, fp32 accumulation.
 //
-// One CTA computes a 128-row query tile of one (sequence, query head); two CTAs share an SM, so that
-// one CTA's MMAs run under the other's softmax:
-//   warp 0      TMA producer: the Q tile once, then K tiles (3-stage ring) and V tiles (2-stage ring)
-//               of 64 rows each
+// The unit of work is a 128-row query tile of one (sequence, query head).  The CTAs are persistent: two
+// per SM (so that one CTA's MMAs run under the other's softmax), each drawing tiles from a global counter
+// until none is left.  TMEM, the barriers and the stage rings live for the whole kernel; their phases run
+// on from tile to tile, so the loads and the first Q K^T of the next tile are under way while the softmax
+// threads finish the current one (a fresh CTA per tile cost 6.3 us of launch, set-up, load latency and
+// epilogue per tile against ~1 us per 64-row kv block):
+//   warp 0      draws and decodes tiles (one ahead) and hands them to the other roles through a ring in
+//               shared memory; TMA producer: the Q tile, then K tiles (3-stage ring) and V tiles (2-stage
+//               ring) of 64 rows each
 //   warp 1      allocates TMEM (256 columns) and issues the MMAs: S = Q K^T into a 64-column TMEM buffer
 //               (both operands in shared memory), then O += P V with P read from TMEM (the A operand)
 //               and V from shared memory; completion is reported to mbarriers with tcgen05.commit
@@ -14,8 +19,9 @@
 //               tiles only, running maximum in the exp2 domain (the O accumulator is rescaled in TMEM
 //               only when the maximum grew by more than 2^8), write P as packed fp16 into one of two
 //               TMEM buffers with tcgen05.st, so that the next tile's softmax does not wait for this
-//               tile's P V, and finally divide O by the row sum and store fp16 rows.  The row sum adds
-//               the fp16-rounded P values, the very numbers the numerator uses.
+//               tile's P V, and finally divide O by the row sum and store fp16 rows (O is handed back to
+//               the MMA warp as soon as it is in registers).  The row sum adds the fp16-rounded P values,
+//               the very numbers the numerator uses.
 // Both the producer and the MMA warp run warp-uniform code (every lane waits, an elected lane issues).
 // K/V come from this call's fp16 current_key/current_value (the default), or, with
 // enable_cache_prefill, from an fp16 staging copy of the INT8 cache rows (history included) that a
