@@ -22,7 +22,9 @@
  *   start_pos      [batch]     tokens already cached
  *   cache          int8,  cache_layout 0: (MaxT, L, 2, Hkv, Dh)       3: (L, 2, Hkv, MaxT, Dh)
  *   scale          fp16,  same with Dh/quant_group in place of Dh
- *   attn_output    [T, num_heads, head_dim]        fp16
+ *   attn_output    [T, num_heads, head_dim]        fp16, 32-byte aligned (PPLB200_INVALID_VALUE otherwise)
+ * All tensors are dense (no padding between rows); query, current_key, current_value, cache and scale
+ * must be 16-byte aligned, which every device allocation is.
  * The first `decoding_batches` sequences are decode sequences (one query token each); the rest
  * are prefill sequences.
  */

@@ -5,6 +5,7 @@
 #include <stdio.h>
 
 #include <atomic>
+#include <initializer_list>
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -144,6 +145,22 @@ static int validate(const pplb200_attn_params* p) {
     return PPLB200_SUCCESS;
 }
 
+// The kernels use 16-byte vector accesses and TMA on the payload tensors and 8-byte loads on the index
+// tensors; a misaligned pointer would fault on the device, so it is refused here.
+static bool misaligned(std::initializer_list<const void*> payload, std::initializer_list<const void*> index) {
+    for (const void* q : payload) {
+        if (reinterpret_cast<uintptr_t>(q) & 15u) {
+            return true;
+        }
+    }
+    for (const void* q : index) {
+        if (reinterpret_cast<uintptr_t>(q) & 7u) {
+            return true;
+        }
+    }
+    return false;
+}
+
 static CacheGeom make_geom(const pplb200_attn_params& p) {
     CacheGeom g;
     g.stride_s = p.cache_stride_s;
@@ -233,6 +250,9 @@ int pplb200_kv_append_i8g8(const pplb200_attn_params* p, const void* current_key
     if (!current_key || !current_value || !seqstarts || !cachestarts || !start_pos || !cache) {
         return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
     }
+    if (misaligned({current_key, current_value, cache, scale}, {seqstarts, cachestarts, start_pos})) {
+        return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
+    }
     DeviceInfo di;
     rc = require_device(&di);
     if (rc != PPLB200_SUCCESS) {
@@ -257,6 +277,9 @@ int pplb200_kv_gather_dequant(const pplb200_attn_params* p, const int64_t* kvsta
     }
     if (total_kv < 0) {
         return fail(PPLB200_INVALID_VALUE, "total_kv is negative");
+    }
+    if (misaligned({cache, scale, key_out, value_out}, {kvstarts, cachestarts})) {
+        return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
     }
     DeviceInfo di;
     rc = require_device(&di);
@@ -316,6 +339,10 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     if (!query || !current_key || !current_value || !seqstarts || !kvstarts || !cachestarts || !start_pos || !cache ||
         !attn_output) {
         return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    if (misaligned({query, current_key, current_value, cache, scale, attn_output},
+                   {seqstarts, kvstarts, cachestarts, start_pos})) {
+        return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
     }
     DeviceInfo di;
     rc = require_device(&di);
@@ -408,6 +435,9 @@ int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const vo
     if (!query || !key || !value || !seqstarts || !kvstarts || !attn_output) {
         return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
     }
+    if (misaligned({query, key, value, attn_output}, {seqstarts, kvstarts})) {
+        return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
+    }
     DeviceInfo di;
     int rc = require_device(&di);
     if (rc != PPLB200_SUCCESS) {
@@ -485,6 +515,9 @@ int pplb200_rope_forward(const pplb200_rope_params* p, const void* query, const 
     if (!query || !key || !seqstarts || !start_pos || !rotated_query || !rotated_key) {
         return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
     }
+    if (misaligned({query, key, rotated_query, rotated_key}, {seqstarts, start_pos})) {
+        return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
+    }
     DeviceInfo di;
     rc = require_device(&di);
     if (rc != PPLB200_SUCCESS) {
@@ -523,6 +556,9 @@ int pplb200_rope_kv_append_i8g8(const pplb200_rope_params* p, const pplb200_attn
     }
     if (!query || !key || !value || !seqstarts || !cachestarts || !start_pos || !rotated_query || !cache || !scale) {
         return fail(PPLB200_NOT_FOUND, "a required tensor pointer is null");
+    }
+    if (misaligned({query, key, value, rotated_query, rotated_key, cache, scale}, {seqstarts, cachestarts, start_pos})) {
+        return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
     }
     DeviceInfo di;
     rc = require_device(&di);

@@ -121,6 +121,21 @@ def test_null_pointers_and_missing_device(built_lib, pkg):
         assert built_lib.status_str(rc) == "RC_NO_DEVICE_CODE"
 
 
+def test_misaligned_pointers_are_refused_before_any_launch(built_lib, pkg):
+    """16-byte vector accesses and TMA on the payload tensors, 8-byte loads on the index tensors: a pointer
+    that would fault on the device is an RC_INVALID_VALUE on the host."""
+    from ppl_nn_b200 import capi
+    p = _params(built_lib, capi)
+    fake = ctypes.c_void_p(4096)
+    for bad_slot, bad in ((0, 4096 + 8), (3, 4096 + 4), (7, 4096 + 2)):  # query, seqstarts, cache
+        args = [fake] * 9
+        args[bad_slot] = ctypes.c_void_p(bad)
+        rc = built_lib.mhca_forward(p, *args, fake, 1 << 30, fake, None)
+        assert built_lib.status_str(rc) == "RC_INVALID_VALUE", bad_slot
+    rc = built_lib.kv_append(p, ctypes.c_void_p(4096 + 2), fake, fake, fake, fake, fake, fake, None)
+    assert built_lib.status_str(rc) == "RC_INVALID_VALUE"
+
+
 def test_missing_library_fails_loudly(pkg, tmp_path):
     from ppl_nn_b200 import capi
     with pytest.raises(FileNotFoundError):
