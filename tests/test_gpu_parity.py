@@ -258,6 +258,19 @@ def test_prefill_only(orc, torch_dev, pkg, hq, hkv, dh, lens):
     run_case(orc, torch_dev, hc)
 
 
+def test_prefill_many_short_sequences_through_the_tile_ring(orc, torch_dev, pkg):
+    """400 prompts of 1..290 tokens: 4 800 tile indices for 296 persistent CTAs, two thirds of them beyond
+    the end of their sequence (dropped by the producer warp), so every CTA draws many tiles, wraps the
+    tile ring several times and changes between 1-, 2- and 5-block tiles."""
+    from ppl_nn_b200 import workloads
+    lens = tuple(1 + (37 * i) % 290 for i in range(400))
+    spec = _spec(num_heads=4, num_kv_heads=2, head_dim=128, n_decode=0, kv_dist="list", kv_list=(),
+                 n_prefill=len(lens), seed=33)
+    hc = workloads.host_case(spec)
+    hc = _case_with_index(hc, workloads.make_index([], lens), spec)
+    run_case(orc, torch_dev, hc)
+
+
 def _case_with_index(hc, idx, spec, prefill_hist=None):
     """Re-draw the tensors of a HostCase for an explicit index."""
     from ppl_nn_b200 import workloads
