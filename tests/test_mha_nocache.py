@@ -133,6 +133,7 @@ CASES = [
     ([5, 128, 33], [69, 200, 33], 4, 1, 128),             # kv longer than q: mask aligned to the end
     ([9, 4], [3, 0], 4, 2, 64),                           # fewer kv rows than query rows, and none at all
     ([300], [1000], 32, 8, 128),
+    ([300] * 40, [10] * 40, 4, 2, 128),                   # runs of query tiles that see no kv row at all
 ]
 
 
