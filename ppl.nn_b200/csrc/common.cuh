@@ -201,7 +201,7 @@ __device__ __forceinline__ __half2 biased_bytes_to_half2(uint32_t x) {
 // IEEE division and round-half-even throughout: the file must be compiled without fast-math so
 // that codes and scales are reproducible bit for bit on any IEEE host.
 //
-// The eight divisions are not carried out one by one.  q' = x * fl(1/s) lies within 4e-5 of fl(x/s)
+// The eight divisions are not carried out one by one.  q' = x * (1/s) lies within 4e-5 of fl(x/s)
 // whenever |q'| <= 128, so if q' is further than that from every half-integer, rint(q') IS
 // rint(fl(x/s)); only elements that close to a rounding boundary (a few in ten thousand), and
 // anything non-finite, take the true division.  The rounding itself is the add-and-subtract of
@@ -238,16 +238,19 @@ __device__ __forceinline__ void quant_group8(const uint4 in, uint2& codes, __hal
     uint32_t w[2] = {0u, 0u};
     if (s != 0.0f) {
         constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-        const float r = __frcp_rn(s);
+        // 1 ulp off at most (rcp.approx): q' is then within 127.1 * (2^-23 + 2^-24 + 2^-24) = 3e-5 of fl(x/s)
+        float r;
+        asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(s));
         uint32_t ub[8];
-        bool all_safe = true;
+        // With s a NORMAL half, s >= (a/127)(1 - 2^-11), hence |x/s| <= 127.07: no code can need the clamp.
+        // A subnormal scale can be far below a/127; such groups (|x| < 0.008 throughout) take the exact path.
+        bool all_safe = s >= 6.103515625e-05f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const float qf = __fmul_rn(v[i], r);
             const float u = __fadd_rn(qf, kMagic);
             const float t = __fsub_rn(u, kMagic);  // rint(qf) for |qf| < 2^22
-            // |qf| <= 127.4 also means that no clamp is needed; false for NaN
-            all_safe = all_safe && fabsf(qf) <= 127.4f && fabsf(__fsub_rn(qf, t)) < 0.4999f;
+            all_safe = all_safe && fabsf(__fsub_rn(qf, t)) < 0.4999f;  // false for NaN (an infinite x or s)
             ub[i] = __float_as_uint(u);  // low mantissa byte = the code in two's complement
         }
         if (!all_safe) {  // rare (about one group in a thousand): redo the group with true divisions

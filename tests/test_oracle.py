@@ -259,3 +259,41 @@ def test_uncached_attention_agrees_with_torch_sdpa(orc, causal):
         vv = torch.from_numpy(v[ks[b]:ks[b + 1]].astype(np.float32)).repeat_interleave(rep, dim=1)
         ref = _sdpa(qq, kk, vv, causal_offset=(kvlens[b] - seqlens[b]) if causal else None).numpy()
         np.testing.assert_allclose(got[ss[b]:ss[b + 1]], ref, atol=1e-3, rtol=1e-3)
+
+
+def test_fast_quantiser_path_of_the_cuda_kernels_gives_the_exact_codes(oracle_mod):
+    """The CUDA quantiser (csrc/common.cuh::quant_group8) avoids the eight divisions of a group: it multiplies
+    by an approximate reciprocal of the scale (1 ulp off at most), rounds with the add-and-subtract of
+    1.5 * 2^23, and trusts the result only if the scale is a normal half and every product is further than
+    1e-4 from a half-integer; any other group is redone with the true divisions.  Restated here in numpy
+    float32 (IEEE, like the device's non-fused operations) with the reciprocal pushed one ulp either way:
+    whenever the fast path trusts itself its codes are the codes of the published formula."""
+    rng = np.random.default_rng(17)
+    magic = np.float32(12582912.0)
+    total_fast = 0
+    for mode, scale in enumerate([1.0, 1e-3, 300.0, 3e-5, 6e4, None]):
+        n = 200_000
+        mag = np.float32(scale) if scale is not None else (10.0 ** rng.uniform(-4.5, 4.5, (n, 1))).astype(np.float32)
+        x = (rng.standard_normal((n, 8)).astype(np.float32) * mag).astype(np.float16)
+        # adversarial half: values at (k + 0.5) * s of their own group's scale
+        a0 = np.abs(x.astype(np.float32)).max(axis=1)
+        s0 = (a0 / np.float32(127.0)).astype(np.float16).astype(np.float32)
+        k = rng.integers(-126, 126, (n, 7)).astype(np.float32) + np.float32(0.5)
+        adv = rng.random(n) < 0.5
+        x[adv, 1:] = (k[adv] * s0[adv, None]).astype(np.float16)
+        codes, scales = oracle_mod.np_quant_groups(x)       # the published formula (exact divisions)
+        v = x.astype(np.float32)
+        s = scales.astype(np.float32).reshape(n, 1)
+        ok = np.isfinite(s[:, 0]) & (s[:, 0] != 0)
+        v, s, codes = v[ok], s[ok], codes.reshape(n, 8)[ok]
+        with np.errstate(over="ignore", invalid="ignore"):
+            r0 = (np.float32(1.0) / s).astype(np.float32)
+            for r in (r0, np.nextafter(r0, np.float32(np.inf)), np.nextafter(r0, np.float32(0))):
+                qf = (v * r).astype(np.float32)
+                u = (qf + magic).astype(np.float32)
+                t = (u - magic).astype(np.float32)
+                safe = (s[:, 0] >= np.float32(6.103515625e-05)) & (np.abs((qf - t).astype(np.float32)) < np.float32(0.4999)).all(axis=1)
+                fast = (u.view(np.uint32) & 0xFF).astype(np.uint8).view(np.int8)
+                np.testing.assert_array_equal(fast[safe], codes[safe])
+                total_fast += int(safe.sum())
+    assert total_fast > 1_000_000  # the fast path is the common case, so the check is not vacuous
