@@ -5,6 +5,7 @@ the CPU oracle to chew through gigabytes:
   * softmax weights sum to one: with every V row dequantising to the same vector, the output IS that
     vector, for every sequence and head of the batch;
   * split-k invariance: stream-k ranges, whole-segment scheduling and forced splitting agree;
+  * linearity in V: doubling the V scales doubles the output bit for bit;
   * append -> gather round trip within half a quantisation step for every new token."""
 import numpy as np
 import pytest
@@ -186,6 +187,27 @@ def test_softmax_weights_sum_to_one_at_full_size(dev, pkg):
     assert float(diff.max()) <= 2.0 ** -10 + 1e-7, float(diff.max())
     assert float((diff > 0).float().mean()) < 0.05
     del dc, out
+    torch.cuda.empty_cache()
+
+
+def test_output_is_linear_in_v_at_full_size(dev, pkg):
+    """Doubling every V scale of the cache (a power of two, so every product and every partial sum doubles
+    exactly) must double the output bit for bit: 512 sequences x 64 heads of the LLaMA-2-70B workload, whatever
+    the split points and partial merges are."""
+    import torch
+    from ppl_nn_b200 import capi, workloads
+    spec = workloads.SPECS["cfg4_llama70b_decode"]
+    dc = workloads.device_case(spec, dev)
+    op = _op(dc, spec)
+    once = _forward(op, dc, phase_mask=capi.PHASE_DECODE).clone()   # attend to the cache as it is, no append
+    dc.scale[:, 0, 1] *= 2                                          # (MaxT, L, 2, H, Dh/8): the V scales
+    twice = _forward(op, dc, phase_mask=capi.PHASE_DECODE)
+    assert op.device_status() == 0
+    a, b = once.float(), twice.float()
+    normal = a.abs() >= 2.0 ** -13                                  # 2x of a subnormal half need not be exact
+    assert bool(normal.float().mean() > 0.9)
+    assert bool((b[normal] == 2 * a[normal]).all())
+    del dc, once, twice
     torch.cuda.empty_cache()
 
 
