@@ -6,6 +6,7 @@ the CPU oracle to chew through gigabytes:
     vector, for every sequence and head of the batch;
   * split-k invariance: stream-k ranges, whole-segment scheduling and forced splitting agree;
   * linearity in V: doubling the V scales doubles the output bit for bit;
+  * causality of the prefill: rewriting the tail of every prompt leaves the rows before it bit-identical;
   * append -> gather round trip within half a quantisation step for every new token."""
 import numpy as np
 import pytest
@@ -208,6 +209,34 @@ def test_output_is_linear_in_v_at_full_size(dev, pkg):
     assert bool(normal.float().mean() > 0.9)
     assert bool((b[normal] == 2 * a[normal]).all())
     del dc, once, twice
+    torch.cuda.empty_cache()
+
+
+def test_prefill_is_causal_at_full_size(dev, pkg):
+    """The 8 prompts of the mixed configuration (512 .. 2048 tokens): overwriting the last 100 tokens of every
+    prompt (query, key and value) must leave the output rows before them bit-identical, whichever CTA computed
+    them and in whatever order the tiles were drawn."""
+    import torch
+    from ppl_nn_b200 import workloads
+    spec = workloads.SPECS["cfg3_prefill_only"]
+    dc = workloads.device_case(spec, dev)
+    idx = dc.index
+    op = _op(dc, spec)
+    before = _forward(op, dc).clone()
+    assert op.device_status() == 0
+    keep = torch.ones(dc.query.shape[0], dtype=torch.bool, device=dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    for b in range(idx.batch):
+        lo, hi = int(idx.seqstarts[b + 1]) - 100, int(idx.seqstarts[b + 1])
+        keep[lo:hi] = False
+        for t in (dc.query, dc.current_key, dc.current_value):
+            t[lo:hi] = torch.randn(t[lo:hi].shape, generator=g, device=dev).to(torch.float16)
+    after = _forward(op, dc)
+    assert op.device_status() == 0
+    assert bool((before[keep].view(torch.int16) == after[keep].view(torch.int16)).all())
+    assert not bool((before[~keep].view(torch.int16) == after[~keep].view(torch.int16)).all())
+    del dc, before, after
     torch.cuda.empty_cache()
 
 
