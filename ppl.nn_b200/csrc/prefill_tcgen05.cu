@@ -1006,7 +1006,7 @@ static int launch_attention_core(const void* query, const void* k_src, const voi
         attr_set = true;
     }
     const int64_t tiles = q_tiles_per_seq * a.prefill_batches * num_heads;
-    if (tiles > 0x7fffffff) {
+    if (tiles > 0x7fffffff - (1 << 20)) {  // the counter runs past the last tile by one draw per CTA
         return PPLB200_UNSUPPORTED;
     }
     a.total_tiles = static_cast<int32_t>(tiles);
