@@ -175,6 +175,19 @@ class Op:
         rc = self.d.pplb200_host_op_run(self.handle, ins, len(inputs), outs, len(outputs))
         return retcode_str(rc), list(outs)
 
+    def bind(self, inputs: list, outputs: list):
+        """For a loop that runs the operator on the same buffers every step: builds the argument arrays once
+        and returns (call, output structs); call() runs the operator and returns the RetCode name."""
+        ins = (HostTensor * len(inputs))(*inputs)
+        outs = (HostTensor * len(outputs))(*outputs)
+        run, handle, n_in, n_out = self.d.pplb200_host_op_run, self.handle, len(inputs), len(outputs)
+
+        def call() -> str:
+            rc = run(handle, ins, n_in, outs, n_out)
+            return "RC_SUCCESS" if rc == 0 else retcode_str(rc)
+
+        return call, outs
+
     def run(self, inputs: list, outputs: list):
         """inputs: torch tensors / numpy arrays / ints / None; outputs: torch tensors to write into, or
         None to let the kernel allocate.  Raises RetCodeError unless RC_SUCCESS."""

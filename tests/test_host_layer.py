@@ -179,6 +179,17 @@ def test_mhca_rejects_tensors_the_kernels_would_overrun(host, engine, which, sha
     assert rc == "RC_INVALID_VALUE"
 
 
+def test_bound_call_gives_the_same_return_codes(host, engine):
+    """Op.bind builds the argument arrays once; its call() must behave like run_raw on the same structs."""
+    for attrs, expect in ((dict(cache_layout=1), "RC_UNSUPPORTED"), (dict(cache_mode=1), "RC_INVALID_VALUE")):
+        op = host.Op(engine, "MultiHeadCacheAttention", {**MHCA_ATTRS, **attrs})
+        ins, outs, keep = _mhca_inputs(host)
+        call, bound_outs = op.bind(ins, outs)
+        assert call() == expect == op.run_raw(ins, outs)[0]
+        assert call() == expect  # and again, with the same arrays
+        assert list(bound_outs[0].dims[:3]) == [4, 8, 128]  # Reshape ran: attn_output took query's shape
+
+
 def test_mhca_empty_attn_mask_counts_as_absent_and_output_takes_query_shape(host, engine):
     import torch
     if torch.cuda.is_available():
