@@ -266,7 +266,9 @@ enum {
     PPLB200_DEV_OK = 0,
     PPLB200_DEV_TMA_WAIT_TIMEOUT = 1,  /* a wait for a bulk-tensor copy ran out of iterations    */
     PPLB200_DEV_MMA_WAIT_TIMEOUT = 2,  /* a wait for a tensor-core commit ran out of iterations   */
-    PPLB200_DEV_LENGTH_CLAMPED = 4     /* a sequence exceeded max_kvlen / max_seqlen and was cut   */
+    PPLB200_DEV_LENGTH_CLAMPED = 4,    /* a sequence exceeded max_kvlen / max_seqlen and was cut   */
+    PPLB200_DEV_ROW_OUT_OF_RANGE = 8   /* cachestarts/start_pos named a row outside [0, max_tokens):
+                                          that row was neither read nor written                     */
 };
 
 /* Name of a status code ("RC_SUCCESS", ...).  Never null. */

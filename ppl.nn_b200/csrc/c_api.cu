@@ -123,6 +123,9 @@ static int validate(const pplb200_attn_params* p) {
     if (p->cache_mode == 1 && (p->page_size <= 0 || p->page_size % 16 != 0 || p->cachestart_stride_b <= 0)) {
         return fail(PPLB200_INVALID_VALUE, "paged cache needs page_size % 16 == 0 and 2-d cachestarts");
     }
+    if (p->cache_mode == 1 && p->max_kvlen > p->cachestart_stride_b * static_cast<int64_t>(p->page_size)) {
+        return fail(PPLB200_INVALID_VALUE, "max_kvlen exceeds what a page-table row (cachestarts.dim(1) pages) can hold");
+    }
     if (p->num_layer <= 0 || p->layer_idx < 0 || p->layer_idx >= p->num_layer) {
         return fail(PPLB200_INVALID_VALUE, "layer_idx out of range");
     }
@@ -259,7 +262,7 @@ int pplb200_kv_append_i8g8(const pplb200_attn_params* p, const void* current_key
         return rc;
     }
     return launch_kv_append(*p, make_geom(*p), current_key, current_value, seqstarts, cachestarts, start_pos, cache,
-                            scale, di.sm_count, static_cast<cudaStream_t>(stream));
+                            scale, 0, nullptr, di.sm_count, static_cast<cudaStream_t>(stream));
 }
 
 int pplb200_kv_gather_dequant(const pplb200_attn_params* p, const int64_t* kvstarts, const int64_t* cachestarts,
@@ -369,29 +372,32 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     uint32_t* status = reinterpret_cast<uint32_t*>(ws + w.decode.off_header);  // first word of the header
 
-    if (mask & PPLB200_PHASE_APPEND) {
+    // Order of the launches.  The planning kernel of the decode part (or a memset) clears the status word
+    // first, so that every later kernel of the call can report through it.  The decode kernel appends the new
+    // tokens of the decode sequences itself; the append kernel only sees the remaining sequences, and runs
+    // behind the decode part, which does not depend on it.
+    const bool do_append = (mask & PPLB200_PHASE_APPEND) != 0;
+    const bool do_decode = (mask & PPLB200_PHASE_DECODE) != 0 && p->decoding_batches > 0;
+    const bool do_prefill = (mask & PPLB200_PHASE_PREFILL) != 0 && p->decoding_batches < p->batch;
+    if (do_decode) {
+        rc = launch_decode(*p, geom, w.decode, query, do_append ? current_key : nullptr,
+                           do_append ? current_value : nullptr, seqstarts, cachestarts, start_pos, cache, scale,
+                           workspace, attn_output, stream);
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+    } else if (cudaMemsetAsync(status, 0, 4, stream) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(PPLB200_DEVICE_RUNTIME_ERROR, "cudaMemsetAsync(status) failed");
+    }
+    if (do_append) {
         rc = launch_kv_append(*p, geom, current_key, current_value, seqstarts, cachestarts, start_pos, cache, scale,
-                              di.sm_count, stream);
+                              do_decode ? p->decoding_batches : 0, status, di.sm_count, stream);
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
     }
-    bool status_reset = false;
-    if ((mask & PPLB200_PHASE_DECODE) && p->decoding_batches > 0) {
-        rc = launch_decode(*p, geom, w.decode, query, seqstarts, cachestarts, start_pos, cache, scale, workspace,
-                           attn_output, stream);  // its planning kernel clears the status word
-        if (rc != PPLB200_SUCCESS) {
-            return rc;
-        }
-        status_reset = true;
-    }
-    if ((mask & PPLB200_PHASE_PREFILL) && p->decoding_batches < p->batch) {
-        if (!status_reset) {
-            if (cudaMemsetAsync(status, 0, 4, stream) != cudaSuccess) {
-                (void)cudaGetLastError();
-                return fail(PPLB200_DEVICE_RUNTIME_ERROR, "cudaMemsetAsync(status) failed");
-            }
-        }
+    if (do_prefill) {
         rc = launch_prefill(*p, geom, w.prefill, query, current_key, current_value, seqstarts, cachestarts, start_pos,
                             cache, scale, ws + w.off_prefill, status, attn_output, stream);
         if (rc != PPLB200_SUCCESS) {
@@ -582,8 +588,8 @@ int pplb200_rope_kv_append_i8g8(const pplb200_rope_params* p, const pplb200_attn
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
-        return launch_kv_append(*attn, geom, rotated_key, value, seqstarts, cachestarts, start_pos, cache, scale,
-                                di.sm_count, st);
+        return launch_kv_append(*attn, geom, rotated_key, value, seqstarts, cachestarts, start_pos, cache, scale, 0,
+                                nullptr, di.sm_count, st);
     }
     return launch_rope(*p, attn, &geom, query, key, value, seqstarts, start_pos, cachestarts, workspace, rotated_query,
                        rotated_key, cache, scale, di.sm_count, st);

@@ -15,11 +15,14 @@ namespace pplb200 {
 constexpr uint32_t kDevOk = 0;
 constexpr uint32_t kDevTmaTimeout = 1;
 constexpr uint32_t kDevMmaTimeout = 2;
+constexpr uint32_t kDevLengthClamped = 4;   // a sequence was longer than max_kvlen / max_seqlen and was clamped
+constexpr uint32_t kDevRowOutOfRange = 8;   // an index tensor named a cache row outside [0, max_tokens): access skipped
 
-// Upper bound on polls of one mbarrier wait.  One poll is a try_wait with a hardware time slice,
-// so this is tens of milliseconds at least -- far beyond any legitimate copy latency.
-constexpr uint32_t kMaxWaitPolls = 1u << 20;
-constexpr uint32_t kDevLengthClamped = 4;  // a sequence was longer than max_kvlen / max_seqlen and was clamped
+// Time budget of ONE bounded wait in every kernel of the library, in SM clock cycles: about 100 ms at
+// 2 GHz, four orders of magnitude beyond any legitimate copy or MMA latency.  A wait that exhausts it
+// records a status code; the waiting thread then stops waiting altogether, so a stuck kernel ends after
+// roughly one budget per warp that waits, not one per wait.
+constexpr long long kWaitBudgetCycles = 200000000LL;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -80,9 +83,10 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar_addr, uint32_t p
 #define PPLB200_WAIT_HINT_NS 20000
 #endif
 
-// Bounded wait.  Returns false when the time budget (about a second of SM clocks) ran out; the
-// caller records a status code and carries on with whatever is in shared memory; nothing hangs.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+// Bounded wait.  Returns false when kWaitBudgetCycles ran out; the caller records a status code and
+// carries on with whatever is in shared memory; nothing hangs.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+                                                  long long budget = kWaitBudgetCycles) {
     const uint32_t addr = smem_u32(bar);
     if (mbar_try_wait_hint(addr, parity, PPLB200_WAIT_HINT_NS)) {
         return true;
@@ -92,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         if (mbar_try_wait_hint(addr, parity, PPLB200_WAIT_HINT_NS)) {
             return true;
         }
-        if (clock64() - t0 > 2000000000LL) {
+        if (clock64() - t0 > budget) {
             return false;
         }
     }
@@ -275,15 +279,26 @@ struct CacheGeom {
     int32_t page_size;
 };
 
+// Cache row of position `pos` of sequence b, or -1 when the page table has no such page.  The result still
+// has to be checked against [0, max_tokens) by the caller (cache_row_ok): the index tensors come from outside.
 __device__ __forceinline__ int64_t cache_row(const CacheGeom& g, const int64_t* __restrict__ cachestarts, int64_t b,
                                              int64_t pos) {
     if (g.cache_mode == 0) {
-        return cachestarts[b] + pos;
+        const int64_t first = cachestarts[b];
+        return (first < 0 || pos < 0) ? -1 : first + pos;
     }
     // positions and page sizes are below 2^31 (checked on the host), so the division is a 32-bit one
     const uint32_t p = static_cast<uint32_t>(pos);
     const uint32_t page = p / static_cast<uint32_t>(g.page_size);
-    return cachestarts[b * g.cachestart_stride_b + page] + (p - page * static_cast<uint32_t>(g.page_size));
+    if (pos < 0 || static_cast<int64_t>(page) >= g.cachestart_stride_b) {
+        return -1;
+    }
+    const int64_t first = cachestarts[b * g.cachestart_stride_b + page];
+    return first < 0 ? -1 : first + (p - page * static_cast<uint32_t>(g.page_size));
+}
+
+__device__ __forceinline__ bool cache_row_ok(int64_t row, int64_t max_tokens) {
+    return row >= 0 && row < max_tokens;
 }
 
 __device__ __forceinline__ int64_t cache_offset(const CacheGeom& g, int64_t row, int kv, int head) {

@@ -32,8 +32,16 @@
 //     movmatrix and O^T[Dh x 8 heads] += V^T * P^T follows, with V dequantised the same way (two
 //     tokens are interleaved into one half2 by a permute).
 //
-// Every wait on an mbarrier is bounded; on a timeout the warp records a status code, stops
-// waiting and finishes (with wrong numbers, flagged) instead of hanging.
+//   * The append of the decode sequences' new tokens is part of this kernel: the new token of a sequence is
+//     row kvlen-1, which lies in the LAST tile of each of its segments.  The warp that holds that tile reads
+//     the head's 2 x head_dim halves of current_key/current_value, quantises them (one group of 8 per lane),
+//     stores codes and scales to the cache row and overwrites the row in its own staged copy of the tile,
+//     which the bulk copy may have read before or while the row was being written.  A decode step therefore
+//     needs no separate append launch.
+//
+// Every wait on an mbarrier is bounded; on a timeout the warp records a status code, stops issuing copies
+// and waiting, finishes (with wrong numbers, flagged) and drains the copies it still has in flight before
+// the kernel returns, instead of hanging.
 #include <cuda.h>
 #include <stdlib.h>
 
@@ -61,6 +69,10 @@ namespace {
 #endif
 #ifndef PPLB200_DECODE_CTAS
 #define PPLB200_DECODE_CTAS 2
+#endif
+
+#ifndef PPLB200_DECODE_OVERSUB_DEFAULT
+#define PPLB200_DECODE_OVERSUB_DEFAULT 1
 #endif
 
 constexpr int kTileTok = 16;
@@ -119,6 +131,13 @@ struct DecodeArgs {
     const __half* scale;  // the scale tensor (copied with cp.async, addressed with the cache strides / 8)
     int64_t max_tokens;
     float scale_log2;
+    // Fused append (cur_k != nullptr): the warp that streams the LAST tile of a (sequence, kv head) segment
+    // quantises that head's slice of the sequence's new token, stores it to its cache row and patches its own
+    // shared-memory copy of the tile with the same codes and scales.
+    const __half* cur_k;
+    const __half* cur_v;
+    int8_t* cache;
+    int32_t num_kv_heads;
 };
 
 // Order of the four outer dimensions of the cache tensor maps (see CacheMapOrder), as a template
@@ -286,6 +305,44 @@ __device__ __forceinline__ void dequant_v_pair(uint32_t wa, uint32_t wb, __half2
     h[3] = h2_as_u32(__hmul2(biased_bytes_to_half2<0x5342u>(y), s2));
 }
 
+// The new token of decode sequence b (query row `tok`, position `pos` = kvlen - 1) for kv head `kvh`: one
+// lane per quantisation group (K groups first, then V groups) quantises 8 halves, stores codes and scale to
+// the cache row and overwrites row pos % 16 of the staged tile at `st`, whose bulk copy has completed.
+template <int DH>
+__device__ __forceinline__ void append_token_into_tile(const DecodeArgs& a, uint32_t st, int lane, int64_t tok,
+                                                       int kvh, int32_t b, int32_t pos) {
+    using T = Traits<DH>;
+    constexpr int kGroups = DH / 8;  // quantisation groups of one head row
+    if (lane < 2 * kGroups) {
+        const int kv = lane / kGroups;  // 0: key, 1: value
+        const int grp = lane - kv * kGroups;
+        const __half* src = (kv ? a.cur_v : a.cur_k) + (tok * a.num_kv_heads + kvh) * DH + grp * 8;
+        uint2 codes;
+        __half s16;
+        quant_group8(*reinterpret_cast<const uint4*>(src), codes, s16);
+        const int64_t row = cache_row(a.geom, a.cachestarts, b, pos);
+        if (row >= 0 && row < a.max_tokens) {
+            const int64_t off = cache_offset(a.geom, row, kv, kvh) + grp * 8;
+            *reinterpret_cast<uint2*>(a.cache + off) = codes;
+            const_cast<__half*>(a.scale)[off >> 3] = s16;
+        } else if (grp == 0) {
+            atomicOr(&a.hdr->status, kDevRowOutOfRange);
+        }
+        const int r = pos & (kTileTok - 1);
+        uint32_t caddr = st + kv * T::kCodeBytes + r * DH;
+        if constexpr (DH == 128) {
+            caddr += (((grp >> 1) ^ (r & 7)) << 4) + ((grp & 1) << 3);  // 16-byte chunks swizzled by the row
+        } else {
+            caddr += grp * 8;
+        }
+        asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(caddr), "r"(codes.x), "r"(codes.y) : "memory");
+        const uint32_t saddr = st + 2 * T::kCodeBytes + kv * T::kScaleBytes + r * (kGroups * 2) + grp * 2;
+        asm volatile("st.shared.u16 [%0], %1;" ::"r"(saddr), "h"(__half_as_ushort(s16)) : "memory");
+    }
+    fence_proxy_async_smem();  // the stage is refilled by a bulk copy after these generic-proxy writes
+    __syncwarp();
+}
+
 // Position in the tile sequence of one head class: sequence b, class-local head index vc (the virtual
 // head, i.e. kv head x octet of query heads, is vc * head_lanes + class), tile index within the
 // segment, tiles per segment of this sequence, first cache row of the sequence and the kv head.
@@ -351,7 +408,8 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
 
     uint32_t c_stage = 0, c_phase = 0;  // consume position in the stage ring
     uint32_t i_stage = 0;               // issue position in the stage ring
-    bool wait_dead = false;             // set after the first timed-out wait: stop waiting, just finish
+    bool wait_dead = false;             // set after the first timed-out wait: stop waiting and issuing, just finish
+    int32_t dead_inflight = 0;          // tiles issued but not yet seen complete when the warp gave up
 
     const int nvc = a.class_heads;
     const int cls = warp % a.head_lanes;             // head class of this warp
@@ -369,9 +427,14 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
     const bool lockstep = a.lockstep != 0;
     const int layer = a.layer_idx;
 
+    constexpr int32_t kBadRow = -(1 << 30);  // row_base of a sequence whose cachestarts entry is not a cache row
     auto load_seq = [&](Cursor& c) {  // per-sequence fields
         c.n = a.tile_prefix[c.b + 1] - a.tile_prefix[c.b];
-        c.row_base = paged ? 0 : static_cast<int32_t>(a.cachestarts[c.b]);
+        c.row_base = 0;
+        if (!paged) {
+            const int64_t cs = a.cachestarts[c.b];
+            c.row_base = (cs >= 0 && cs < a.max_tokens) ? static_cast<int32_t>(cs) : kBadRow;
+        }
     };
     auto set_head = [&](Cursor& c) { c.kvh = octets == 1 ? c.vc * head_lanes + cls : (c.vc * head_lanes + cls) / octets; };
     auto advance = [&](Cursor& c, int32_t by) {
@@ -443,14 +506,29 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             if (paged) {  // the page table row of the sequence gives the first cache row of every page
                 const uint32_t page = page_shift >= 0 ? static_cast<uint32_t>(tok) >> page_shift
                                                       : static_cast<uint32_t>(tok) / static_cast<uint32_t>(a.geom.page_size);
-                row = static_cast<int>(a.cachestarts[ic.b * a.geom.cachestart_stride_b + page]) +
-                      (tok - static_cast<int>(page) * a.geom.page_size);
+                row = kBadRow;
+                if (page < static_cast<uint32_t>(a.geom.cachestart_stride_b)) {
+                    const int64_t first = a.cachestarts[ic.b * a.geom.cachestart_stride_b + page];
+                    if (first >= 0 && first < a.max_tokens) {
+                        row = static_cast<int>(first) + (tok - static_cast<int>(page) * a.geom.page_size);
+                    }
+                }
+            }
+            // A tile whose first row is not a cache row (a wrong index tensor) is flagged and read as zeros:
+            // the scale copies read nothing and the bulk copies start past the last row, which zero-fills.
+            const bool row_ok = row >= 0 && row < a.max_tokens;
+            if (!row_ok) {
+                if (lane == 0) {
+                    atomicOr(&a.hdr->status, kDevRowOutOfRange);
+                }
+                row = static_cast<int>(a.max_tokens);
             }
             const uint32_t st = wsm + i_stage * T::kStageBytes;
             const uint32_t bar = wbar + i_stage * 8;
             {
                 // scales: every lane copies its half row of the K tile and of the V tile
-                const char* src = scale_layer + row * scale_row_bytes + ic.kvh * scale_head_bytes + scale_lane_off;
+                const char* src = scale_layer + (row_ok ? row : 0) * scale_row_bytes + ic.kvh * scale_head_bytes +
+                                  scale_lane_off;
                 const uint32_t nbytes = (row + (lane >> 1)) < a.max_tokens ? kScaleCopy : 0;  // rows past the cache: zeros
                 cp_async<kScaleCopy>(st + scale_dst_off, src, nbytes);
                 cp_async<kScaleCopy>(st + scale_dst_off + T::kScaleBytes, src + scale_kv_bytes, nbytes);
@@ -468,6 +546,9 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             advance(ic, 1);
             --to_issue;
         };
+        if (wait_dead) {
+            to_issue = 0;  // a warp that has given up runs through its remaining ranges without copies
+        }
         for (int i = 0; i < kStages && to_issue > 0; ++i) {
             issue_one();
         }
@@ -482,7 +563,11 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             const int kvh = cc.kvh;
             const int oct = vh - kvh * octets;
             const int64_t qtok = a.seqstarts[b];
-            int64_t kvlen64 = a.start_pos[b] + (a.seqstarts[b + 1] - qtok);
+            const int64_t seqlen = a.seqstarts[b + 1] - qtok;
+            int64_t kvlen64 = a.start_pos[b] + seqlen;
+            // the new token is appended by the piece that holds the segment's last tile (never for a clamped or
+            // empty sequence: the first is flagged by the planning kernel, the second has no token)
+            const bool append_here = a.cur_k != nullptr && t_end == cc.n && seqlen >= 1 && kvlen64 <= a.max_kvlen;
             kvlen64 = kvlen64 > a.max_kvlen ? a.max_kvlen : kvlen64;
             const int32_t kvlen = static_cast<int32_t>(kvlen64);
 
@@ -518,7 +603,11 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             for (int32_t tile = t_first; tile < t_end; ++tile) {
                 if (!wait_dead) {
                     if (!mbar_wait_bounded(reinterpret_cast<uint64_t*>(full_bar + warp * kStages + c_stage), c_phase)) {
+                        // Give up: no further copies are issued and no further waits are made; the tiles already
+                        // issued (this one included) are waited for once more, briefly, before the kernel returns.
                         wait_dead = true;
+                        dead_inflight = (to_consume - (tile - t_first)) - to_issue;
+                        to_issue = 0;
                         if (lane == 0) {
                             atomicOr(&a.hdr->status, kDevTmaTimeout);
                         }
@@ -526,6 +615,9 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 }
                 const uint32_t st = wsm + c_stage * T::kStageBytes;
                 const int nvalid = kvlen - tile * kTileTok;  // >= 16 except in the last tile of the sequence
+                if (append_here && tile == cc.n - 1) {
+                    append_token_into_tile<DH>(a, st, lane, qtok + seqlen - 1, kvh, b, kvlen - 1);
+                }
 
                 // ---------------- S^T = K * Q^T ----------------
                 float sacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -676,12 +768,14 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                     asm volatile("bar.sync %0, %1;" ::"r"(1 + sub), "r"(head_lanes * 32) : "memory");
                 }
                 __syncwarp();  // every lane has read this stage: it may be refilled
-                if (++c_stage == kStages) {
-                    c_stage = 0;
-                    c_phase ^= 1u;
-                }
-                if (to_issue > 0) {
-                    issue_one();
+                if (!wait_dead) {
+                    if (++c_stage == kStages) {
+                        c_stage = 0;
+                        c_phase ^= 1u;
+                    }
+                    if (to_issue > 0) {
+                        issue_one();
+                    }
                 }
             }
 
@@ -732,6 +826,17 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             to_consume -= t_end - t_first;
             first_piece = false;
             advance(cc, t_end - t_first);
+        }
+    }
+    if (wait_dead) {
+        // Copies that were in flight when the warp gave up may still land in this CTA's shared memory: give
+        // each of them one more bounded wait (frozen consume position onwards) before the CTA may exit.
+        for (int32_t i = 0; i < dead_inflight && i < kStages; ++i) {
+            mbar_wait_bounded(reinterpret_cast<uint64_t*>(full_bar + warp * kStages + c_stage), c_phase);
+            if (++c_stage == kStages) {
+                c_stage = 0;
+                c_phase ^= 1u;
+            }
         }
     }
 }
@@ -786,6 +891,8 @@ decode_reduce_kernel(const PlanHeader* __restrict__ hdr, const int32_t* __restri
     for (int off = 16; off > 0; off >>= 1) {
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     }
+    // Up to 32 pieces at a time: lane i works out the weight and the slot of piece i, then the warp walks
+    // the pieces four at a time so that the loads of four partial rows are in flight together.
     constexpr int kPer = DH / 32;
     float acc[kPer];
 #pragma unroll
@@ -793,21 +900,60 @@ decode_reduce_kernel(const PlanHeader* __restrict__ hdr, const int32_t* __restri
         acc[i] = 0.0f;
     }
     float den = 0.0f;
-    for (int64_t rr = r_first; rr <= r_last; ++rr) {
-        const int64_t sl = slot_of(rr);
-        const float w = ex2_approx(part_ml[sl * 2] - mx);
-        den += w * part_ml[sl * 2 + 1];
-        const float* po = part_o + sl * DH + lane * kPer;
-#pragma unroll
-        for (int i = 0; i < kPer; ++i) {
-            acc[i] += w * po[i];
+    for (int64_t base = r_first; base <= r_last; base += 32) {
+        const int64_t rr = base + lane;
+        const bool valid = rr <= r_last;
+        const int64_t my_slot = valid ? slot_of(rr) : 0;
+        float w = 0.0f;
+        if (valid) {
+            const float2 ml = *reinterpret_cast<const float2*>(part_ml + my_slot * 2);
+            w = ex2_approx(ml.x - mx);
+            den += w * ml.y;
         }
+        const int cnt = static_cast<int>(r_last - base + 1 < 32 ? r_last - base + 1 : 32);
+        for (int j = 0; j < cnt; j += 4) {
+            float wj[4];
+            float v[4][kPer];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                // lanes past `cnt` hold weight 0 and slot 0 (a valid address whenever any partial exists)
+                wj[u] = __shfl_sync(0xffffffffu, w, (j + u) & 31);
+                const int64_t sl = __shfl_sync(0xffffffffu, my_slot, (j + u) & 31);
+                const float* po = part_o + sl * DH + lane * kPer;
+                if (j + u >= cnt) {
+                    wj[u] = 0.0f;
+                    po = part_o + lane * kPer;
+                }
+                if constexpr (kPer == 4) {
+                    const float4 t4 = *reinterpret_cast<const float4*>(po);
+                    v[u][0] = t4.x; v[u][1] = t4.y; v[u][2] = t4.z; v[u][3] = t4.w;
+                } else {
+                    const float2 t2 = *reinterpret_cast<const float2*>(po);
+                    v[u][0] = t2.x; v[u][1] = t2.y;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                for (int i = 0; i < kPer; ++i) {
+                    acc[i] += wj[u] * v[u][i];
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        den += __shfl_xor_sync(0xffffffffu, den, off);
     }
     const float inv = den > 0.0f ? 1.0f / den : 0.0f;
     __half* dst = out + (seqstarts[b] * num_heads + qh) * DH + lane * kPer;
-#pragma unroll
-    for (int i = 0; i < kPer; ++i) {
-        dst[i] = __float2half_rn(acc[i] * inv);
+    if constexpr (kPer == 4) {
+        uint2 o2;
+        o2.x = h2_as_u32(__floats2half2_rn(acc[0] * inv, acc[1] * inv));
+        o2.y = h2_as_u32(__floats2half2_rn(acc[2] * inv, acc[3] * inv));
+        *reinterpret_cast<uint2*>(dst) = o2;
+    } else {
+        *reinterpret_cast<__half2*>(dst) = __floats2half2_rn(acc[0] * inv, acc[1] * inv);
     }
 }
 
@@ -820,6 +966,7 @@ uint64_t align_up_u64(uint64_t x, uint64_t a) {
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
+int decode_oversubscription();
 int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* plan) {
     DecodePlan& d = *plan;
     const int64_t DB = p.decoding_batches;
@@ -835,7 +982,9 @@ int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* pla
     }
     d.class_heads = d.num_vheads / d.head_lanes;
     d.grid = static_cast<int64_t>(sm_count) * kCtasPerSm;
-    d.workers = d.grid * (kWarps / d.head_lanes);  // resident warps per head class
+    // Ranges per resident warp of a class.  More than one trades extra split partials for a shorter tail
+    // (ranges are handed out dynamically, so warps that fall behind take fewer of them).
+    d.workers = d.grid * (kWarps / d.head_lanes) * decode_oversubscription();
     // upper bound of the number of ranges (per class) the planning kernel may create
     if (p.split_k_mode == 0 || DB == 0) {
         d.max_ranges = DB * d.class_heads;
@@ -858,6 +1007,12 @@ int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* pla
     off = align_up_u64(off + static_cast<uint64_t>(d.partial_slots) * 8 * p.head_dim * 4, 256);
     d.bytes = off;
     return PPLB200_SUCCESS;
+}
+
+int decode_oversubscription() {
+    const char* e = getenv("PPLB200_DECODE_OVERSUB");  // tuning only; read per call so that a sweep can change it
+    const int n = e ? atoi(e) : 0;
+    return (n >= 1 && n <= 16) ? n : PPLB200_DECODE_OVERSUB_DEFAULT;
 }
 
 static int map_order_kind(const CacheMapOrder& od) {
@@ -919,9 +1074,9 @@ static bool want_lockstep(const pplb200_attn_params& p, const DecodePlan& plan) 
 
 template <int DH>
 static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan,
-                            const void* query, const int64_t* seqstarts, const int64_t* cachestarts,
-                            const int64_t* start_pos, const void* cache, const void* scale, void* workspace,
-                            void* attn_output, cudaStream_t stream) {
+                            const void* query, const void* append_key, const void* append_value,
+                            const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos,
+                            void* cache, void* scale, void* workspace, void* attn_output, cudaStream_t stream) {
     static_assert(sizeof(PlanHeader) <= 256, "the header must fit in front of the prefix sums");
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     PlanHeader* hdr = reinterpret_cast<PlanHeader*>(ws + plan.off_header);
@@ -967,6 +1122,10 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.scale = static_cast<const __half*>(scale);
     a.max_tokens = p.max_tokens;
     a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
+    a.cur_k = static_cast<const __half*>(append_key);
+    a.cur_v = static_cast<const __half*>(append_value);
+    a.cache = static_cast<int8_t*>(cache);
+    a.num_kv_heads = p.num_kv_heads;
 
     // never more CTAs than there can be ranges
     int64_t grid = plan.grid;
@@ -995,18 +1154,22 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
 }
 
 int launch_decode(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan, const void* query,
-                  const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos, const void* cache,
-                  const void* scale, void* workspace, void* attn_output, cudaStream_t stream) {
+                  const void* append_key, const void* append_value, const int64_t* seqstarts,
+                  const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale, void* workspace,
+                  void* attn_output, cudaStream_t stream) {
     if (p.decoding_batches <= 0) {
         return PPLB200_SUCCESS;
     }
+    if ((append_key == nullptr) != (append_value == nullptr)) {
+        return PPLB200_INVALID_VALUE;
+    }
     if (p.head_dim == 128) {
-        return launch_decode_dh<128>(p, geom, plan, query, seqstarts, cachestarts, start_pos, cache, scale, workspace,
-                                     attn_output, stream);
+        return launch_decode_dh<128>(p, geom, plan, query, append_key, append_value, seqstarts, cachestarts, start_pos,
+                                     cache, scale, workspace, attn_output, stream);
     }
     if (p.head_dim == 64) {
-        return launch_decode_dh<64>(p, geom, plan, query, seqstarts, cachestarts, start_pos, cache, scale, workspace,
-                                    attn_output, stream);
+        return launch_decode_dh<64>(p, geom, plan, query, append_key, append_value, seqstarts, cachestarts, start_pos,
+                                    cache, scale, workspace, attn_output, stream);
     }
     return PPLB200_UNSUPPORTED;
 }

@@ -14,9 +14,16 @@ __global__ void __launch_bounds__(256)
 kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict__ cur_v,
                       const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ cachestarts,
                       const int64_t* __restrict__ start_pos, int8_t* __restrict__ cache, __half* __restrict__ scale,
-                      CacheGeom geom, int32_t batch, int64_t total_tokens, int num_kv_heads, int head_dim) {
+                      CacheGeom geom, int32_t batch, int32_t first_seq, int64_t total_tokens, int64_t max_tokens,
+                      uint32_t* __restrict__ status, int num_kv_heads, int head_dim) {
     grid_launch_dependents();
     grid_dependency_wait();
+    // tokens of the sequences before first_seq are not this launch's business (the decode kernel appends the
+    // new tokens of the decode sequences itself)
+    const int64_t tok_begin = first_seq > 0 ? seqstarts[first_seq] : 0;
+    total_tokens -= tok_begin;
+    cur_k += tok_begin * num_kv_heads * head_dim;
+    cur_v += tok_begin * num_kv_heads * head_dim;
     const int lane = threadIdx.x & 31;
     const int group_shift = head_dim == 128 ? 4 : 3;
     const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
@@ -39,8 +46,15 @@ kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict
                 in[c] = *reinterpret_cast<const uint4*>((is_v ? v_tok : k_tok) + r2 * 8);
             }
         }
-        const int32_t b = warp_find_segment(seqstarts, batch, it.tok, lane);
-        const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (it.tok - seqstarts[b]));
+        const int64_t tok = it.tok + tok_begin;
+        const int32_t b = warp_find_segment(seqstarts, batch, tok, lane);
+        const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (tok - seqstarts[b]));
+        if (!cache_row_ok(row, max_tokens)) {  // a wrong index tensor: flag it and leave the cache alone
+            if (lane == 0 && status != nullptr) {
+                atomicOr(status, kDevRowOutOfRange);
+            }
+            continue;
+        }
         const int64_t row_off = row * geom.stride_s + geom.layer_idx * geom.stride_l;
         int8_t* c_row = cache + row_off;
         __half* s_row = scale + (row_off >> 3);
@@ -65,7 +79,7 @@ __global__ void __launch_bounds__(256)
 kv_gather_dequant_kernel(const int64_t* __restrict__ kvstarts, const int64_t* __restrict__ cachestarts,
                          const int8_t* __restrict__ cache, const __half* __restrict__ scale,
                          __half* __restrict__ key_out, __half* __restrict__ value_out, CacheGeom geom, int32_t batch,
-                         int64_t total_kv, int num_kv_heads, int head_dim) {
+                         int64_t total_kv, int64_t max_tokens, int num_kv_heads, int head_dim) {
     const int lane = threadIdx.x & 31;
     const int group_shift = head_dim == 128 ? 4 : 3;
     const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
@@ -74,6 +88,7 @@ kv_gather_dequant_kernel(const int64_t* __restrict__ kvstarts, const int64_t* __
         const int64_t j = it.tok;
         const int32_t b = warp_find_segment(kvstarts, batch, j, lane);
         const int64_t row = cache_row(geom, cachestarts, b, j - kvstarts[b]);
+        const bool row_ok = cache_row_ok(row, max_tokens);  // a row outside the cache reads as zeros
         uint2 codes[kChunks];
         uint16_t sbits[kChunks];
 #pragma unroll
@@ -81,7 +96,7 @@ kv_gather_dequant_kernel(const int64_t* __restrict__ kvstarts, const int64_t* __
             const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
             codes[c] = make_uint2(0u, 0u);
             sbits[c] = 0;
-            if (g < groups_per_token) {
+            if (g < groups_per_token && row_ok) {
                 int kv, head, grp;
                 split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
                 const int64_t off = cache_offset(geom, row, kv, head);
@@ -124,17 +139,19 @@ static int grid_for(int64_t work_items, int threads, int sm_count) {
 
 int launch_kv_append(const pplb200_attn_params& p, const CacheGeom& geom, const void* cur_k, const void* cur_v,
                      const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos, void* cache,
-                     void* scale, int sm_count, cudaStream_t stream) {
-    if (p.total_tokens <= 0) {
+                     void* scale, int64_t first_seq, uint32_t* status, int sm_count, cudaStream_t stream) {
+    // sequences before first_seq are decode sequences with one token each, so this many tokens remain
+    const int64_t tokens = p.total_tokens - first_seq;
+    if (tokens <= 0 || first_seq >= p.batch) {
         return PPLB200_SUCCESS;
     }
     const int64_t items_per_token = (2 * p.num_kv_heads * (p.head_dim / 8) + 32 * kChunks - 1) / (32 * kChunks);
-    const int grid = grid_for(p.total_tokens * items_per_token * 32, 256, sm_count);  // a warp per item
+    const int grid = grid_for(tokens * items_per_token * 32, 256, sm_count);  // a warp per item
     KernelTimer timer(PPLB200_KERNEL_APPEND, stream);
     launch_dependent(kv_append_i8g8_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const __half*>(cur_k),
                      static_cast<const __half*>(cur_v), seqstarts, cachestarts, start_pos, static_cast<int8_t*>(cache),
-                     static_cast<__half*>(scale), geom, static_cast<int32_t>(p.batch), p.total_tokens, p.num_kv_heads,
-                     p.head_dim);
+                     static_cast<__half*>(scale), geom, static_cast<int32_t>(p.batch), static_cast<int32_t>(first_seq),
+                     p.total_tokens, p.max_tokens, status, p.num_kv_heads, p.head_dim);
     return check_launch("kv_append_i8g8_kernel");
 }
 
@@ -149,8 +166,7 @@ int launch_kv_gather_dequant(const pplb200_attn_params& p, const CacheGeom& geom
     kv_gather_dequant_kernel<<<grid, 256, 0, stream>>>(
         kvstarts, cachestarts, static_cast<const int8_t*>(cache), static_cast<const __half*>(scale),
         static_cast<__half*>(key_out), static_cast<__half*>(value_out), geom, static_cast<int32_t>(p.batch), total_kv,
-        p.num_kv_heads,
-        p.head_dim);
+        p.max_tokens, p.num_kv_heads, p.head_dim);
     return check_launch("kv_gather_dequant_kernel");
 }
 

@@ -63,9 +63,11 @@ struct DeviceInfo {
 };
 int current_device_info(DeviceInfo* info);
 
+// Appends the tokens of sequences [first_seq, batch) (all of them with first_seq 0).  `status` (nullable)
+// receives kDevRowOutOfRange when an index tensor names a row outside the cache; such rows are skipped.
 int launch_kv_append(const pplb200_attn_params& p, const CacheGeom& geom, const void* cur_k, const void* cur_v,
                      const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos, void* cache,
-                     void* scale, int sm_count, cudaStream_t stream);
+                     void* scale, int64_t first_seq, uint32_t* status, int sm_count, cudaStream_t stream);
 
 int launch_kv_gather_dequant(const pplb200_attn_params& p, const CacheGeom& geom, const int64_t* kvstarts,
                              const int64_t* cachestarts, const void* cache, const void* scale, int64_t total_kv,
@@ -88,9 +90,13 @@ struct DecodePlan {
 };
 int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* plan);
 
+// `append_key` / `append_value` non-null: the decode kernel also quantises and appends the new token of
+// every decode sequence (query row seqstarts[b+1]-1, position start_pos[b]+seqlen-1) and attends to it;
+// null: the cache already holds that token.
 int launch_decode(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan, const void* query,
-                  const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos, const void* cache,
-                  const void* scale, void* workspace, void* attn_output, cudaStream_t stream);
+                  const void* append_key, const void* append_value, const int64_t* seqstarts,
+                  const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale, void* workspace,
+                  void* attn_output, cudaStream_t stream);
 
 // ---- prefill (causal, tcgen05) -------------------------------------------------------------------
 struct PrefillPlan {

@@ -290,15 +290,21 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // a phase that has completed already, costs one test; the polling loop is kept out of line.
 __device__ __noinline__ bool wait_or_abort_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                 uint32_t* status, uint32_t code) {
-    for (uint32_t i = 0; i < kMaxWaitPolls; i += 4) {
+    const long long t0 = clock64();
+    for (uint32_t i = 0;; i += 4) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             if (PPLB200_PREFILL_WAIT(bar, parity)) {
                 return true;
             }
         }
-        if ((i & 255u) == 252u && *abort_flag) {
-            return false;
+        if ((i & 255u) == 252u) {
+            if (*abort_flag) {
+                return false;
+            }
+            if (clock64() - t0 > kWaitBudgetCycles) {
+                break;
+            }
         }
     }
     *abort_flag = 1;
@@ -877,8 +883,8 @@ prefill_stage_dequant_kernel(const int64_t* __restrict__ seqstarts, const int64_
                              const int64_t* __restrict__ cachestarts, const int64_t* __restrict__ stage_starts,
                              const int8_t* __restrict__ cache, const __half* __restrict__ scale,
                              __half* __restrict__ k_stage, __half* __restrict__ v_stage, CacheGeom geom,
-                             int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen, int num_kv_heads,
-                             int head_dim) {
+                             int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen, int64_t max_tokens,
+                             uint32_t* __restrict__ status, int num_kv_heads, int head_dim) {
     const int groups_per_head = head_dim >> 3;
     const int64_t groups_per_tensor_row = static_cast<int64_t>(num_kv_heads) * groups_per_head;
     const int64_t groups_per_token = 2 * groups_per_tensor_row;
@@ -907,8 +913,12 @@ prefill_stage_dequant_kernel(const int64_t* __restrict__ seqstarts, const int64_
         int64_t kvlen = start_pos[b] + (seqstarts[b + 1] - seqstarts[b]);
         kvlen = kvlen > max_kvlen ? max_kvlen : kvlen;
         uint4 out = make_uint4(0u, 0u, 0u, 0u);
-        if (pos < kvlen) {
-            const int64_t crow = cache_row(geom, cachestarts, b, pos);
+        const int64_t crow = pos < kvlen ? cache_row(geom, cachestarts, b, pos) : 0;
+        if (pos < kvlen && !cache_row_ok(crow, max_tokens)) {  // a wrong index tensor: flagged, read as zeros
+            if (grp == 0) {
+                atomicOr(status, kDevRowOutOfRange);
+            }
+        } else if (pos < kvlen) {
             const int64_t off = cache_offset(geom, crow, kv, head);
             const uint2 codes = *reinterpret_cast<const uint2*>(cache + off + grp * 8);
             const float s = __half2float(scale[(off >> 3) + grp]);
@@ -1058,7 +1068,7 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
         prefill_stage_dequant_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
             seqstarts, start_pos, cachestarts, ss, static_cast<const int8_t*>(cache), static_cast<const __half*>(scale),
             ks, vs, geom, static_cast<int32_t>(p.decoding_batches), static_cast<int32_t>(plan.prefill_batches),
-            p.max_kvlen, p.num_kv_heads, p.head_dim);
+            p.max_kvlen, p.max_tokens, status, p.num_kv_heads, p.head_dim);
         rc = check_launch("prefill_stage_dequant_kernel");
         if (rc != PPLB200_SUCCESS) {
             return rc;

@@ -109,6 +109,7 @@ struct RopeArgs {
     RopeDev rope;
     int32_t batch;
     int64_t total_tokens;
+    int64_t max_tokens;          // fused only: rows of the cache
     int32_t num_heads;
     int32_t num_kv_heads;
     int32_t head_dim;
@@ -155,8 +156,10 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
         }
         const float* inv_freq = a.rope.table + (a.rope.table_per_seq ? static_cast<int64_t>(b) * a.rope.half_rot : 0);
         int64_t row = 0;
+        bool row_ok = false;  // a row outside the cache (a wrong index tensor) is not written
         if (FUSED) {
             row = cache_row(a.geom, a.cachestarts, b, pos);
+            row_ok = cache_row_ok(row, a.max_tokens);
         }
         LaneRotation rotn;
         rotn.init(grp, pos_eff, inv_freq, a.rope.half_rot);
@@ -182,7 +185,7 @@ __global__ void __launch_bounds__(256) rope_kernel(const RopeArgs a) {
                     *reinterpret_cast<uint4*>(a.rotated_key + (it.tok * k_groups + gk) * 8) = r;
                 }
             }
-            if (FUSED) {
+            if (FUSED && row_ok) {
                 uint2 codes;
                 __half s16;
                 quant_group8(r, codes, s16);
@@ -253,6 +256,7 @@ int launch_rope(const pplb200_rope_params& p, const pplb200_attn_params* append,
     a.num_kv_heads = p.num_kv_heads;
     a.head_dim = p.head_dim;
     a.bypass_key = p.bypass_key;
+    a.max_tokens = append ? append->max_tokens : 0;
     const int32_t groups = (p.num_heads + p.num_kv_heads * (append ? 2 : 1)) * (p.head_dim / 8);
     const int grid = grid_for_items(p.total_tokens, groups, sm_count);
     KernelTimer timer(PPLB200_KERNEL_APPEND, stream);

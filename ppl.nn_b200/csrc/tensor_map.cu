@@ -72,8 +72,13 @@ int make_cache_tensor_map(const pplb200_attn_params& p, const void* cache, int t
     const uint64_t stride[4] = {static_cast<uint64_t>(p.cache_stride_s), static_cast<uint64_t>(p.cache_stride_h),
                                 static_cast<uint64_t>(p.cache_stride_kv), static_cast<uint64_t>(p.cache_stride_l)};
     int idx[4] = {0, 1, 2, 3};
-    for (int i = 1; i < 4; ++i) {  // insertion sort by stride, stable
-        for (int j = i; j > 0 && stride[idx[j]] < stride[idx[j - 1]]; --j) {
+    // Insertion sort by stride; among equal strides the row dimension goes last, so that a one-layer
+    // token-major cache (row and layer strides tie) gets the same order as a multi-layer one.
+    auto before = [&](int x, int y) {
+        return stride[x] < stride[y] || (stride[x] == stride[y] && y == 0 && x != 0);
+    };
+    for (int i = 1; i < 4; ++i) {
+        for (int j = i; j > 0 && before(idx[j], idx[j - 1]); --j) {
             const int tmp = idx[j];
             idx[j] = idx[j - 1];
             idx[j - 1] = tmp;

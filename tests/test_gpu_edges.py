@@ -1,5 +1,6 @@
 """Edge cases of the ragged batch on the GPU, against the oracle: empty sequences inside a batch, an empty
-batch, a single one-token sequence, and lengths beyond the max_seqlen / max_kvlen the caller announced."""
+batch, a single one-token sequence, lengths beyond the max_seqlen / max_kvlen the caller announced, and index
+tensors that name rows outside the cache (skipped and reported, never dereferenced)."""
 import numpy as np
 import pytest
 
@@ -69,6 +70,81 @@ def test_lengths_beyond_the_announced_maximum_are_clamped_and_reported(orc, torc
     out = op.forward(*args, 64, idx.max_kvlen, cache, scale)        # max_seqlen too small for the prefill sequence
     assert op.device_status() & 4
     assert bool(torch.isfinite(out[:idx.seqstarts[2] + 64].float()).all())
+
+
+def test_rows_outside_the_cache_are_skipped_and_reported(orc, torch_dev, pkg, built_lib):
+    """cachestarts / start_pos come from the caller.  A row they name outside [0, max_tokens) is neither read
+    nor written; the status word carries PPLB200_DEV_ROW_OUT_OF_RANGE (8); the other sequences are served as
+    usual.  Every access in these cases is guarded, so nothing can fault."""
+    import torch
+    from ppl_nn_b200 import ops, workloads
+    dev = torch_dev
+    Hq, Hkv, Dh = 8, 2, 128
+    spec = _spec(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, n_decode=3, kv_dist="list", kv_list=(40, 100, 70),
+                 n_prefill=1, seed=45)
+    idx = workloads.make_index([40, 100, 70], [50])
+    hc = _case_with_index(workloads.host_case(spec), idx, spec)
+    err, op = run_case(orc, dev, hc)  # the honest call: clean status, parity
+    assert op.device_status() == 0
+
+    def history():
+        cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, Hkv, Dh)
+        cache = torch.zeros(cshape, dtype=torch.int8, device=dev)
+        scale = torch.zeros(sshape, dtype=torch.float16, device=dev)
+        hidx = hc.hist_index
+        ops.KeyValueCache(ops.KeyValueCacheParam(num_layer=1, layer_idx=0, quant_bit=8)).forward(
+            _t(hc.hist_key, dev), _t(hc.hist_value, dev), _t(hidx.seqstarts, dev), _t(hidx.kvstarts, dev),
+            _t(hidx.cachestarts, dev), _t(hidx.start_pos, dev), hidx.max_seqlen, hidx.max_kvlen, cache, scale,
+            total_kv=0)
+        return cache, scale
+
+    def call(cachestarts, cache, scale):
+        return op.forward(_t(hc.query, dev), _t(hc.current_key, dev), _t(hc.current_value, dev),
+                          _t(idx.seqstarts, dev), _t(idx.kvstarts, dev), _t(cachestarts, dev), _t(idx.start_pos, dev),
+                          idx.decoding_batches, idx.max_seqlen, idx.max_kvlen, cache, scale)
+
+    before, _ = history()
+    good_cache, good_scale = history()
+    good = call(idx.cachestarts, good_cache, good_scale).clone()
+    assert op.device_status() == 0
+    for victim, what in ((1, "beyond"), (1, "negative"), (3, "beyond")):
+        cache, scale = history()
+        cs = idx.cachestarts.copy()
+        cs[victim] = idx.max_tokens + 5 if what == "beyond" else -7
+        out = call(cs, cache, scale)
+        assert op.device_status() & 8, (victim, what)
+        assert bool(torch.isfinite(out.float()).all())
+        # the sequences with honest indices are served as usual, bit for bit
+        for b in range(idx.batch):
+            if b != victim:
+                lo, hi = int(idx.seqstarts[b]), int(idx.seqstarts[b + 1])
+                assert bool((out[lo:hi].view(torch.int16) == good[lo:hi].view(torch.int16)).all()), (victim, what, b)
+        # and the victim's new tokens were not written anywhere: its own rows still hold what they held
+        expect = good_cache.clone()
+        lo = int(idx.cachestarts[victim] + idx.start_pos[victim])
+        hi = lo + int(idx.seqlens[victim])
+        expect[lo:hi] = before[lo:hi]
+        assert bool((cache == expect).all()), (victim, what)
+
+    # paged mode: a page table too short for the announced max_kvlen is refused on the host
+    pop = ops.MultiHeadCacheAttention(ops.MultiHeadCacheAttentionParam(
+        num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, num_layer=1, layer_idx=0, quant_bit=8, cache_mode=1, page_size=16))
+    pidx = workloads.make_index([40, 100, 70], [50], page_size=16)
+    cshape, sshape = workloads.cache_shapes(0, pidx.max_tokens, 1, Hkv, Dh)
+    pc, ps = torch.zeros(cshape, dtype=torch.int8, device=dev), torch.zeros(sshape, dtype=torch.float16, device=dev)
+    pargs = (_t(hc.query, dev), _t(hc.current_key, dev), _t(hc.current_value, dev), _t(pidx.seqstarts, dev),
+             _t(pidx.kvstarts, dev))
+    with pytest.raises(ops.OpError) as ei:
+        pop.forward(*pargs, _t(pidx.cachestarts[:, :3], dev), _t(pidx.start_pos, dev), pidx.decoding_batches,
+                    pidx.max_seqlen, pidx.max_kvlen, pc, ps)
+    assert ei.value.name == "RC_INVALID_VALUE"
+    # ... and a page entry that is not a cache row is skipped and reported on the device
+    table = pidx.cachestarts.copy()
+    table[1, 2] = -16
+    out = pop.forward(*pargs, _t(table, dev), _t(pidx.start_pos, dev), pidx.decoding_batches, pidx.max_seqlen,
+                      pidx.max_kvlen, pc, ps)
+    assert pop.device_status() & 8
+    assert bool(torch.isfinite(out.float()).all())
 
 
 def test_second_device_in_the_same_process(orc, torch_dev, pkg):
