@@ -3,6 +3,7 @@
 // stream) and pplb200_profile_read (waits for the recorded events).
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <initializer_list>
@@ -329,9 +330,6 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     if (rc != PPLB200_SUCCESS) {
         return rc;
     }
-    if (p->is_causal == 0 && p->decoding_batches < p->batch) {
-        return fail(PPLB200_UNSUPPORTED, "prefill sequences need is_causal == 1");
-    }
     if (!scale) {
         return fail(PPLB200_UNSUPPORTED, "only a quantised cache is supported but scale is null");
     }
@@ -379,10 +377,19 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     const bool do_append = (mask & PPLB200_PHASE_APPEND) != 0;
     const bool do_decode = (mask & PPLB200_PHASE_DECODE) != 0 && p->decoding_batches > 0;
     const bool do_prefill = (mask & PPLB200_PHASE_PREFILL) != 0 && p->decoding_batches < p->batch;
+    // PPLB200_FUSE_APPEND=0 (measurement only): the append kernel handles every token ahead of the decode part
+    const char* fuse_env = getenv("PPLB200_FUSE_APPEND");
+    const bool fuse = do_append && do_decode && !(fuse_env && fuse_env[0] == '0');
+    if (do_append && do_decode && !fuse) {
+        rc = launch_kv_append(*p, geom, current_key, current_value, seqstarts, cachestarts, start_pos, cache, scale, 0,
+                              nullptr, di.sm_count, stream);
+        if (rc != PPLB200_SUCCESS) {
+            return rc;
+        }
+    }
     if (do_decode) {
-        rc = launch_decode(*p, geom, w.decode, query, do_append ? current_key : nullptr,
-                           do_append ? current_value : nullptr, seqstarts, cachestarts, start_pos, cache, scale,
-                           workspace, attn_output, stream);
+        rc = launch_decode(*p, geom, w.decode, query, fuse ? current_key : nullptr, fuse ? current_value : nullptr,
+                           seqstarts, cachestarts, start_pos, cache, scale, workspace, attn_output, stream);
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
@@ -390,9 +397,9 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
         (void)cudaGetLastError();
         return fail(PPLB200_DEVICE_RUNTIME_ERROR, "cudaMemsetAsync(status) failed");
     }
-    if (do_append) {
+    if (do_append && (fuse || !do_decode)) {
         rc = launch_kv_append(*p, geom, current_key, current_value, seqstarts, cachestarts, start_pos, cache, scale,
-                              do_decode ? p->decoding_batches : 0, status, di.sm_count, stream);
+                              fuse ? p->decoding_batches : 0, status, di.sm_count, stream);
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }

@@ -916,20 +916,23 @@ decode_reduce_kernel(const PlanHeader* __restrict__ hdr, const int32_t* __restri
             float v[4][kPer];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                // lanes past `cnt` hold weight 0 and slot 0 (a valid address whenever any partial exists)
                 wj[u] = __shfl_sync(0xffffffffu, w, (j + u) & 31);
                 const int64_t sl = __shfl_sync(0xffffffffu, my_slot, (j + u) & 31);
                 const float* po = part_o + sl * DH + lane * kPer;
-                if (j + u >= cnt) {
-                    wj[u] = 0.0f;
-                    po = part_o + lane * kPer;
+#pragma unroll
+                for (int i = 0; i < kPer; ++i) {
+                    v[u][i] = 0.0f;
                 }
-                if constexpr (kPer == 4) {
-                    const float4 t4 = *reinterpret_cast<const float4*>(po);
-                    v[u][0] = t4.x; v[u][1] = t4.y; v[u][2] = t4.z; v[u][3] = t4.w;
+                if (j + u < cnt) {  // nothing is read past the last piece: unwritten slots may hold anything
+                    if constexpr (kPer == 4) {
+                        const float4 t4 = *reinterpret_cast<const float4*>(po);
+                        v[u][0] = t4.x; v[u][1] = t4.y; v[u][2] = t4.z; v[u][3] = t4.w;
+                    } else {
+                        const float2 t2 = *reinterpret_cast<const float2*>(po);
+                        v[u][0] = t2.x; v[u][1] = t2.y;
+                    }
                 } else {
-                    const float2 t2 = *reinterpret_cast<const float2*>(po);
-                    v[u][0] = t2.x; v[u][1] = t2.y;
+                    wj[u] = 0.0f;
                 }
             }
 #pragma unroll

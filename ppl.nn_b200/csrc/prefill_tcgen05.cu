@@ -1091,7 +1091,7 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
     a.decoding_batches = static_cast<int32_t>(p.decoding_batches);
     a.prefill_batches = static_cast<int32_t>(plan.prefill_batches);
     a.kv_mode = p.enable_cache_prefill ? 1 : 0;
-    a.is_causal = 1;
+    a.is_causal = p.is_causal ? 1 : 0;  // the attribute is passed through, as the reference passes it
     return launch_attention_core<DH>(query, k_src, v_src, p.total_tokens, kv_rows, p.num_heads, p.num_kv_heads,
                                      plan.q_tiles_per_seq, a, stream);
 }

@@ -250,13 +250,38 @@ class DeviceCase:
     scale: "object"
 
 
-def _torch_kv(gen, rows, heads, dim, spec: Spec, is_key: bool, device):
+class _HeadStreams:
+    """One random stream per GLOBAL kv head (plus one for the token-level draws), so that the values of a
+    head do not depend on how many ranks the heads are sharded over: rank r of N holds exactly the numbers
+    that heads [r * Hkv / N, (r + 1) * Hkv / N) hold in the unsharded workload."""
+
+    def __init__(self, spec: Spec, device, first_head: int, heads: int):
+        import torch
+        self.heads = []
+        for h in range(first_head, first_head + heads):
+            g = torch.Generator(device=device)
+            g.manual_seed(spec.seed * 7919 + 1000 + h)
+            self.heads.append(g)
+        self.tokens = torch.Generator(device=device)
+        self.tokens.manual_seed(spec.seed * 7919 + 999)
+
+    def normal(self, rows, per_head, dim, device):
+        """[rows, len(heads) * per_head, dim] fp32: `per_head` heads' worth of N(0,1) from every stream."""
+        import torch
+        out = torch.empty((rows, len(self.heads) * per_head, dim), device=device, dtype=torch.float32)
+        for i, g in enumerate(self.heads):
+            out[:, i * per_head:(i + 1) * per_head] = torch.randn((rows, per_head, dim), generator=g, device=device,
+                                                                  dtype=torch.float32)
+        return out
+
+
+def _torch_kv(streams: _HeadStreams, rows, dim, spec: Spec, is_key: bool, device):
     import torch
-    x = torch.randn((rows, heads, dim), generator=gen, device=device, dtype=torch.float32)
+    x = streams.normal(rows, 1, dim, device)
     if is_key and spec.outlier_k:
         x[:, :, ::16] *= 8.0
     if is_key and spec.peaked and rows > 0:
-        hot = torch.rand((rows,), generator=gen, device=device) < 0.01
+        hot = torch.rand((rows,), generator=streams.tokens, device=device) < 0.01
         x[hot] += 6.0
     return x.to(torch.float16)
 
@@ -271,8 +296,7 @@ def device_case(spec: Spec, device, rank: int = 0, world: int = 1, layout: int =
         raise ValueError("head counts must divide by the number of ranks")
     hkv, hq, dh = spec.num_kv_heads // world, spec.num_heads // world, spec.head_dim
     idx = index_for(spec, page_size=page_size)
-    gen = torch.Generator(device=device)
-    gen.manual_seed(spec.seed * 7919 + 1000 + rank)
+    gen = _HeadStreams(spec, device, rank * hkv, hkv)
     cshape, sshape = cache_shapes(layout, idx.max_tokens, num_layer, hkv, dh)
     cache = torch.zeros(cshape, dtype=torch.int8, device=device)
     scale = torch.zeros(sshape, dtype=torch.float16, device=device)
@@ -313,9 +337,9 @@ def device_case(spec: Spec, device, rank: int = 0, world: int = 1, layout: int =
             _append_slab(lib, kvc, spec, gen, device, hkv, dh, idx, cachestarts, cache, scale, seqs, lens,
                          [0] * len(seqs), page_size)
     T = idx.total_tokens
-    q = torch.randn((T, hq, dh), generator=gen, device=device, dtype=torch.float32).to(torch.float16)
-    ck = _torch_kv(gen, T, hkv, dh, spec, True, device)
-    cv = _torch_kv(gen, T, hkv, dh, spec, False, device)
+    q = gen.normal(T, hq // hkv, dh, device).to(torch.float16)
+    ck = _torch_kv(gen, T, dh, spec, True, device)
+    cv = _torch_kv(gen, T, dh, spec, False, device)
     torch.cuda.synchronize(device)
     return DeviceCase(spec=spec, index=idx, num_heads=hq, num_kv_heads=hkv, layout=layout, num_layer=num_layer,
                       layer_idx=layer_idx, query=q, current_key=ck, current_value=cv, seqstarts=dev(idx.seqstarts),
@@ -329,8 +353,8 @@ def _append_slab(lib, kvc, spec, gen, device, hkv, dh, idx, cachestarts_all, cac
     from . import capi
 
     rows = int(sum(lens))
-    hk = _torch_kv(gen, rows, hkv, dh, spec, True, device)
-    hv = _torch_kv(gen, rows, hkv, dh, spec, False, device)
+    hk = _torch_kv(gen, rows, dh, spec, True, device)
+    hv = _torch_kv(gen, rows, dh, spec, False, device)
     seqstarts = torch.tensor(np.concatenate([[0], np.cumsum(lens)]), dtype=torch.int64, device=device)
     start_pos = torch.tensor(offsets, dtype=torch.int64, device=device)
     sel = torch.tensor(seqs, dtype=torch.int64, device=device)

@@ -145,8 +145,9 @@ def test_cache_offsets_beyond_4_gib(orc, dev, pkg, layout):
 
 
 def test_long_context_full_size(orc, dev, pkg):
-    """16 sequences of 32k..128k cached tokens with peaked softmax: the shortest one against the oracle,
-    all of them for split-k invariance, and the appended token of every sequence bit-exact."""
+    """16 sequences of 32k..128k cached tokens with peaked softmax: the shortest and the LONGEST one (where
+    split-k merges the most partials) against the oracle, all of them for split-k invariance, and the appended
+    token of every sequence bit-exact."""
     import torch
     from ppl_nn_b200 import workloads
     spec = workloads.SPECS["cfg5_longctx"]
@@ -154,8 +155,8 @@ def test_long_context_full_size(orc, dev, pkg):
     op = _op(dc, spec)
     out = _forward(op, dc)
     assert op.device_status() == 0
-    shortest = int(np.argmin(dc.index.kvlens))
-    _check_sample(orc, dc, spec, out, [shortest])
+    shortest, longest = int(np.argmin(dc.index.kvlens)), int(np.argmax(dc.index.kvlens))
+    _check_sample(orc, dc, spec, out, [shortest, longest])
     other = _forward(_op(dc, spec, split_k=0), dc).float()
     diff = (other - out.float()).abs()
     assert float(diff.max()) <= MAX_ABS and float(diff.mean()) <= MEAN_ABS

@@ -71,6 +71,7 @@ def run_case(orc, dev, hc, *, layout=0, num_layer=1, layer_idx=0, split_k=1, cac
     np.testing.assert_array_equal(scale.cpu().numpy().view(np.uint16), o_scale.view(np.uint16),
                                   err_msg="fp16 cache scales differ")
     got = got.cpu().numpy().astype(np.float32)
+    run_case.last_output = got
     assert np.isfinite(got).all()
     err = np.abs(got - want.astype(np.float32))
     if check_attention:
@@ -96,8 +97,11 @@ def test_cfg1_tiny_decode(orc, torch_dev, pkg):
     # and against the committed golden output of the oracle
     from pathlib import Path
     g = Path(__file__).resolve().parent / "golden" / "attn_output-4_8_64-fp16.dat"
-    want = np.fromfile(g, dtype=np.float16).reshape(4, 8, 64)
-    assert err.shape == want.shape
+    want = np.fromfile(g, dtype=np.float16).reshape(4, 8, 64).astype(np.float32)
+    got = run_case.last_output
+    assert got.shape == want.shape
+    gerr = np.abs(got - want)
+    assert gerr.max() <= MAX_ABS and gerr.mean() <= MEAN_ABS, (gerr.max(), gerr.mean())
 
 
 @pytest.mark.parametrize("layout,num_layer,layer_idx", [(0, 1, 0), (3, 1, 0), (0, 3, 1), (3, 2, 1)])
@@ -313,6 +317,19 @@ def test_cache_prefill_with_history(orc, torch_dev, pkg, layout):
     idx = workloads.make_index([40, 300, 17], [100, 64, 130], prefill_hist=[0, 200, 131])
     hc = _case_with_index(hc, idx, spec)
     run_case(orc, torch_dev, hc, layout=layout, cache_prefill=True)
+
+
+@pytest.mark.parametrize("cache_prefill", [False, True])
+def test_non_causal_prefill_in_the_cached_operator(orc, torch_dev, pkg, cache_prefill):
+    """is_causal = 0 is passed through (multi_head_cache_attention_kernel.cc:184 passes param_->is_causal):
+    every query row of a prefill sequence sees all of the sequence's kv positions; decode rows are unaffected."""
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=8, num_kv_heads=2, head_dim=128, n_decode=2, kv_dist="list", kv_list=(40, 300),
+                 n_prefill=3, seed=34, is_causal=False)
+    hc = workloads.host_case(spec)
+    idx = workloads.make_index([40, 300], [100, 64, 200], prefill_hist=[0, 77, 0] if cache_prefill else None)
+    hc = _case_with_index(hc, idx, spec)
+    run_case(orc, torch_dev, hc, cache_prefill=cache_prefill)
 
 
 def test_smoke_entry_point(torch_dev):
