@@ -143,6 +143,37 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
                          void* workspace, uint64_t workspace_bytes, void* attn_output, void* stream);
 
 /*
+ * The optional attn_mask input of both attention operators.  The reference hands its shape and pointer
+ * to the external kernel (multi_head_cache_attention_kernel.cc:105-110,179-180;
+ * multi_head_attention_kernel.cc:96-103,114-115) and treats a tensor of zero elements as absent; the meaning
+ * of the values is fixed by this library as follows.  The mask is ADDITIVE, fp16, dense, of shape
+ * [T, C] (one mask for all heads) or [num_heads, T, C]; T = seqstarts[batch] query tokens, C >= kvstarts[batch]
+ * and C % 8 == 0.  The element for query token i and kv position j of sequence b is
+ * [.., seqstarts[b] + i, kvstarts[b] + j]; it is added to the scaled score q.k / sqrt(head_dim) before the
+ * softmax, in addition to the causal mask when is_causal is set.  -inf removes a position; a query row whose
+ * visible positions are all removed yields zeros; +inf and NaN entries count as -inf.  Entries the tensor
+ * is too narrow to hold read as 0 and set PPLB200_DEV_MASK_OUT_OF_RANGE in the device status word.
+ * data == NULL (or a NULL pplb200_attn_mask pointer): no mask.
+ */
+typedef struct pplb200_attn_mask {
+    const void* data; /* device pointer, fp16 */
+    int32_t ndim;     /* 2 or 3 */
+    int32_t reserved;
+    int64_t dims[3];  /* the first `ndim` entries are used */
+} pplb200_attn_mask;
+
+/* Host-only shape check of a mask against the operator's head count and query rows: PPLB200_SUCCESS (also
+ * for an absent mask) or PPLB200_INVALID_VALUE.  The forward calls run the same check. */
+int pplb200_attn_mask_check(const pplb200_attn_mask* attn_mask, int32_t num_heads, int64_t total_tokens);
+
+/* pplb200_mhca_forward with the attn_mask input (multi_head_cache_attention_kernel.cc:39, input 12). */
+int pplb200_mhca_forward_masked(const pplb200_attn_params* p, const void* query, const void* current_key,
+                                const void* current_value, const int64_t* seqstarts, const int64_t* kvstarts,
+                                const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale,
+                                const pplb200_attn_mask* attn_mask, void* workspace, uint64_t workspace_bytes,
+                                void* attn_output, void* stream);
+
+/*
  * MultiHeadCacheAttention without a caller workspace.  This entry point has no counterpart in the
  * reference: ppl.nn always borrows the scratch from its engine's tmp-buffer pool
  * (multi_head_cache_attention_kernel.cc:218-228).  It is for callers that cannot allocate device
@@ -158,7 +189,7 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
  *     current); make that first call before starting any stream capture.
  *   - All calls on a device share the one array, which keeps whatever the previous call left in
  *     it; the kernels re-initialise what they rely on, but two calls that overlap on the GPU
- *     (different streams) race on it.  pplb200_mhca_device_status cannot be used with it.
+ *     (different streams) race on it.  The status word is read with pplb200_static_scratch_status.
  */
 int pplb200_mhca_forward_noalloc(const pplb200_attn_params* p, const void* query, const void* current_key,
                                  const void* current_value, const int64_t* seqstarts, const int64_t* kvstarts,
@@ -167,6 +198,11 @@ int pplb200_mhca_forward_noalloc(const pplb200_attn_params* p, const void* query
 
 /* Capacity in bytes of the built-in scratch used by pplb200_mhca_forward_noalloc. */
 uint64_t pplb200_static_scratch_bytes(void);
+
+/* pplb200_mhca_device_status for the built-in scratch of the current device: the status word the last
+ * pplb200_mhca_forward_noalloc call on this device left behind.  Synchronises `stream`.  The library does
+ * not follow a cudaDeviceReset: the looked-up address is kept for the life of the process. */
+int pplb200_static_scratch_status(void* stream, uint32_t* status);
 
 /*
  * MultiHeadAttention without a cache (opmx.dynamic_batching.MultiHeadAttention).  Replaces
@@ -178,8 +214,9 @@ uint64_t pplb200_static_scratch_bytes(void);
  *   is_causal: query row i of a sequence sees kv positions <= (kvlen - seqlen) + i, i.e. the mask is
  *   aligned to the end of the kv range; a row that sees nothing yields zeros.  Scores are scaled by
  *   1/sqrt(head_dim).  `decoding_batches` is accepted for symmetry with the cached operator and not used.
- * The attn_mask input and is_alibi of the reference operator are not supported; the host-side
- * operator rejects them.  `workspace`: at least pplb200_mha_workspace_size() bytes of device memory
+ * is_alibi of the reference operator is not supported (the reference refuses it as well,
+ * multi_head_attention_kernel.cc:72-75); the attn_mask input goes through pplb200_mha_forward_masked.
+ * `workspace`: at least pplb200_mha_workspace_size() bytes of device memory
  * (it only holds the device status word, readable with pplb200_mhca_device_status).
  */
 typedef struct pplb200_mha_params {
@@ -200,6 +237,12 @@ int pplb200_mha_workspace_size(const pplb200_mha_params* p, uint64_t* bytes);
 int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const void* key, const void* value,
                         const int64_t* seqstarts, const int64_t* kvstarts, void* workspace, uint64_t workspace_bytes,
                         void* attn_output, void* stream);
+
+/* pplb200_mha_forward with the attn_mask input (multi_head_attention_kernel.cc:30, input 3); see
+ * pplb200_attn_mask for the convention. */
+int pplb200_mha_forward_masked(const pplb200_mha_params* p, const void* query, const void* key, const void* value,
+                               const int64_t* seqstarts, const int64_t* kvstarts, const pplb200_attn_mask* attn_mask,
+                               void* workspace, uint64_t workspace_bytes, void* attn_output, void* stream);
 
 /*
  * RotaryPositionEmbedding for ragged batches (opmx.dynamic_batching.RotaryPositionEmbedding).  Replaces
@@ -267,8 +310,10 @@ enum {
     PPLB200_DEV_TMA_WAIT_TIMEOUT = 1,  /* a wait for a bulk-tensor copy ran out of iterations    */
     PPLB200_DEV_MMA_WAIT_TIMEOUT = 2,  /* a wait for a tensor-core commit ran out of iterations   */
     PPLB200_DEV_LENGTH_CLAMPED = 4,    /* a sequence exceeded max_kvlen / max_seqlen and was cut   */
-    PPLB200_DEV_ROW_OUT_OF_RANGE = 8   /* cachestarts/start_pos named a row outside [0, max_tokens):
+    PPLB200_DEV_ROW_OUT_OF_RANGE = 8,  /* cachestarts/start_pos named a row outside [0, max_tokens):
                                           that row was neither read nor written                     */
+    PPLB200_DEV_MASK_OUT_OF_RANGE = 16 /* attn_mask has fewer columns than kvstarts needs: the missing
+                                          entries were read as 0                                    */
 };
 
 /* Name of a status code ("RC_SUCCESS", ...).  Never null. */

@@ -232,12 +232,35 @@ int orc_kv_gather_dequant(const orc_desc* d, const int64_t* kvstarts, const int6
 
 /* ---------------------------------------------------------------- attention ----------- */
 
+/* The optional attn_mask input of both attention operators.  The reference only forwards its shape and
+ * pointer to the external kernel library (multi_head_cache_attention_kernel.cc:105-110,179-180;
+ * multi_head_attention_kernel.cc:96-103,114-115), so the convention is fixed here, after the operator
+ * description of the OPMX dynamic-batching attention ops: an ADDITIVE fp16 mask of shape [T, C] or
+ * [num_heads, T, C], T = seqstarts[batch] query tokens, C >= kvstarts[batch]; the element for query token i and
+ * kv position j of sequence b is [.., seqstarts[b] + i, kvstarts[b] + j]; it is added to the scaled score
+ * before the softmax, on top of the causal mask when is_causal is set.  A row whose visible positions are all
+ * masked with -inf yields zeros.  data == NULL: no mask. */
+typedef struct {
+    const uint16_t* data;
+    int64_t heads; /* 1: one mask for all heads */
+    int64_t rows;
+    int64_t cols;
+} orc_mask;
+
+static const uint16_t* mask_row_ptr(const orc_mask* m, int64_t head, int64_t tok, int64_t col0) {
+    if (!m || !m->data) {
+        return NULL;
+    }
+    const int64_t hh = m->heads > 1 ? head : 0;
+    return m->data + (hh * m->rows + tok) * m->cols + col0;
+}
+
 /* One (sequence, query token, query head): scores over kv positions [0, n_kv), softmax, PV.
  * K/V rows come from `fetch` = 0: INT8 cache, 1: fp16 current tensors. */
 static void attend_one(const orc_desc* d, const float* q, int64_t n_kv, int fetch, int64_t b, int kvh,
                        const int64_t* cachestarts, const int8_t* cache, const uint16_t* scale,
-                       const uint16_t* cur_k, const uint16_t* cur_v, int64_t cur_base, float* scores,
-                       float* krow, uint16_t* out) {
+                       const uint16_t* cur_k, const uint16_t* cur_v, int64_t cur_base, const uint16_t* mask_row,
+                       float* scores, float* krow, uint16_t* out) {
     const int64_t Dh = d->head_dim, H = d->num_kv_heads, Gs = Dh / 8;
     const float inv_sqrt = 1.0f / sqrtf((float)Dh);
     float mx = -INFINITY;
@@ -263,9 +286,18 @@ static void attend_one(const orc_desc* d, const float* q, int64_t n_kv, int fetc
             acc += q[e] * krow[e];
         }
         scores[j] = acc * inv_sqrt;
+        if (mask_row) { /* additive mask, applied to the scaled score */
+            scores[j] += orc_half_to_float(mask_row[j]);
+        }
         if (scores[j] > mx) {
             mx = scores[j];
         }
+    }
+    if (!(mx > -INFINITY)) { /* every visible position is masked with -inf: the row attends to nothing */
+        for (int64_t e = 0; e < Dh; ++e) {
+            out[e] = 0;
+        }
+        return;
     }
     float denom = 0.0f;
     for (int64_t j = 0; j < n_kv; ++j) {
@@ -302,9 +334,10 @@ static void attend_one(const orc_desc* d, const float* q, int64_t n_kv, int fetc
 /* MultiHeadCacheAttention, read side only: attention over a cache that already holds this
  * step's tokens.  seq_lo/seq_hi restrict the work to sequences [seq_lo, seq_hi) so that the
  * benchmark can time a bounded sample.  Parallel over (sequence, query token, head). */
-int orc_attention(const orc_desc* d, const uint16_t* query, const uint16_t* cur_k, const uint16_t* cur_v,
-                  const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos,
-                  const int8_t* cache, const uint16_t* scale, uint16_t* out, int64_t seq_lo, int64_t seq_hi) {
+int orc_attention_masked(const orc_desc* d, const uint16_t* query, const uint16_t* cur_k, const uint16_t* cur_v,
+                         const int64_t* seqstarts, const int64_t* kvstarts, const int64_t* cachestarts,
+                         const int64_t* start_pos, const int8_t* cache, const uint16_t* scale, uint16_t* out,
+                         int64_t seq_lo, int64_t seq_hi, const orc_mask* mask) {
     const int64_t Dh = d->head_dim, Hq = d->num_heads, Hkv = d->num_kv_heads;
     if (Hkv <= 0 || Hq % Hkv != 0 || d->quant_group != 8) {
         return 1;
@@ -343,8 +376,11 @@ int orc_attention(const orc_desc* d, const uint16_t* query, const uint16_t* cur_
                         qf[e] = orc_half_to_float(q16[e]);
                     }
                     const int64_t n_kv = d->is_causal ? hist + i + 1 : hist + seqlen;
+                    /* kv position 0 of what this row reads: position 0 of the sequence, or its first new token */
+                    const uint16_t* mrow = (mask && mask->data)
+                        ? mask_row_ptr(mask, h, tok, kvstarts[b] + (from_cache ? 0 : start_pos[b])) : NULL;
                     attend_one(d, qf, n_kv, from_cache ? 0 : 1, b, h / group, cachestarts, cache, scale, cur_k,
-                               cur_v, seqstarts[b], scores, krow, out + (tok * Hq + h) * Dh);
+                               cur_v, seqstarts[b], mrow, scores, krow, out + (tok * Hq + h) * Dh);
                 }
             }
         }
@@ -353,6 +389,13 @@ int orc_attention(const orc_desc* d, const uint16_t* query, const uint16_t* cur_
         free(qf);
     }
     return failed;
+}
+
+int orc_attention(const orc_desc* d, const uint16_t* query, const uint16_t* cur_k, const uint16_t* cur_v,
+                  const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos,
+                  const int8_t* cache, const uint16_t* scale, uint16_t* out, int64_t seq_lo, int64_t seq_hi) {
+    return orc_attention_masked(d, query, cur_k, cur_v, seqstarts, NULL, cachestarts, start_pos, cache, scale, out,
+                                seq_lo, seq_hi, NULL);
 }
 
 /* The whole MultiHeadCacheAttention op: append this step's K/V, then attend. */
@@ -367,14 +410,26 @@ int orc_mhca(const orc_desc* d, const uint16_t* query, const uint16_t* cur_k, co
                          d->batch);
 }
 
+/* The same with the optional attn_mask input (see orc_mask). */
+int orc_mhca_masked(const orc_desc* d, const uint16_t* query, const uint16_t* cur_k, const uint16_t* cur_v,
+                    const int64_t* seqstarts, const int64_t* kvstarts, const int64_t* cachestarts,
+                    const int64_t* start_pos, int8_t* cache, uint16_t* scale, uint16_t* out, const orc_mask* mask) {
+    int rc = orc_kv_append(d, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale);
+    if (rc != 0) {
+        return rc;
+    }
+    return orc_attention_masked(d, query, cur_k, cur_v, seqstarts, kvstarts, cachestarts, start_pos, cache, scale,
+                                out, 0, d->batch, mask);
+}
+
 /* MultiHeadAttention without a cache (contract: src/ppl/nn/engines/llm_cuda/kernels/opmx/dynamic_batching/
  * multi_head_attention_kernel.cc:24-128; the arithmetic is not in the reference tree).  Sequence b owns query
  * rows [seqstarts[b], seqstarts[b+1]) and key/value rows [kvstarts[b], kvstarts[b+1]) of tensors shaped
  * [rows, heads, head_dim].  With is_causal, query row i sees kv positions <= (kvlen - seqlen) + i (the mask
  * is aligned to the end of the kv range; a choice of this repository); a row that sees nothing gives zeros.
  * Only num_heads, num_kv_heads, head_dim, is_causal and batch of the descriptor are read. */
-int orc_mha(const orc_desc* d, const uint16_t* query, const uint16_t* key, const uint16_t* value,
-            const int64_t* seqstarts, const int64_t* kvstarts, uint16_t* out) {
+int orc_mha_masked(const orc_desc* d, const uint16_t* query, const uint16_t* key, const uint16_t* value,
+                   const int64_t* seqstarts, const int64_t* kvstarts, uint16_t* out, const orc_mask* mask) {
     const int64_t Dh = d->head_dim, Hq = d->num_heads, Hkv = d->num_kv_heads;
     if (Hkv <= 0 || Hq % Hkv != 0) {
         return 1;
@@ -419,7 +474,8 @@ int orc_mha(const orc_desc* d, const uint16_t* query, const uint16_t* key, const
                     for (int64_t e = 0; e < Dh; ++e) {
                         qf[e] = orc_half_to_float(q16[e]);
                     }
-                    attend_one(d, qf, n_kv, 1, b, h / group, NULL, NULL, NULL, key, value, kvstarts[b], scores, krow, o);
+                    attend_one(d, qf, n_kv, 1, b, h / group, NULL, NULL, NULL, key, value, kvstarts[b],
+                               mask_row_ptr(mask, h, tok, kvstarts[b]), scores, krow, o);
                 }
             }
         }
@@ -428,6 +484,11 @@ int orc_mha(const orc_desc* d, const uint16_t* query, const uint16_t* key, const
         free(qf);
     }
     return failed;
+}
+
+int orc_mha(const orc_desc* d, const uint16_t* query, const uint16_t* key, const uint16_t* value,
+            const int64_t* seqstarts, const int64_t* kvstarts, uint16_t* out) {
+    return orc_mha_masked(d, query, key, value, seqstarts, kvstarts, out, NULL);
 }
 
 /* RotaryPositionEmbedding for ragged batches (contract: src/ppl/nn/engines/llm_cuda/kernels/opmx/

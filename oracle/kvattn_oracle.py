@@ -51,6 +51,19 @@ class OrcDesc(ctypes.Structure):
     ]
 
 
+class OrcMask(ctypes.Structure):
+    """The optional attn_mask input: additive fp16, [T, C] or [num_heads, T, C] (see orc_mask in the C file)."""
+    _fields_ = [("data", ctypes.c_void_p), ("heads", ctypes.c_int64), ("rows", ctypes.c_int64), ("cols", ctypes.c_int64)]
+
+
+def _mask(m: np.ndarray | None):
+    if m is None or m.size == 0:
+        return None
+    assert m.dtype == np.float16 and m.flags["C_CONTIGUOUS"] and m.ndim in (2, 3)
+    heads = m.shape[0] if m.ndim == 3 else 1
+    return OrcMask(m.ctypes.data, heads, m.shape[-2], m.shape[-1])
+
+
 def _ptr(a: np.ndarray):
     assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
     return a.ctypes.data_as(ctypes.c_void_p)
@@ -83,6 +96,10 @@ class COracle:
                                ctypes.c_float, ctypes.c_int64] + [vp] * 6
         L.orc_mha.restype = ctypes.c_int
         L.orc_mha.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 6
+        L.orc_mhca_masked.restype = ctypes.c_int
+        L.orc_mhca_masked.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 10 + [ctypes.POINTER(OrcMask)]
+        L.orc_mha_masked.restype = ctypes.c_int
+        L.orc_mha_masked.argtypes = [ctypes.POINTER(OrcDesc)] + [vp] * 6 + [ctypes.POINTER(OrcMask)]
         L.orc_num_threads.restype = ctypes.c_int
 
     # -- scalar helpers ---------------------------------------------------------------
@@ -149,19 +166,32 @@ class COracle:
             raise RuntimeError(f"orc_attention failed: {rc}")
         return out
 
-    def mhca(self, d, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale):
+    def mhca(self, d, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale, *, kvstarts=None,
+             attn_mask=None):
+        """The whole operator: append, then attend.  `attn_mask` (with `kvstarts`): the optional additive mask."""
         out = np.zeros(query.shape, dtype=np.float16)
-        rc = self.lib.orc_mhca(ctypes.byref(d), _ptr(query), _ptr(cur_k), _ptr(cur_v), _ptr(seqstarts),
-                               _ptr(cachestarts), _ptr(start_pos), _ptr(cache), _ptr(scale), _ptr(out))
+        m = _mask(attn_mask)
+        if m is None:
+            rc = self.lib.orc_mhca(ctypes.byref(d), _ptr(query), _ptr(cur_k), _ptr(cur_v), _ptr(seqstarts),
+                                   _ptr(cachestarts), _ptr(start_pos), _ptr(cache), _ptr(scale), _ptr(out))
+        else:
+            rc = self.lib.orc_mhca_masked(ctypes.byref(d), _ptr(query), _ptr(cur_k), _ptr(cur_v), _ptr(seqstarts),
+                                          _ptr(kvstarts), _ptr(cachestarts), _ptr(start_pos), _ptr(cache), _ptr(scale),
+                                          _ptr(out), ctypes.byref(m))
         if rc != 0:
             raise RuntimeError(f"orc_mhca failed: {rc}")
         return out
 
-    def mha(self, d, query, key, value, seqstarts, kvstarts):
+    def mha(self, d, query, key, value, seqstarts, kvstarts, *, attn_mask=None):
         """The un-cached operator: attention over the call's own key/value tensors."""
         out = np.zeros(query.shape, dtype=np.float16)
-        rc = self.lib.orc_mha(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts), _ptr(kvstarts),
-                              _ptr(out))
+        m = _mask(attn_mask)
+        if m is None:
+            rc = self.lib.orc_mha(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts),
+                                  _ptr(kvstarts), _ptr(out))
+        else:
+            rc = self.lib.orc_mha_masked(ctypes.byref(d), _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts),
+                                         _ptr(kvstarts), _ptr(out), ctypes.byref(m))
         if rc != 0:
             raise RuntimeError(f"orc_mha failed: {rc}")
         return out
@@ -202,15 +232,21 @@ def np_dequant(codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
     return (c * scales.astype(np.float32)[..., None]).reshape(codes.shape)
 
 
-def np_attention_one(q: np.ndarray, k: np.ndarray, v: np.ndarray) -> np.ndarray:
-    """One query vector against n_kv rows; all float32.  q [Dh], k/v [n_kv, Dh] -> [Dh]."""
+def np_attention_one(q: np.ndarray, k: np.ndarray, v: np.ndarray, mask_row: np.ndarray | None = None) -> np.ndarray:
+    """One query vector against n_kv rows; all float32.  q [Dh], k/v [n_kv, Dh] -> [Dh]; `mask_row` [n_kv] is added
+    to the scaled scores; a row masked with -inf everywhere gives zeros."""
     s = (k @ q) * np.float32(1.0 / np.sqrt(np.float32(q.shape[0])))
+    if mask_row is not None:
+        s = s + mask_row.astype(np.float32)
+    if not s.max() > -np.inf:
+        return np.zeros(v.shape[1], dtype=np.float32)
     p = np.exp(s - s.max())
     return (p @ v) / p.sum()
 
 
-def np_mha(query, key, value, seqstarts, kvstarts, num_kv_heads: int, is_causal: bool) -> np.ndarray:
-    """numpy twin of orc_mha (float32 inside, fp16 result): causal masks aligned to the end of the kv range."""
+def np_mha(query, key, value, seqstarts, kvstarts, num_kv_heads: int, is_causal: bool, attn_mask=None) -> np.ndarray:
+    """numpy twin of orc_mha (float32 inside, fp16 result): causal masks aligned to the end of the kv range;
+    attn_mask [T, C] or [Hq, T, C] is indexed [.., seqstarts[b] + i, kvstarts[b] + j]."""
     T, Hq, Dh = query.shape
     group = Hq // num_kv_heads
     out = np.zeros((T, Hq, Dh), dtype=np.float16)
@@ -224,7 +260,11 @@ def np_mha(query, key, value, seqstarts, kvstarts, num_kv_heads: int, is_causal:
                 continue
             for h in range(Hq):
                 kvh = h // group
-                out[s0 + i, h] = np_attention_one(q32[s0 + i, h], k32[k0:k0 + n, kvh], v32[k0:k0 + n, kvh]).astype(np.float16)
+                mrow = None
+                if attn_mask is not None:
+                    mrow = (attn_mask[h] if attn_mask.ndim == 3 else attn_mask)[s0 + i, k0:k0 + n]
+                out[s0 + i, h] = np_attention_one(q32[s0 + i, h], k32[k0:k0 + n, kvh], v32[k0:k0 + n, kvh],
+                                                  mrow).astype(np.float16)
     return out
 
 

@@ -31,6 +31,8 @@ DEV_OK = 0
 DEV_TMA_WAIT_TIMEOUT = 1
 DEV_MMA_WAIT_TIMEOUT = 2
 DEV_LENGTH_CLAMPED = 4
+DEV_ROW_OUT_OF_RANGE = 8
+DEV_MASK_OUT_OF_RANGE = 16
 
 # every symbol include/ppl_nn_b200.h declares
 EXPORTS = (
@@ -39,11 +41,15 @@ EXPORTS = (
     "pplb200_kv_gather_dequant",
     "pplb200_mhca_workspace_size",
     "pplb200_mhca_forward",
+    "pplb200_mhca_forward_masked",
+    "pplb200_attn_mask_check",
     "pplb200_mhca_forward_noalloc",
     "pplb200_static_scratch_bytes",
+    "pplb200_static_scratch_status",
     "pplb200_mhca_device_status",
     "pplb200_mha_workspace_size",
     "pplb200_mha_forward",
+    "pplb200_mha_forward_masked",
     "pplb200_rope_workspace_size",
     "pplb200_rope_forward",
     "pplb200_rope_kv_append_i8g8",
@@ -91,6 +97,22 @@ class MhaParams(ctypes.Structure):
     ]
 
 
+class AttnMask(ctypes.Structure):
+    """Mirror of ``pplb200_attn_mask``: the optional additive fp16 mask, [T, C] or [num_heads, T, C]."""
+
+    _fields_ = [("data", ctypes.c_void_p), ("ndim", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("dims", ctypes.c_int64 * 3)]
+
+    @classmethod
+    def of(cls, data_ptr: int, shape) -> "AttnMask":
+        m = cls()
+        m.data = data_ptr
+        m.ndim = len(shape)
+        for i, d in enumerate(shape[:3]):
+            m.dims[i] = int(d)
+        return m
+
+
 class RopeParams(ctypes.Structure):
     """Mirror of ``pplb200_rope_params``."""
 
@@ -134,10 +156,16 @@ class Library:
         d.pplb200_mhca_workspace_size.argtypes = [pp, ctypes.POINTER(ctypes.c_uint64)]
         d.pplb200_mhca_forward.restype = ctypes.c_int
         d.pplb200_mhca_forward.argtypes = [pp, vp, vp, vp, i64p, i64p, i64p, i64p, vp, vp, vp, ctypes.c_uint64, vp, vp]
+        kp = ctypes.POINTER(AttnMask)
+        d.pplb200_mhca_forward_masked.restype = ctypes.c_int
+        d.pplb200_mhca_forward_masked.argtypes = [pp, vp, vp, vp, i64p, i64p, i64p, i64p, vp, vp, kp, vp,
+                                                  ctypes.c_uint64, vp, vp]
         d.pplb200_mhca_forward_noalloc.restype = ctypes.c_int
         d.pplb200_mhca_forward_noalloc.argtypes = [pp, vp, vp, vp, i64p, i64p, i64p, i64p, vp, vp, vp, vp]
         d.pplb200_static_scratch_bytes.restype = ctypes.c_uint64
         d.pplb200_static_scratch_bytes.argtypes = []
+        d.pplb200_static_scratch_status.restype = ctypes.c_int
+        d.pplb200_static_scratch_status.argtypes = [vp, ctypes.POINTER(ctypes.c_uint32)]
         d.pplb200_mhca_device_status.restype = ctypes.c_int
         d.pplb200_mhca_device_status.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_uint32)]
         mp = ctypes.POINTER(MhaParams)
@@ -145,6 +173,8 @@ class Library:
         d.pplb200_mha_workspace_size.argtypes = [mp, ctypes.POINTER(ctypes.c_uint64)]
         d.pplb200_mha_forward.restype = ctypes.c_int
         d.pplb200_mha_forward.argtypes = [mp, vp, vp, vp, i64p, i64p, vp, ctypes.c_uint64, vp, vp]
+        d.pplb200_mha_forward_masked.restype = ctypes.c_int
+        d.pplb200_mha_forward_masked.argtypes = [mp, vp, vp, vp, i64p, i64p, kp, vp, ctypes.c_uint64, vp, vp]
         rp = ctypes.POINTER(RopeParams)
         d.pplb200_rope_workspace_size.restype = ctypes.c_int
         d.pplb200_rope_workspace_size.argtypes = [rp, ctypes.POINTER(ctypes.c_uint64)]
@@ -209,6 +239,25 @@ class Library:
                      workspace, workspace_bytes, out, stream) -> int:
         return self.dll.pplb200_mhca_forward(ctypes.byref(p), q, cur_k, cur_v, seqstarts, kvstarts, cachestarts,
                                              start_pos, cache, scale, workspace, int(workspace_bytes), out, stream)
+
+    def mhca_forward_masked(self, p, q, cur_k, cur_v, seqstarts, kvstarts, cachestarts, start_pos, cache, scale,
+                            mask: "AttnMask | None", workspace, workspace_bytes, out, stream) -> int:
+        return self.dll.pplb200_mhca_forward_masked(ctypes.byref(p), q, cur_k, cur_v, seqstarts, kvstarts, cachestarts,
+                                                    start_pos, cache, scale,
+                                                    ctypes.byref(mask) if mask is not None else None, workspace,
+                                                    int(workspace_bytes), out, stream)
+
+    def mha_forward_masked(self, p, q, k, v, seqstarts, kvstarts, mask: "AttnMask | None", workspace,
+                           workspace_bytes, out, stream) -> int:
+        return self.dll.pplb200_mha_forward_masked(ctypes.byref(p), q, k, v, seqstarts, kvstarts,
+                                                   ctypes.byref(mask) if mask is not None else None, workspace,
+                                                   int(workspace_bytes), out, stream)
+
+    def static_scratch_status(self, stream) -> tuple[int, int]:
+        """Device status word the last no-alloc call left in the built-in scratch (synchronises the stream)."""
+        s = ctypes.c_uint32(0)
+        rc = self.dll.pplb200_static_scratch_status(stream, ctypes.byref(s))
+        return rc, int(s.value)
 
     def mhca_forward_noalloc(self, p, q, cur_k, cur_v, seqstarts, kvstarts, cachestarts, start_pos, cache, scale,
                              out, stream) -> int:

@@ -322,10 +322,53 @@ int pplb200_mhca_workspace_size(const pplb200_attn_params* p, uint64_t* bytes) {
     return PPLB200_SUCCESS;
 }
 
+// Shape checks of the optional attn_mask input; fills `m` (data == nullptr when there is no mask).
+static int make_mask(const pplb200_attn_mask* in, int num_heads, int64_t total_tokens, const int64_t* kvstarts,
+                     MaskDev* m) {
+    m->data = nullptr;
+    m->kvstarts = kvstarts;
+    m->cols = 0;
+    m->head_stride = 0;
+    if (!in || !in->data) {
+        return PPLB200_SUCCESS;
+    }
+    if (in->ndim != 2 && in->ndim != 3) {
+        return fail(PPLB200_INVALID_VALUE, "attn_mask must have 2 or 3 dimensions");
+    }
+    const int64_t heads = in->ndim == 3 ? in->dims[0] : 1;
+    const int64_t rows = in->dims[in->ndim - 2], cols = in->dims[in->ndim - 1];
+    if ((in->ndim == 3 && heads != num_heads) || rows < total_tokens || cols <= 0 || cols % 8 != 0) {
+        return fail(PPLB200_INVALID_VALUE,
+                    "attn_mask must be [T, C] or [num_heads, T, C] with T >= query rows and C a multiple of 8");
+    }
+    if (reinterpret_cast<uintptr_t>(in->data) & 1u) {
+        return fail(PPLB200_INVALID_VALUE, "attn_mask must be 2-byte aligned");
+    }
+    m->data = static_cast<const __half*>(in->data);
+    m->cols = cols;
+    m->head_stride = in->ndim == 3 ? rows * cols : 0;
+    return PPLB200_SUCCESS;
+}
+
+int pplb200_attn_mask_check(const pplb200_attn_mask* attn_mask, int32_t num_heads, int64_t total_tokens) {
+    MaskDev m;
+    return make_mask(attn_mask, num_heads, total_tokens, nullptr, &m);
+}
+
 int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const void* current_key,
                          const void* current_value, const int64_t* seqstarts, const int64_t* kvstarts,
                          const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale,
                          void* workspace, uint64_t workspace_bytes, void* attn_output, void* stream_v) {
+    return pplb200_mhca_forward_masked(p, query, current_key, current_value, seqstarts, kvstarts, cachestarts,
+                                       start_pos, cache, scale, nullptr, workspace, workspace_bytes, attn_output,
+                                       stream_v);
+}
+
+int pplb200_mhca_forward_masked(const pplb200_attn_params* p, const void* query, const void* current_key,
+                                const void* current_value, const int64_t* seqstarts, const int64_t* kvstarts,
+                                const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale,
+                                const pplb200_attn_mask* attn_mask, void* workspace, uint64_t workspace_bytes,
+                                void* attn_output, void* stream_v) {
     int rc = validate(p);
     if (rc != PPLB200_SUCCESS) {
         return rc;
@@ -344,6 +387,11 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     if (misaligned({query, current_key, current_value, cache, scale, attn_output},
                    {seqstarts, kvstarts, cachestarts, start_pos})) {
         return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
+    }
+    MaskDev amask;
+    rc = make_mask(attn_mask, p->num_heads, p->total_tokens, kvstarts, &amask);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
     }
     DeviceInfo di;
     rc = require_device(&di);
@@ -389,7 +437,7 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     }
     if (do_decode) {
         rc = launch_decode(*p, geom, w.decode, query, fuse ? current_key : nullptr, fuse ? current_value : nullptr,
-                           seqstarts, cachestarts, start_pos, cache, scale, workspace, attn_output, stream);
+                           seqstarts, cachestarts, start_pos, cache, scale, amask, workspace, attn_output, stream);
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
@@ -406,7 +454,7 @@ int pplb200_mhca_forward(const pplb200_attn_params* p, const void* query, const 
     }
     if (do_prefill) {
         rc = launch_prefill(*p, geom, w.prefill, query, current_key, current_value, seqstarts, cachestarts, start_pos,
-                            cache, scale, ws + w.off_prefill, status, attn_output, stream);
+                            cache, scale, amask, ws + w.off_prefill, status, attn_output, stream);
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
@@ -425,6 +473,13 @@ int pplb200_mha_workspace_size(const pplb200_mha_params* p, uint64_t* bytes) {
 int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const void* key, const void* value,
                         const int64_t* seqstarts, const int64_t* kvstarts, void* workspace, uint64_t workspace_bytes,
                         void* attn_output, void* stream_v) {
+    return pplb200_mha_forward_masked(p, query, key, value, seqstarts, kvstarts, nullptr, workspace, workspace_bytes,
+                                      attn_output, stream_v);
+}
+
+int pplb200_mha_forward_masked(const pplb200_mha_params* p, const void* query, const void* key, const void* value,
+                               const int64_t* seqstarts, const int64_t* kvstarts, const pplb200_attn_mask* attn_mask,
+                               void* workspace, uint64_t workspace_bytes, void* attn_output, void* stream_v) {
     if (!p) {
         return fail(PPLB200_NOT_FOUND, "params is null");
     }
@@ -451,8 +506,13 @@ int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const vo
     if (misaligned({query, key, value, attn_output}, {seqstarts, kvstarts})) {
         return fail(PPLB200_INVALID_VALUE, "tensor pointers must be 16-byte aligned (index tensors 8-byte)");
     }
+    MaskDev amask;
+    int rc = make_mask(attn_mask, p->num_heads, p->total_tokens, kvstarts, &amask);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
     DeviceInfo di;
-    int rc = require_device(&di);
+    rc = require_device(&di);
     if (rc != PPLB200_SUCCESS) {
         return rc;
     }
@@ -469,8 +529,8 @@ int pplb200_mha_forward(const pplb200_mha_params* p, const void* query, const vo
         return fail(PPLB200_DEVICE_RUNTIME_ERROR, "cudaMemsetAsync(status) failed");
     }
     return launch_mha(p->num_heads, p->num_kv_heads, p->head_dim, p->is_causal, p->batch, p->max_seqlen, p->max_kvlen,
-                      p->total_tokens, p->total_kv_tokens, query, key, value, seqstarts, kvstarts, status, attn_output,
-                      stream);
+                      p->total_tokens, p->total_kv_tokens, query, key, value, seqstarts, kvstarts, amask, status,
+                      attn_output, stream);
 }
 
 static int validate_rope(const pplb200_rope_params* p) {

@@ -18,6 +18,8 @@ constexpr uint32_t kDevMmaTimeout = 2;
 constexpr uint32_t kDevLengthClamped = 4;   // a sequence was longer than max_kvlen / max_seqlen and was clamped
 constexpr uint32_t kDevRowOutOfRange = 8;   // an index tensor named a cache row outside [0, max_tokens): access skipped
 
+constexpr uint32_t kDevMaskOutOfRange = 16;  // attn_mask is narrower than kvstarts needs: the missing entries read as 0
+
 // Time budget of ONE bounded wait in every kernel of the library, in SM clock cycles: about 100 ms at
 // 2 GHz, four orders of magnitude beyond any legitimate copy or MMA latency.  A wait that exhausts it
 // records a status code; the waiting thread then stops waiting altogether, so a stuck kernel ends after
@@ -300,6 +302,16 @@ __device__ __forceinline__ int64_t cache_row(const CacheGeom& g, const int64_t* 
 __device__ __forceinline__ bool cache_row_ok(int64_t row, int64_t max_tokens) {
     return row >= 0 && row < max_tokens;
 }
+
+// The optional attn_mask input on the device: additive fp16, [rows, cols] or [heads, rows, cols]; the element
+// for query token q (row of the query tensor), head h and kv position j of sequence b is
+// data[h * head_stride + q * cols + kvstarts[b] + j].  data == nullptr: no mask.
+struct MaskDev {
+    const __half* data;
+    const int64_t* kvstarts;
+    int64_t cols;
+    int64_t head_stride;  // rows * cols, or 0 when one mask serves every head
+};
 
 __device__ __forceinline__ int64_t cache_offset(const CacheGeom& g, int64_t row, int kv, int head) {
     return row * g.stride_s + g.layer_idx * g.stride_l + kv * g.stride_kv + head * g.stride_h;

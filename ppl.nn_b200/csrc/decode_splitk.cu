@@ -71,6 +71,9 @@ namespace {
 #define PPLB200_DECODE_CTAS 2
 #endif
 
+#ifndef PPLB200_DECODE_KRESID
+#define PPLB200_DECODE_KRESID 1  // second MMA with the rounding remainders of the dequantised keys (see dequant_k_word)
+#endif
 #ifndef PPLB200_DECODE_OVERSUB_DEFAULT
 #define PPLB200_DECODE_OVERSUB_DEFAULT 1
 #endif
@@ -138,6 +141,7 @@ struct DecodeArgs {
     const __half* cur_v;
     int8_t* cache;
     int32_t num_kv_heads;
+    MaskDev mask;  // the optional attn_mask input (kernel instances with MASK only)
 };
 
 // Order of the four outer dimensions of the cache tensor maps (see CacheMapOrder), as a template
@@ -288,11 +292,25 @@ decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restr
 // Main kernel
 // ------------------------------------------------------------------------------------------
 
-// K codes word -> two half2 (channels 0,1 and 2,3 of the word), scaled.
-__device__ __forceinline__ void dequant_k_word(uint32_t w, __half2 s2, uint32_t& lo, uint32_t& hi) {
+// K codes word -> two half2 (channels 0,1 and 2,3 of the word), scaled: k = fp16(code * scale).  The product
+// of a 7-bit code and an 11-bit scale does not fit fp16; its rounding error, 2^-11 relative per element, is the
+// largest error of the whole kernel on keys with outlier channels (scores with a wide range: a pair of
+// competing tokens then shifts weight by 1e-3).  So the error itself is kept: e = fma(code, scale, -k) is the
+// exact remainder code * scale - k (the rounding error of a product is representable), and a second MMA adds
+// e . q to the same accumulator, which makes the scores those of the exactly dequantised keys.
+__device__ __forceinline__ void dequant_k_word(uint32_t w, __half2 s2, uint32_t& lo, uint32_t& hi, uint32_t& elo,
+                                               uint32_t& ehi) {
     const uint32_t x = w ^ 0x80808080u;
-    lo = h2_as_u32(__hmul2(biased_bytes_to_half2<0x5140u>(x), s2));
-    hi = h2_as_u32(__hmul2(biased_bytes_to_half2<0x5342u>(x), s2));
+    const __half2 c_lo = biased_bytes_to_half2<0x5140u>(x), c_hi = biased_bytes_to_half2<0x5342u>(x);
+    const __half2 k_lo = __hmul2(c_lo, s2), k_hi = __hmul2(c_hi, s2);
+    lo = h2_as_u32(k_lo);
+    hi = h2_as_u32(k_hi);
+#if PPLB200_DECODE_KRESID
+    elo = h2_as_u32(__hfma2(c_lo, s2, __hneg2(k_lo)));
+    ehi = h2_as_u32(__hfma2(c_hi, s2, __hneg2(k_hi)));
+#else
+    elo = ehi = 0u;
+#endif
 }
 
 // V codes words of two tokens (same 4 channels) -> four half2 {token A, token B}, one per channel.
@@ -352,7 +370,7 @@ struct Cursor {
     int32_t kvh;
 };
 
-template <int DH, int ORDER>
+template <int DH, int ORDER, bool MASK>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const DecodeArgs a) {
     using T = Traits<DH>;
@@ -599,6 +617,25 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
             }
             float m0 = kNegBig, m1 = kNegBig, l0 = 0.0f, l1 = 0.0f;
+            // attn_mask rows of this thread's two query heads (2t, 2t+1 of the octet): element [kv position]
+            const __half* mrow0 = nullptr;
+            const __half* mrow1 = nullptr;
+            int64_t mask_room = 0;  // columns of the mask from this sequence's position 0 on
+            if constexpr (MASK) {
+                const int64_t col0 = a.mask.kvstarts[b];
+                mask_room = a.mask.cols - col0;
+                const __half* base = a.mask.data + qtok * a.mask.cols + col0;
+                const int h0 = oct * 8 + 2 * t;
+                if (h0 < a.group) {
+                    mrow0 = base + static_cast<int64_t>(kvh * a.group + h0) * a.mask.head_stride;
+                }
+                if (h0 + 1 < a.group) {
+                    mrow1 = base + static_cast<int64_t>(kvh * a.group + h0 + 1) * a.mask.head_stride;
+                }
+                if (mask_room < kvlen && lane == 0) {
+                    atomicOr(&a.hdr->status, kDevMaskOutOfRange);
+                }
+            }
 
             for (int32_t tile = t_first; tile < t_end; ++tile) {
                 if (!wait_dead) {
@@ -652,10 +689,13 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                         const __half2 pa = u32_as_h2(sa[rr >> 2]), pb = u32_as_h2(sb[rr >> 2]);
                         const __half2 s2a = (rr & 2) ? __high2half2(pa) : __low2half2(pa);
                         const __half2 s2b = (rr & 2) ? __high2half2(pb) : __low2half2(pb);
-                        uint32_t a0, a1, a2, a3;
-                        dequant_k_word(wa[rr], s2a, a0, a2);
-                        dequant_k_word(wb[rr], s2b, a1, a3);
+                        uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
+                        dequant_k_word(wa[rr], s2a, a0, a2, e0, e2);
+                        dequant_k_word(wb[rr], s2b, a1, a3, e1, e3);
                         mma_m16n8k16_f16f32(sacc, a0, a1, a2, a3, qf[rr][0], qf[rr][1]);
+#if PPLB200_DECODE_KRESID
+                        mma_m16n8k16_f16f32(sacc, e0, e1, e2, e3, qf[rr][0], qf[rr][1]);
+#endif
                     }
                 }
 
@@ -664,6 +704,24 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 float s1 = sacc[1] * a.scale_log2;  // token g,   head 2t+1
                 float s2 = sacc[2] * a.scale_log2;  // token g+8, head 2t
                 float s3 = sacc[3] * a.scale_log2;  // token g+8, head 2t+1
+                if constexpr (MASK) {  // additive mask on the scaled scores (exp2 domain: times log2 e)
+                    constexpr float kLog2e = 1.4426950408889634f;
+                    const int64_t p0 = static_cast<int64_t>(tile) * kTileTok + g, p1 = p0 + 8;
+                    const bool in0 = p0 < kvlen && p0 < mask_room, in1 = p1 < kvlen && p1 < mask_room;
+                    if (mrow0) {
+                        if (in0) s0 = fmaf(__half2float(mrow0[p0]), kLog2e, s0);
+                        if (in1) s2 = fmaf(__half2float(mrow0[p1]), kLog2e, s2);
+                    }
+                    if (mrow1) {
+                        if (in0) s1 = fmaf(__half2float(mrow1[p0]), kLog2e, s1);
+                        if (in1) s3 = fmaf(__half2float(mrow1[p1]), kLog2e, s3);
+                    }
+                    // +inf or NaN in a mask would poison the running maximum: such entries count as "masked out"
+                    s0 = s0 < 3.0e38f ? s0 : kNegBig;
+                    s1 = s1 < 3.0e38f ? s1 : kNegBig;
+                    s2 = s2 < 3.0e38f ? s2 : kNegBig;
+                    s3 = s3 < 3.0e38f ? s3 : kNegBig;
+                }
                 if (nvalid < kTileTok) {  // only the last tile of a sequence has rows past its end
                     if (g >= nvalid) {
                         s0 = kNegBig;
@@ -1028,7 +1086,7 @@ static int map_order_kind(const CacheMapOrder& od) {
     return kOrderGeneric;
 }
 
-template <int DH, int ORDER>
+template <int DH, int ORDER, bool MASK>
 static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t grid, cudaStream_t stream) {
     using T = Traits<DH>;
     // the attribute belongs to the (kernel, device) pair: remembered per template instance and device
@@ -1039,7 +1097,7 @@ static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t
     }
     bool& attr_set = attr_set_on[dev_id];
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(decode_splitk_kernel<DH, ORDER>,
+        cudaError_t e = cudaFuncSetAttribute(decode_splitk_kernel<DH, ORDER, MASK>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
         if (e != cudaSuccess) {
             fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(decode_splitk_kernel): %s\n", cudaGetErrorString(e));
@@ -1049,7 +1107,7 @@ static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t
     }
     {
         KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
-        launch_dependent(decode_splitk_kernel<DH, ORDER>, dim3(static_cast<unsigned>(grid)), dim3(kThreads),
+        launch_dependent(decode_splitk_kernel<DH, ORDER, MASK>, dim3(static_cast<unsigned>(grid)), dim3(kThreads),
                          T::kSmemBytes, stream, tm_codes, a);
     }
     return check_launch("decode_splitk_kernel");
@@ -1079,7 +1137,8 @@ template <int DH>
 static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan,
                             const void* query, const void* append_key, const void* append_value,
                             const int64_t* seqstarts, const int64_t* cachestarts, const int64_t* start_pos,
-                            void* cache, void* scale, void* workspace, void* attn_output, cudaStream_t stream) {
+                            void* cache, void* scale, const MaskDev& mask, void* workspace, void* attn_output,
+                            cudaStream_t stream) {
     static_assert(sizeof(PlanHeader) <= 256, "the header must fit in front of the prefix sums");
     uint8_t* ws = static_cast<uint8_t*>(workspace);
     PlanHeader* hdr = reinterpret_cast<PlanHeader*>(ws + plan.off_header);
@@ -1129,6 +1188,7 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.cur_v = static_cast<const __half*>(append_value);
     a.cache = static_cast<int8_t*>(cache);
     a.num_kv_heads = p.num_kv_heads;
+    a.mask = mask;
 
     // never more CTAs than there can be ranges
     int64_t grid = plan.grid;
@@ -1136,10 +1196,14 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     if ((plan.max_ranges + per_cta - 1) / per_cta < grid) {
         grid = (plan.max_ranges + per_cta - 1) / per_cta;
     }
-    switch (map_order_kind(order)) {
-        case kOrderRowLast: rc = launch_main<DH, kOrderRowLast>(tm_codes, a, grid, stream); break;
-        case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst>(tm_codes, a, grid, stream); break;
-        default: rc = launch_main<DH, kOrderGeneric>(tm_codes, a, grid, stream); break;
+    if (a.mask.data != nullptr) {  // the mask path need not be the fastest: one instance, run-time coordinate order
+        rc = launch_main<DH, kOrderGeneric, true>(tm_codes, a, grid, stream);
+    } else {
+        switch (map_order_kind(order)) {
+            case kOrderRowLast: rc = launch_main<DH, kOrderRowLast, false>(tm_codes, a, grid, stream); break;
+            case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst, false>(tm_codes, a, grid, stream); break;
+            default: rc = launch_main<DH, kOrderGeneric, false>(tm_codes, a, grid, stream); break;
+        }
     }
     if (rc != PPLB200_SUCCESS) {
         return rc;
@@ -1158,8 +1222,8 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
 
 int launch_decode(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan, const void* query,
                   const void* append_key, const void* append_value, const int64_t* seqstarts,
-                  const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale, void* workspace,
-                  void* attn_output, cudaStream_t stream) {
+                  const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale, const MaskDev& mask,
+                  void* workspace, void* attn_output, cudaStream_t stream) {
     if (p.decoding_batches <= 0) {
         return PPLB200_SUCCESS;
     }
@@ -1168,11 +1232,11 @@ int launch_decode(const pplb200_attn_params& p, const CacheGeom& geom, const Dec
     }
     if (p.head_dim == 128) {
         return launch_decode_dh<128>(p, geom, plan, query, append_key, append_value, seqstarts, cachestarts, start_pos,
-                                     cache, scale, workspace, attn_output, stream);
+                                     cache, scale, mask, workspace, attn_output, stream);
     }
     if (p.head_dim == 64) {
         return launch_decode_dh<64>(p, geom, plan, query, append_key, append_value, seqstarts, cachestarts, start_pos,
-                                    cache, scale, workspace, attn_output, stream);
+                                    cache, scale, mask, workspace, attn_output, stream);
     }
     return PPLB200_UNSUPPORTED;
 }

@@ -10,6 +10,7 @@
 namespace pplb200 {
 
 struct CacheGeom;
+struct MaskDev;
 
 constexpr int kMaxDevices = 64;  // devices per process that per-device launch state is kept for
 
@@ -95,8 +96,8 @@ int make_decode_plan(const pplb200_attn_params& p, int sm_count, DecodePlan* pla
 // null: the cache already holds that token.
 int launch_decode(const pplb200_attn_params& p, const CacheGeom& geom, const DecodePlan& plan, const void* query,
                   const void* append_key, const void* append_value, const int64_t* seqstarts,
-                  const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale, void* workspace,
-                  void* attn_output, cudaStream_t stream);
+                  const int64_t* cachestarts, const int64_t* start_pos, void* cache, void* scale, const MaskDev& mask,
+                  void* workspace, void* attn_output, cudaStream_t stream);
 
 // ---- prefill (causal, tcgen05) -------------------------------------------------------------------
 struct PrefillPlan {
@@ -109,14 +110,14 @@ int make_prefill_plan(const pplb200_attn_params& p, PrefillPlan* plan);
 
 int launch_prefill(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan, const void* query,
                    const void* cur_k, const void* cur_v, const int64_t* seqstarts, const int64_t* cachestarts,
-                   const int64_t* start_pos, const void* cache, const void* scale, void* workspace_region,
-                   uint32_t* status_word, void* attn_output, cudaStream_t stream);
+                   const int64_t* start_pos, const void* cache, const void* scale, const MaskDev& mask,
+                   void* workspace_region, uint32_t* status_word, void* attn_output, cudaStream_t stream);
 
 // The un-cached attention operator through the prefill kernel (K/V from their own tensors).
 int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int64_t batch, int64_t max_seqlen,
                int64_t max_kvlen, int64_t total_q, int64_t total_kv, const void* query, const void* key,
-               const void* value, const int64_t* seqstarts, const int64_t* kvstarts, uint32_t* status_word,
-               void* attn_output, cudaStream_t stream);
+               const void* value, const int64_t* seqstarts, const int64_t* kvstarts, const MaskDev& mask,
+               uint32_t* status_word, void* attn_output, cudaStream_t stream);
 
 // Rotary position embedding, alone (append == nullptr) or fused with the cache append.
 uint64_t rope_workspace_bytes(const pplb200_rope_params& p);

@@ -40,6 +40,12 @@
 #ifndef PPLB200_PREFILL_WAIT
 #define PPLB200_PREFILL_WAIT mbar_test_wait
 #endif
+#ifndef PPLB200_PF_EXP16
+#define PPLB200_PF_EXP16 0
+#endif
+#ifndef PPLB200_PF_FMA2
+#define PPLB200_PF_FMA2 0
+#endif
 
 namespace pplb200 {
 
@@ -92,6 +98,8 @@ struct PrefillArgs {
     int32_t is_causal;  // query row i sees kv positions <= (kvlen - seqlen) + i; otherwise all of them
     int64_t max_kvlen;
     float scale_log2;
+    MaskDev mask;      // the optional attn_mask input (kernel instances with MASK only)
+    float mask_scale;  // sqrt(head_dim): a mask value in units of the raw (unscaled) scores
 };
 
 // One unit of work: a 128-row query tile of one head, as decoded by the producer warp and handed to the
@@ -100,6 +108,7 @@ struct Tile {
     int head, kvh, n_kv, rows_valid;
     int64_t q_row0, kv_row0, kvlen;
     int64_t first_row_last;  // last kv position visible to row 0 of the tile (negative: rows that see nothing)
+    int64_t mask_col0;       // attn_mask column of kv position 0 of the tile's kv range (MASK instances)
 };
 
 struct Barriers {
@@ -210,6 +219,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// two exponentials in one special-function operation: fp16 arguments, fp16 results
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
+    uint32_t y;
+    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -319,7 +334,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
     return wait_or_abort_slow(bar, parity, abort_flag, status, code);
 }
 
-template <int DH>
+template <int DH, bool MASK>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
@@ -444,6 +459,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         // last kv position visible to row 0 of the tile, and whether rows of this tile see nothing at all
         // (causal, more query rows than kv rows)
         ti.first_row_last = a.is_causal ? hist + i0 : kvlen - 1;
+        ti.mask_col0 = 0;
+        if constexpr (MASK) {
+            // mask columns count kv positions of the sequence; with K/V taken from this call's rows (kv_mode 0)
+            // kv row 0 is the sequence's first NEW token, position start_pos[b]
+            ti.mask_col0 = a.mask.kvstarts[b] + (a.kv_mode == 0 ? a.start_pos[b] : 0);
+        }
         return true;
     };
     const int total_tiles = a.total_tiles;
@@ -743,6 +764,27 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 // row's horizon or past the end of the kv range need the mask (uniform for the CTA).  Unless the
                 // tile has rows that see nothing at all (handled below), column 0 of tile 0 is visible to every
                 // row, so m_ref is a real score from the first tile on.
+                if constexpr (MASK) {
+                    // additive mask, one fp16 per (query row, kv position); entries that the mask tensor does not
+                    // hold read as 0 and are reported; +inf / NaN entries count as masked out
+                    const int64_t col = ti.mask_col0 + static_cast<int64_t>(j) * kBlockN;
+                    const int64_t room = a.mask.cols - col;
+                    const int64_t vis = kvlen - static_cast<int64_t>(j) * kBlockN;
+                    if (room < vis && room < kBlockN && r == 0) {
+                        atomicOr(a.status, kDevMaskOutOfRange);
+                    }
+                    if (r < rows_valid) {
+                        const __half* mrow = a.mask.data + static_cast<int64_t>(head) * a.mask.head_stride +
+                                             (q_row0 + r) * a.mask.cols + col;
+#pragma unroll
+                        for (int e = 0; e < kBlockN; ++e) {
+                            if (e < room && e < vis) {
+                                const float t = fmaf(__half2float(mrow[e]), a.mask_scale, sv[e]);
+                                sv[e] = t < 3.0e38f ? t : kNegBig;
+                            }
+                        }
+                    }
+                }
                 const int64_t tile_hi = static_cast<int64_t>(j + 1) * kBlockN - 1;
                 if (tile_hi > first_row_last || tile_hi >= kvlen) {
                     int64_t lim64 = (a.is_causal ? first_row_last + r : kvlen - 1);
@@ -798,9 +840,19 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     uint32_t pk[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
-                        const float p0 = ex2_approx(fmaf(sv[32 * q + 2 * e], sc, neg_m));
-                        const float p1 = ex2_approx(fmaf(sv[32 * q + 2 * e + 1], sc, neg_m));
-                        pk[e] = h2_as_u32(__floats2half2_rn(p0, p1));
+#if PPLB200_PF_FMA2
+                        const float2 x = __ffma2_rn(make_float2(sv[32 * q + 2 * e], sv[32 * q + 2 * e + 1]),
+                                                    make_float2(sc, sc), make_float2(neg_m, neg_m));
+                        const float x0 = x.x, x1 = x.y;
+#else
+                        const float x0 = fmaf(sv[32 * q + 2 * e], sc, neg_m);
+                        const float x1 = fmaf(sv[32 * q + 2 * e + 1], sc, neg_m);
+#endif
+#if PPLB200_PF_EXP16
+                        pk[e] = ex2_f16x2(h2_as_u32(__floats2half2_rn(x0, x1)));
+#else
+                        pk[e] = h2_as_u32(__floats2half2_rn(ex2_approx(x0), ex2_approx(x1)));
+#endif
                         add_half2_to_float(l_sum, pk[e]);
                     }
                     tmem_st16(t_pb + 16 * q, pk);
@@ -999,15 +1051,19 @@ static int launch_attention_core(const void* query, const void* k_src, const voi
     a.group = num_heads / num_kv_heads;
     a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
 
+    a.mask_scale = sqrtf(static_cast<float>(DH));
+    const bool masked = a.mask.data != nullptr;
+    auto kernel = masked ? prefill_tcgen05_kernel<DH, true> : prefill_tcgen05_kernel<DH, false>;
+
     // the attribute belongs to the (kernel, device) pair: remembered per template instance and device
-    static bool attr_set_on[kMaxDevices] = {};
+    static bool attr_set_on[2][kMaxDevices] = {};
     int dev_id = 0;
     if (cudaGetDevice(&dev_id) != cudaSuccess || dev_id < 0 || dev_id >= kMaxDevices) {
         return PPLB200_DEVICE_RUNTIME_ERROR;
     }
-    bool& attr_set = attr_set_on[dev_id];
+    bool& attr_set = attr_set_on[masked ? 1 : 0][dev_id];
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_tcgen05_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              T::kSmemBytes);
         if (e != cudaSuccess) {
             fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(prefill_tcgen05_kernel): %s\n", cudaGetErrorString(e));
@@ -1035,7 +1091,7 @@ static int launch_attention_core(const void* query, const void* k_src, const voi
     const dim3 grid(static_cast<unsigned>(tiles < resident ? tiles : resident));
     {
         KernelTimer timer(PPLB200_KERNEL_PREFILL, stream);
-        prefill_tcgen05_kernel<DH><<<grid, kThreads, T::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
+        kernel<<<grid, kThreads, T::kSmemBytes, stream>>>(tm_q, tm_k, tm_v, a);
     }
     return check_launch("prefill_tcgen05_kernel");
 }
@@ -1044,7 +1100,8 @@ template <int DH>
 static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan,
                              const void* query, const void* cur_k, const void* cur_v, const int64_t* seqstarts,
                              const int64_t* cachestarts, const int64_t* start_pos, const void* cache, const void* scale,
-                             void* region, uint32_t* status, void* attn_output, cudaStream_t stream) {
+                             const MaskDev& mask, void* region, uint32_t* status, void* attn_output,
+                             cudaStream_t stream) {
     const void* k_src = cur_k;
     const void* v_src = cur_v;
     int64_t kv_rows = p.total_tokens;
@@ -1092,6 +1149,7 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
     a.prefill_batches = static_cast<int32_t>(plan.prefill_batches);
     a.kv_mode = p.enable_cache_prefill ? 1 : 0;
     a.is_causal = p.is_causal ? 1 : 0;  // the attribute is passed through, as the reference passes it
+    a.mask = mask;
     return launch_attention_core<DH>(query, k_src, v_src, p.total_tokens, kv_rows, p.num_heads, p.num_kv_heads,
                                      plan.q_tiles_per_seq, a, stream);
 }
@@ -1099,8 +1157,8 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
 // The un-cached operator: every sequence of the batch through the same kernel, K/V from their own tensors.
 int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int64_t batch, int64_t max_seqlen,
                int64_t max_kvlen, int64_t total_q, int64_t total_kv, const void* query, const void* key,
-               const void* value, const int64_t* seqstarts, const int64_t* kvstarts, uint32_t* status_word,
-               void* attn_output, cudaStream_t stream) {
+               const void* value, const int64_t* seqstarts, const int64_t* kvstarts, const MaskDev& mask,
+               uint32_t* status_word, void* attn_output, cudaStream_t stream) {
     if (batch <= 0 || max_seqlen <= 0 || total_q <= 0) {
         return PPLB200_SUCCESS;
     }
@@ -1117,6 +1175,7 @@ int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int
     a.prefill_batches = static_cast<int32_t>(batch);
     a.kv_mode = 2;
     a.is_causal = is_causal ? 1 : 0;
+    a.mask = mask;
     const int64_t q_tiles = (max_seqlen + kBlockM - 1) / kBlockM;
     const int64_t kv_rows = total_kv > 0 ? total_kv : 1;  // a tensor map needs a non-empty extent
     if (head_dim == 128) {
@@ -1130,18 +1189,18 @@ int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int
 
 int launch_prefill(const pplb200_attn_params& p, const CacheGeom& geom, const PrefillPlan& plan, const void* query,
                    const void* cur_k, const void* cur_v, const int64_t* seqstarts, const int64_t* cachestarts,
-                   const int64_t* start_pos, const void* cache, const void* scale, void* workspace_region,
-                   uint32_t* status_word, void* attn_output, cudaStream_t stream) {
+                   const int64_t* start_pos, const void* cache, const void* scale, const MaskDev& mask,
+                   void* workspace_region, uint32_t* status_word, void* attn_output, cudaStream_t stream) {
     if (plan.prefill_batches <= 0 || plan.q_tiles_per_seq <= 0) {
         return PPLB200_SUCCESS;
     }
     if (p.head_dim == 128) {
         return launch_prefill_dh<128>(p, geom, plan, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache,
-                                      scale, workspace_region, status_word, attn_output, stream);
+                                      scale, mask, workspace_region, status_word, attn_output, stream);
     }
     if (p.head_dim == 64) {
         return launch_prefill_dh<64>(p, geom, plan, query, cur_k, cur_v, seqstarts, cachestarts, start_pos, cache, scale,
-                                     workspace_region, status_word, attn_output, stream);
+                                     mask, workspace_region, status_word, attn_output, stream);
     }
     return PPLB200_UNSUPPORTED;
 }

@@ -87,4 +87,16 @@ int pplb200_mhca_forward_noalloc(const pplb200_attn_params* p, const void* query
                                 cache, scale, scratch, kStaticScratchBytes, attn_output, stream);
 }
 
+int pplb200_static_scratch_status(void* stream, uint32_t* status) {
+    if (!status) {
+        return PPLB200_NOT_FOUND;
+    }
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != PPLB200_SUCCESS) {
+        return rc;
+    }
+    return pplb200_mhca_device_status(scratch, stream, status);
+}
+
 }  // extern "C"

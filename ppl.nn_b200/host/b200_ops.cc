@@ -57,6 +57,37 @@ RetCode RequireOnDevice(const TensorImpl* t, const Device* dev) {
     return RC_SUCCESS;
 }
 
+// The optional attn_mask input: shape and pointer are handed down as the reference hands them down
+// (multi_head_cache_attention_kernel.cc:105-110,179-180); a tensor without elements counts as absent.
+// Fills `m` (data stays null without a mask); the tensor must be fp16 and live on the device.
+RetCode MaskFromTensor(TensorImpl* attn_mask, const Device* dev, int32_t num_heads, int64_t tokens,
+                       pplb200_attn_mask* m) {
+    memset(m, 0, sizeof(*m));
+    if (!attn_mask || attn_mask->GetShape()->CalcElementsExcludingPadding() == 0) {
+        return RC_SUCCESS;
+    }
+    const TensorShape* shape = attn_mask->GetShape();
+    if (shape->GetDataType() != DATATYPE_FLOAT16) {
+        LOG(ERROR) << "attn_mask must be fp16";
+        return RC_UNSUPPORTED;
+    }
+    if (shape->GetDimCount() != 2 && shape->GetDimCount() != 3) {
+        LOG(ERROR) << "attn_mask must be a 2d or 3d tensor";
+        return RC_INVALID_VALUE;
+    }
+    const RetCode rc = RequireOnDevice(attn_mask, dev);
+    if (rc != RC_SUCCESS) {
+        return rc;
+    }
+    m->data = attn_mask->GetBufferPtr();
+    m->ndim = static_cast<int32_t>(shape->GetDimCount());
+    for (uint32_t i = 0; i < shape->GetDimCount(); ++i) {
+        m->dims[i] = shape->GetDim(i);
+    }
+    return FromStatus(pplb200_attn_mask_check(m, num_heads, tokens));
+}
+
+
 // The kernels index [tokens, heads, head_dim] tensors with the attribute values, so a tensor of another
 // shape would be read out of bounds; the reference leaves this to its kernel library.
 RetCode RequireTokenTensor(const TensorImpl* t, int64_t tokens, int64_t heads, int64_t head_dim) {
@@ -148,9 +179,11 @@ RetCode DynamicBatchingMultiHeadCacheAttentionKernel::DoExecute(KernelExecContex
         LOG(ERROR) << "currently only support quantized cache but scale not found";
         return RC_UNSUPPORTED;
     }
-    if (attn_mask && attn_mask->GetShape()->CalcElementsExcludingPadding() > 0) {
-        LOG(ERROR) << "attn_mask is not supported";  // an empty mask counts as absent
-        return RC_UNSUPPORTED;
+    pplb200_attn_mask mask;
+    if ((rc = MaskFromTensor(attn_mask, GetCudaDevice(), param_->num_heads,
+                             query->GetShape()->GetDimCount() > 0 ? query->GetShape()->GetDim(0) : 0, &mask)) !=
+        RC_SUCCESS) {
+        return rc;
     }
     if (query->GetShape()->GetDataType() != DATATYPE_FLOAT16) {
         LOG(ERROR) << "currently only support fp16";
@@ -240,11 +273,11 @@ RetCode DynamicBatchingMultiHeadCacheAttentionKernel::DoExecute(KernelExecContex
     }
     Destructor tmp_guard([this, &tmp]() { GetCudaDevice()->FreeTmpBuffer(&tmp); });
 
-    return FromStatus(pplb200_mhca_forward(
+    return FromStatus(pplb200_mhca_forward_masked(
         &p, query->GetBufferPtr(), current_key->GetBufferPtr(), current_value->GetBufferPtr(),
         seqstarts->GetBufferPtr<int64_t>(), kvstarts->GetBufferPtr<int64_t>(), cachestarts->GetBufferPtr<int64_t>(),
-        start_pos->GetBufferPtr<int64_t>(), cache->GetBufferPtr(), scale->GetBufferPtr(), tmp.addr, workspace_bytes,
-        attn_output->GetBufferPtr(), GetStream()));
+        start_pos->GetBufferPtr<int64_t>(), cache->GetBufferPtr(), scale->GetBufferPtr(), &mask, tmp.addr,
+        workspace_bytes, attn_output->GetBufferPtr(), GetStream()));
 }
 
 // =================================================================================================
@@ -294,9 +327,11 @@ RetCode DynamicBatchingMultiHeadAttentionKernel::DoExecute(KernelExecContext* ct
         LOG(ERROR) << "currently only support is_alibi == false";
         return RC_UNSUPPORTED;
     }
-    if (attn_mask && attn_mask->GetShape()->CalcElementsExcludingPadding() > 0) {
-        LOG(ERROR) << "attn_mask is not supported";  // an empty mask counts as absent
-        return RC_UNSUPPORTED;
+    pplb200_attn_mask mask;
+    if ((rc = MaskFromTensor(attn_mask, GetCudaDevice(), param_->num_heads,
+                             query->GetShape()->GetDimCount() > 0 ? query->GetShape()->GetDim(0) : 0, &mask)) !=
+        RC_SUCCESS) {
+        return rc;
     }
     if (query->GetShape()->GetDataType() != DATATYPE_FLOAT16) {
         LOG(ERROR) << "currently only support fp16";
@@ -352,9 +387,10 @@ RetCode DynamicBatchingMultiHeadAttentionKernel::DoExecute(KernelExecContext* ct
     }
     Destructor tmp_guard([this, &tmp]() { GetCudaDevice()->FreeTmpBuffer(&tmp); });
 
-    return FromStatus(pplb200_mha_forward(&p, query->GetBufferPtr(), key->GetBufferPtr(), value->GetBufferPtr(),
-                                          seqstarts->GetBufferPtr<int64_t>(), kvstarts->GetBufferPtr<int64_t>(), tmp.addr,
-                                          workspace_bytes, attn_output->GetBufferPtr(), GetStream()));
+    return FromStatus(pplb200_mha_forward_masked(&p, query->GetBufferPtr(), key->GetBufferPtr(), value->GetBufferPtr(),
+                                                 seqstarts->GetBufferPtr<int64_t>(), kvstarts->GetBufferPtr<int64_t>(),
+                                                 &mask, tmp.addr, workspace_bytes, attn_output->GetBufferPtr(),
+                                                 GetStream()));
 }
 
 // =================================================================================================

@@ -113,6 +113,19 @@ def _require_cuda(**tensors):
             raise OpError("RC_INVALID_VALUE", f"{name} must be contiguous")
 
 
+def _mask_arg(attn_mask):
+    """The optional attn_mask input as the C ABI wants it; a tensor of zero elements is "absent", as in the
+    reference (multi_head_cache_attention_kernel.cc:107)."""
+    if attn_mask is None or attn_mask.numel() == 0:
+        return None
+    _require_cuda(attn_mask=attn_mask)
+    if attn_mask.dtype != torch.float16:
+        raise OpError("RC_UNSUPPORTED", "attn_mask must be fp16")
+    if attn_mask.dim() not in (2, 3):
+        raise OpError("RC_INVALID_VALUE", "attn_mask must be [T, C] or [num_heads, T, C]")
+    return capi.AttnMask.of(attn_mask.data_ptr(), tuple(attn_mask.shape))
+
+
 def _max_tokens(cache: torch.Tensor, layout: int) -> int:
     if layout == 0:
         return cache.shape[0]
@@ -176,8 +189,7 @@ class MultiHeadCacheAttention(_Base):
             raise OpError("RC_UNSUPPORTED", "currently only support is_alibi == false")
         if scale is None or scale.numel() == 0:
             raise OpError("RC_UNSUPPORTED", "currently only support qunatized cache but scale not found")
-        if attn_mask is not None and attn_mask.numel() > 0:
-            raise OpError("RC_UNSUPPORTED", "attn_mask is not supported")
+        mask = _mask_arg(attn_mask)
         _require_cuda(scale=scale)
         stride_b = 0
         if a.cache_mode == 1:
@@ -192,9 +204,14 @@ class MultiHeadCacheAttention(_Base):
         if attn_output is None:
             attn_output = torch.empty_like(query)
         ws = self.workspace_for(p, query.device)
-        rc = self.lib.mhca_forward(p, _ptr(query), _ptr(current_key), _ptr(current_value), _ptr(seqstarts),
-                                   _ptr(kvstarts), _ptr(cachestarts), _ptr(start_pos), _ptr(cache), _ptr(scale),
-                                   _ptr(ws), ws.numel(), _ptr(attn_output), _stream())
+        if mask is None:
+            rc = self.lib.mhca_forward(p, _ptr(query), _ptr(current_key), _ptr(current_value), _ptr(seqstarts),
+                                       _ptr(kvstarts), _ptr(cachestarts), _ptr(start_pos), _ptr(cache), _ptr(scale),
+                                       _ptr(ws), ws.numel(), _ptr(attn_output), _stream())
+        else:
+            rc = self.lib.mhca_forward_masked(p, _ptr(query), _ptr(current_key), _ptr(current_value), _ptr(seqstarts),
+                                              _ptr(kvstarts), _ptr(cachestarts), _ptr(start_pos), _ptr(cache),
+                                              _ptr(scale), mask, _ptr(ws), ws.numel(), _ptr(attn_output), _stream())
         self._raise("pplb200_mhca_forward", rc)
         self._last_params = p
         return attn_output
@@ -278,8 +295,7 @@ class MultiHeadAttention(_Base):
         _require_cuda(query=query, key=key, value=value, seqstarts=seqstarts, kvstarts=kvstarts)
         if a.is_alibi:
             raise OpError("RC_UNSUPPORTED", "currently only support is_alibi == false")
-        if attn_mask is not None and attn_mask.numel() > 0:
-            raise OpError("RC_UNSUPPORTED", "attn_mask is not supported")
+        mask = _mask_arg(attn_mask)
         p = capi.MhaParams()
         p.num_heads, p.num_kv_heads, p.head_dim, p.is_causal = a.num_heads, a.num_kv_heads, a.head_dim, int(a.is_causal)
         p.batch = seqstarts.shape[0] - 1
@@ -290,8 +306,8 @@ class MultiHeadAttention(_Base):
             attn_output = torch.empty_like(query)
         if self._workspace is None or self._workspace.device != query.device:
             self._workspace = torch.empty(256, dtype=torch.uint8, device=query.device)
-        rc = self.lib.mha_forward(p, _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts), _ptr(kvstarts),
-                                  _ptr(self._workspace), self._workspace.numel(), _ptr(attn_output), _stream())
+        rc = self.lib.mha_forward_masked(p, _ptr(query), _ptr(key), _ptr(value), _ptr(seqstarts), _ptr(kvstarts), mask,
+                                         _ptr(self._workspace), self._workspace.numel(), _ptr(attn_output), _stream())
         self._raise("pplb200_mha_forward", rc)
         return attn_output
 

@@ -131,3 +131,39 @@ def test_host_scalars_on_the_device_are_read_with_a_sync(orc, env):
     err = np.abs(out.cpu().numpy().astype(np.float32) - want.astype(np.float32))
     assert err.max() <= 2e-3 and err.mean() <= 1e-3
     op.close()
+
+
+def test_attn_mask_is_input_12_of_the_host_operator(orc, env):
+    """The optional mask travels through the host kernel as the reference forwards it
+    (multi_head_cache_attention_kernel.cc:39,105-110): 13th input, fp16, [T, C]."""
+    import torch
+    from ppl_nn_b200 import workloads
+    host, eng, dev = env
+    assert eng.configure("cache_prefill", 0) == "RC_SUCCESS"
+    Hq, Hkv, Dh = 8, 2, 128
+    idx = workloads.make_index([9, 333, 64], [40])
+    T, KV = idx.total_tokens, int(idx.kvstarts[-1])
+    rng = np.random.default_rng(8)
+    q = rng.standard_normal((T, Hq, Dh), dtype=np.float32).astype(np.float16)
+    ck = rng.standard_normal((T, Hkv, Dh), dtype=np.float32).astype(np.float16)
+    cv = rng.standard_normal((T, Hkv, Dh), dtype=np.float32).astype(np.float16)
+    cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, Hkv, Dh)
+    o_cache = rng.integers(-127, 128, size=cshape, dtype=np.int8)
+    o_scale = rng.uniform(0.002, 0.012, size=sshape).astype(np.float16)
+    cache, scale = _t(o_cache, dev), _t(o_scale, dev)
+    mask = (rng.standard_normal((T, (KV + 7) // 8 * 8)) * 0.5).astype(np.float16)
+    mask[rng.random(mask.shape) < 0.2] = -np.inf
+    want = orc.mhca(orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=idx.batch, decoding_batches=3,
+                             max_tokens=idx.max_tokens), q, ck, cv, idx.seqstarts, idx.cachestarts, idx.start_pos,
+                    o_cache, o_scale, kvstarts=idx.kvstarts, attn_mask=mask)
+    op = host.Op(eng, "MultiHeadCacheAttention", dict(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, num_layer=1,
+                                                      layer_idx=0, quant_bit=8))
+    out = torch.zeros((T, Hq, Dh), dtype=torch.float16, device=dev)
+    op.run([_t(q, dev), _t(ck, dev), _t(cv, dev), _t(idx.seqstarts, dev), _t(idx.kvstarts, dev),
+            _t(idx.cachestarts, dev), _t(idx.start_pos, dev), 3, idx.max_seqlen, idx.max_kvlen, cache, scale,
+            _t(mask, dev)], [out])
+    eng.synchronize()
+    np.testing.assert_array_equal(cache.cpu().numpy(), o_cache)
+    err = np.abs(out.cpu().numpy().astype(np.float32) - want.astype(np.float32))
+    assert err.max() <= 2e-3 and err.mean() <= 1e-3, (err.max(), err.mean())
+    op.close()

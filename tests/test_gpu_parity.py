@@ -27,7 +27,7 @@ def _t(a, dev):
 
 
 def run_case(orc, dev, hc, *, layout=0, num_layer=1, layer_idx=0, split_k=1, cache_prefill=False,
-             check_attention=True):
+             check_attention=True, attn_mask=None):
     """History append + one MultiHeadCacheAttention call on both sides; returns the error stats."""
     import torch
     from ppl_nn_b200 import ops, workloads
@@ -46,7 +46,8 @@ def run_case(orc, dev, hc, *, layout=0, num_layer=1, layer_idx=0, split_k=1, cac
     orc.kv_append(orc.desc(decoding_batches=0, **kw), hc.hist_key, hc.hist_value, hidx.seqstarts, hidx.cachestarts,
                   hidx.start_pos, o_cache, o_scale)
     want = orc.mhca(orc.desc(decoding_batches=idx.decoding_batches, **kw), hc.query, hc.current_key,
-                    hc.current_value, idx.seqstarts, idx.cachestarts, idx.start_pos, o_cache, o_scale)
+                    hc.current_value, idx.seqstarts, idx.cachestarts, idx.start_pos, o_cache, o_scale,
+                    kvstarts=idx.kvstarts, attn_mask=attn_mask)
     # ---- CUDA ----
     cache = torch.zeros(cshape, dtype=torch.int8, device=dev)
     scale = torch.zeros(sshape, dtype=torch.float16, device=dev)
@@ -65,7 +66,8 @@ def run_case(orc, dev, hc, *, layout=0, num_layer=1, layer_idx=0, split_k=1, cac
         ops.EngineConfig(enable_cache_prefill=cache_prefill, specify_decoding_attn_split_k=split_k))
     got = op.forward(_t(hc.query, dev), _t(hc.current_key, dev), _t(hc.current_value, dev), _t(idx.seqstarts, dev),
                      _t(idx.kvstarts, dev), _t(idx.cachestarts, dev), _t(idx.start_pos, dev), idx.decoding_batches,
-                     idx.max_seqlen, idx.max_kvlen, cache, scale)
+                     idx.max_seqlen, idx.max_kvlen, cache, scale,
+                     attn_mask=None if attn_mask is None else _t(attn_mask, dev))
     assert op.device_status() == 0
     np.testing.assert_array_equal(cache.cpu().numpy(), o_cache, err_msg="INT8 cache codes differ")
     np.testing.assert_array_equal(scale.cpu().numpy().view(np.uint16), o_scale.view(np.uint16),
@@ -330,6 +332,57 @@ def test_non_causal_prefill_in_the_cached_operator(orc, torch_dev, pkg, cache_pr
     idx = workloads.make_index([40, 300], [100, 64, 200], prefill_hist=[0, 77, 0] if cache_prefill else None)
     hc = _case_with_index(hc, idx, spec)
     run_case(orc, torch_dev, hc, cache_prefill=cache_prefill)
+
+
+def _random_mask(rng, idx, heads=None, cols_extra=0):
+    """Additive fp16 mask [T, C] (or [heads, T, C]): small biases, about a fifth of the entries -inf, one query
+    row with every position removed, columns padded up to a multiple of 8 (plus `cols_extra`)."""
+    T, KV = idx.total_tokens, int(idx.kvstarts[-1])
+    C = (KV + 7) // 8 * 8 + cols_extra
+    shape = (T, C) if heads is None else (heads, T, C)
+    m = (rng.standard_normal(shape) * 0.5).astype(np.float16)
+    m[rng.random(shape) < 0.2] = -np.inf
+    b = idx.batch - 1  # the first query row of the last sequence sees nothing at all
+    m[..., int(idx.seqstarts[b]), int(idx.kvstarts[b]):int(idx.kvstarts[b + 1])] = -np.inf
+    return m
+
+
+@pytest.mark.parametrize("per_head", [False, True])
+@pytest.mark.parametrize("cache_prefill", [False, True])
+def test_attn_mask_on_a_mixed_batch(orc, torch_dev, pkg, per_head, cache_prefill):
+    """The optional attn_mask input: additive fp16, [T, C] or [num_heads, T, C], element
+    [.., seqstarts[b] + i, kvstarts[b] + j]; decode and prefill sequences in one call, split-k forced on a long
+    decode sequence, prefill with and without the INT8 cache (history included)."""
+    from ppl_nn_b200 import workloads
+    spec = _spec(num_heads=8, num_kv_heads=2, head_dim=128, n_decode=3, kv_dist="list", kv_list=(40, 700, 17),
+                 n_prefill=3, seed=35)
+    hc = workloads.host_case(spec)
+    idx = workloads.make_index([40, 700, 17], [100, 64, 150], prefill_hist=[0, 90, 31] if cache_prefill else None)
+    hc = _case_with_index(hc, idx, spec)
+    mask = _random_mask(np.random.default_rng(36), idx, heads=8 if per_head else None, cols_extra=16 if per_head else 0)
+    run_case(orc, torch_dev, hc, cache_prefill=cache_prefill, attn_mask=mask, split_k=2)
+
+
+def test_attn_mask_head_dim_64_and_a_narrow_mask_is_reported(orc, torch_dev, pkg):
+    import torch
+    from ppl_nn_b200 import ops, workloads
+    spec = _spec(num_heads=8, num_kv_heads=8, head_dim=64, n_decode=4, kv_dist="list", kv_list=(17, 64, 130, 255),
+                 n_prefill=1, seed=37)
+    hc = workloads.host_case(spec)
+    idx = workloads.make_index([17, 64, 130, 255], [70])
+    hc = _case_with_index(hc, idx, spec)
+    mask = _random_mask(np.random.default_rng(38), idx)
+    err, op = run_case(orc, torch_dev, hc, attn_mask=mask)
+    # a mask with too few columns for kvstarts: nothing is read past its rows' ends, and the status word says so
+    dev = torch_dev
+    narrow = np.ascontiguousarray(mask[:, :256])
+    cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, 8, 64)
+    out = op.forward(_t(hc.query, dev), _t(hc.current_key, dev), _t(hc.current_value, dev), _t(idx.seqstarts, dev),
+                     _t(idx.kvstarts, dev), _t(idx.cachestarts, dev), _t(idx.start_pos, dev), idx.decoding_batches,
+                     idx.max_seqlen, idx.max_kvlen, torch.zeros(cshape, dtype=torch.int8, device=dev),
+                     torch.zeros(sshape, dtype=torch.float16, device=dev), attn_mask=_t(narrow, dev))
+    assert op.device_status() & 16
+    assert bool(torch.isfinite(out.float()).all())
 
 
 def test_smoke_entry_point(torch_dev):

@@ -96,7 +96,7 @@ def test_engine_knobs(engine):
 
 # ---- kernel guards that need no GPU ----------------------------------------------------------------
 def _mhca_inputs(host, *, T=4, B=4, Hq=8, Hkv=2, Dh=128, L=2, maxt=64, fake=4096, drop_after=None, scale=True,
-                 attn_mask=None, cachestarts_2d=False, q_dtype=np.float16):
+                 attn_mask=None, mask_dtype=np.float16, cachestarts_2d=False, q_dtype=np.float16):
     """HostTensor structs with fake device pointers: nothing below dereferences them on the paths tested."""
     def dev(shape, dtype):
         t, _ = host.describe(np.zeros(shape, dtype=dtype))
@@ -117,7 +117,7 @@ def _mhca_inputs(host, *, T=4, B=4, Hq=8, Hkv=2, Dh=128, L=2, maxt=64, fake=4096
     elif scale is None:
         ins.append(host.describe(None)[0])
     if attn_mask is not None:
-        ins.append(dev(attn_mask, np.float16))
+        ins.append(dev(attn_mask, mask_dtype))
     if drop_after is not None:
         ins = ins[:drop_after]
     out = dev((T, Hq, Dh), np.float16)
@@ -146,7 +146,11 @@ def test_mhca_missing_output(host, engine):
     (dict(is_alibi=1), {}, "RC_UNSUPPORTED"),
     ({}, dict(scale=None), "RC_UNSUPPORTED"),
     ({}, dict(scale="empty"), "RC_UNSUPPORTED"),
-    ({}, dict(attn_mask=(4, 4)), "RC_UNSUPPORTED"),
+    ({}, dict(attn_mask=(4, 8), mask_dtype=np.float32), "RC_UNSUPPORTED"),  # the mask is fp16
+    ({}, dict(attn_mask=(5,)), "RC_INVALID_VALUE"),       # [T, C] or [num_heads, T, C]
+    ({}, dict(attn_mask=(4, 4)), "RC_INVALID_VALUE"),     # C must be a multiple of 8
+    ({}, dict(attn_mask=(2, 8)), "RC_INVALID_VALUE"),     # fewer rows than query tokens
+    ({}, dict(attn_mask=(3, 4, 8)), "RC_INVALID_VALUE"),  # leading dimension is not num_heads
     ({}, dict(q_dtype=np.float32), "RC_UNSUPPORTED"),
     (dict(cache_layout=1), {}, "RC_UNSUPPORTED"),
     (dict(cache_mode=1), {}, "RC_INVALID_VALUE"),        # paged mode with 1-d cachestarts
@@ -195,7 +199,7 @@ def test_mhca_empty_attn_mask_counts_as_absent_and_output_takes_query_shape(host
     if torch.cuda.is_available():
         pytest.skip("this case passes every guard; with a GPU it would launch kernels on the fake pointers")
     op = host.Op(engine, "MultiHeadCacheAttention", MHCA_ATTRS)
-    ins, outs, keep = _mhca_inputs(host, attn_mask=(0,))
+    ins, outs, keep = _mhca_inputs(host, attn_mask=(0,))  # zero elements: absent
     outs[0].ndim = 1
     outs[0].dims[0] = 7  # stale shape: Reshape must overwrite it with query's
     rc, res = op.run_raw(ins, outs)

@@ -72,7 +72,8 @@ def test_required_attributes(host, engine, missing):
     assert e.value.name == "RC_NOT_FOUND"
 
 
-def _fake_inputs(host, *, T=6, Tkv=9, B=2, Hq=8, Hkv=2, Dh=128, drop_after=None, attn_mask=None, q_dtype=np.float16):
+def _fake_inputs(host, *, T=6, Tkv=9, B=2, Hq=8, Hkv=2, Dh=128, drop_after=None, attn_mask=None,
+                 mask_dtype=np.float16, q_dtype=np.float16):
     def dev(shape, dtype):
         t, _ = host.describe(np.zeros(shape, dtype=dtype))
         t.on_host = 0
@@ -84,7 +85,7 @@ def _fake_inputs(host, *, T=6, Tkv=9, B=2, Hq=8, Hkv=2, Dh=128, drop_after=None,
     for k in keep:
         ins.append(host.describe(k)[0])
     if attn_mask is not None:
-        ins.append(dev(attn_mask, np.float16))
+        ins.append(dev(attn_mask, mask_dtype))
     if drop_after is not None:
         ins = ins[:drop_after]
     return ins, [dev((T, Hq, Dh), np.float16)], keep
@@ -97,11 +98,18 @@ def test_missing_required_input(host, engine, n_inputs):
     assert op.run_raw(ins, outs)[0] == "RC_NOT_FOUND"
 
 
-@pytest.mark.parametrize("attrs,kw", [(dict(is_alibi=1), {}), ({}, dict(attn_mask=(6, 9))), ({}, dict(q_dtype=np.float32))])
-def test_guards(host, engine, attrs, kw):
+@pytest.mark.parametrize("attrs,kw,expect", [
+    (dict(is_alibi=1), {}, "RC_UNSUPPORTED"),
+    ({}, dict(q_dtype=np.float32), "RC_UNSUPPORTED"),
+    ({}, dict(attn_mask=(6, 16), mask_dtype=np.float32), "RC_UNSUPPORTED"),  # the mask is fp16
+    ({}, dict(attn_mask=(6, 9)), "RC_INVALID_VALUE"),      # columns must be a multiple of 8
+    ({}, dict(attn_mask=(4, 16)), "RC_INVALID_VALUE"),     # fewer rows than query tokens
+    ({}, dict(attn_mask=(3, 6, 16)), "RC_INVALID_VALUE"),  # leading dimension is not num_heads
+])
+def test_guards(host, engine, attrs, kw, expect):
     op = host.Op(engine, "MultiHeadAttention", {**MHA_ATTRS, **attrs})
     ins, outs, keep = _fake_inputs(host, **kw)
-    assert op.run_raw(ins, outs)[0] == "RC_UNSUPPORTED"
+    assert op.run_raw(ins, outs)[0] == expect
 
 
 def test_host_index_tensor_is_refused(host, engine):
@@ -160,6 +168,79 @@ def test_gpu_matches_oracle(orc, dev, pkg, case, causal):
     assert np.isfinite(got).all()
     err = np.abs(got - want)
     assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS, (err.max(), err.mean())
+
+
+def _mask_for(rng, q_rows, kv_rows, heads=None):
+    C = (kv_rows + 7) // 8 * 8
+    shape = (q_rows, C) if heads is None else (heads, q_rows, C)
+    m = (rng.standard_normal(shape) * 0.5).astype(np.float16)
+    m[rng.random(shape) < 0.2] = -np.inf
+    return m
+
+
+@pytest.mark.parametrize("per_head", [False, True])
+def test_oracle_mask_matches_its_numpy_twin(orc, oracle_mod, per_head):
+    """attn_mask in the C oracle against the numpy restatement: additive, [T, C] or [heads, T, C], element
+    [.., seqstarts[b] + i, kvstarts[b] + j], on top of the causal mask; a fully removed row gives zeros."""
+    rng = np.random.default_rng(17)
+    Hq, Hkv, Dh = 4, 2, 64
+    seqlens, kvlens = [5, 1, 9], [12, 30, 9]
+    q, k, v, ss, ks = _case(rng, seqlens, kvlens, Hq, Hkv, Dh)
+    mask = _mask_for(rng, sum(seqlens), sum(kvlens), Hq if per_head else None)
+    mask[..., 3, 0:12] = -np.inf  # query row 3 (sequence 0) sees nothing
+    for causal in (True, False):
+        d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=3, is_causal=int(causal))
+        got = orc.mha(d, q, k, v, ss, ks, attn_mask=mask).astype(np.float32)
+        want = oracle_mod.np_mha(q, k, v, ss, ks, Hkv, causal, attn_mask=mask).astype(np.float32)
+        assert np.isfinite(got).all() and not got[3].any()
+        assert np.abs(got - want).max() <= 1e-3
+        assert np.abs(got - orc.mha(d, q, k, v, ss, ks).astype(np.float32)).max() > 1e-2  # the mask does something
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("per_head", [False, True])
+@pytest.mark.parametrize("causal", [True, False])
+def test_gpu_attn_mask_matches_oracle(orc, dev, pkg, causal, per_head):
+    import torch
+    from ppl_nn_b200 import ops
+    Hq, Hkv, Dh = 8, 2, 128
+    seqlens, kvlens = [130, 7, 257, 1], [130, 40, 300, 77]
+    rng = np.random.default_rng(23)
+    q, k, v, ss, ks = _case(rng, seqlens, kvlens, Hq, Hkv, Dh)
+    mask = _mask_for(rng, sum(seqlens), sum(kvlens), Hq if per_head else None)
+    mask[..., 131, 130:170] = -np.inf  # a query row of sequence 1 that sees nothing
+    d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=len(seqlens), is_causal=int(causal))
+    want = orc.mha(d, q, k, v, ss, ks, attn_mask=mask).astype(np.float32)
+    op = ops.MultiHeadAttention(ops.MultiHeadAttentionParam(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, is_causal=causal))
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    got = op.forward(t(q), t(k), t(v), t(ss), t(ks), 0, max(seqlens), max(kvlens), attn_mask=t(mask))
+    assert op.device_status() == 0
+    got = got.cpu().numpy().astype(np.float32)
+    assert np.isfinite(got).all()
+    err = np.abs(got - want)
+    assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS, (err.max(), err.mean())
+
+
+@pytest.mark.gpu
+def test_gpu_host_operator_with_attn_mask(orc, dev, pkg, host):
+    """The mask as input 8 of the host-layer operator (multi_head_attention_kernel.cc:30)."""
+    import torch
+    rng = np.random.default_rng(6)
+    Hq, Hkv, Dh = 8, 2, 128
+    q, k, v, ss, ks = _case(rng, [70, 3, 129], [70, 40, 129], Hq, Hkv, Dh)
+    mask = _mask_for(rng, 202, 239)
+    d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=3, is_causal=1)
+    want = orc.mha(d, q, k, v, ss, ks, attn_mask=mask).astype(np.float32)
+    eng = host.Engine(0, torch.cuda.current_stream().cuda_stream)
+    op = host.Op(eng, "MultiHeadAttention", MHA_ATTRS)
+    t = lambda a: torch.from_numpy(a).to(dev)
+    out = torch.empty((q.shape[0], Hq, Dh), dtype=torch.float16, device=dev)
+    op.run([t(q), t(k), t(v), t(ss), t(ks), 0, int(129), int(129), t(mask)], [out])
+    eng.synchronize()
+    err = np.abs(out.cpu().numpy().astype(np.float32) - want)
+    assert err.max() <= MAX_ABS and err.mean() <= MEAN_ABS
+    op.close()
+    eng.close()
 
 
 @pytest.mark.gpu

@@ -297,3 +297,43 @@ def test_fast_quantiser_path_of_the_cuda_kernels_gives_the_exact_codes(oracle_mo
                 np.testing.assert_array_equal(fast[safe], codes[safe])
                 total_fast += int(safe.sum())
     assert total_fast > 1_000_000  # the fast path is the common case, so the check is not vacuous
+
+
+@pytest.mark.parametrize("cache_prefill", [False, True])
+def test_cached_operator_mask_matches_numpy(pkg, orc, oracle_mod, cache_prefill):
+    """attn_mask in orc_mhca against numpy over the dequantised rows: decode rows read the cache from position 0,
+    prefill rows read this call's fp16 K/V (mask columns start at start_pos) or, with enable_cache_prefill, the
+    cache (mask columns start at 0)."""
+    from ppl_nn_b200 import workloads
+    rng = np.random.default_rng(9)
+    Hq, Hkv, Dh = 4, 2, 64
+    idx = workloads.make_index([9, 30], [6, 11], prefill_hist=[0, 5] if cache_prefill else [0, 5])
+    T, KV = idx.total_tokens, int(idx.kvstarts[-1])
+    q = rng.standard_normal((T, Hq, Dh)).astype(np.float16)
+    ck = rng.standard_normal((T, Hkv, Dh)).astype(np.float16)
+    cv = rng.standard_normal((T, Hkv, Dh)).astype(np.float16)
+    cshape, sshape = workloads.cache_shapes(0, idx.max_tokens, 1, Hkv, Dh)
+    cache = rng.integers(-127, 128, size=cshape, dtype=np.int8)
+    scale = rng.uniform(0.004, 0.02, size=sshape).astype(np.float16)
+    mask = (rng.standard_normal((T, (KV + 7) // 8 * 8)) * 0.5).astype(np.float16)
+    mask[rng.random(mask.shape) < 0.2] = -np.inf
+    d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=idx.batch, decoding_batches=2,
+                 max_tokens=idx.max_tokens, enable_cache_prefill=int(cache_prefill))
+    got = orc.mhca(d, q, ck, cv, idx.seqstarts, idx.cachestarts, idx.start_pos, cache, scale, kvstarts=idx.kvstarts,
+                   attn_mask=mask).astype(np.float32)
+    deq = oracle_mod.np_dequant(cache[:, 0], scale[:, 0])  # [rows, 2, Hkv, Dh] after the append
+    for b in range(idx.batch):
+        s0, k0, c0, sp = int(idx.seqstarts[b]), int(idx.kvstarts[b]), int(idx.cachestarts[b]), int(idx.start_pos[b])
+        from_cache = b < 2 or cache_prefill
+        for i in range(int(idx.seqlens[b])):
+            n = sp + i + 1 if from_cache else i + 1
+            for h in range(Hq):
+                if from_cache:
+                    k, v = deq[c0:c0 + n, 0, h // 2], deq[c0:c0 + n, 1, h // 2]
+                    mrow = mask[s0 + i, k0:k0 + n]
+                else:
+                    k = ck[s0:s0 + n, h // 2].astype(np.float32)
+                    v = cv[s0:s0 + n, h // 2].astype(np.float32)
+                    mrow = mask[s0 + i, k0 + sp:k0 + sp + n]
+                want = oracle_mod.np_attention_one(q[s0 + i, h].astype(np.float32), k, v, mrow)
+                assert np.abs(got[s0 + i, h] - want).max() <= 2e-3, (b, i, h)
