@@ -69,6 +69,8 @@ def _run_both(lib, op, dev, idx, x):
                                   x["start_pos"].data_ptr(), cache_b.data_ptr(), scale_b.data_ptr(), got.data_ptr(),
                                   stream)
     assert rc == capi.SUCCESS
+    rc, status = lib.static_scratch_status(stream)  # the status word lives in the built-in scratch
+    assert rc == capi.SUCCESS and status == 0
     torch.cuda.synchronize(dev)
     assert torch.equal(cache_a, cache_b) and torch.equal(scale_a, scale_b)
     r = ref.float().cpu().numpy()
