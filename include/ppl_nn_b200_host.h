@@ -55,6 +55,11 @@ void pplb200_host_op_destroy(void* op);
  * valid until the next run or destroy). */
 int pplb200_host_op_run(void* op, const pplb200_host_tensor* inputs, int num_inputs, pplb200_host_tensor* outputs,
                         int num_outputs);
+/* States which inputs (bit i = input i) the op is the LAST consumer of, what the runtime's
+ * KernelExecContext::IsLastConsumerOfInput() answers from the graph; default 0.  A kernel may then hand such an
+ * input's buffer over to an output instead of allocating one (the rotary embedding does, like the reference):
+ * after the run the output's `data` is the input's pointer. */
+void pplb200_host_op_set_last_consumer(void* op, uint32_t input_mask);
 int pplb200_host_engine_synchronize(void* engine);
 
 const char* pplb200_host_retcode_str(int rc);

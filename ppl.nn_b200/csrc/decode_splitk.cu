@@ -498,14 +498,17 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             lo = static_cast<int64_t>(r) * range_tiles;
             hi = lo + range_tiles;
             hi = hi > total_tiles ? total_tiles : hi;
-            int32_t l = 0, h = DB;  // largest b with tile_prefix[b] * nvc <= lo
+            // largest b with tile_prefix[b] * nvc <= lo.  All lanes search together, 32 pivots per round: a
+            // thousand sequences take two dependent loads instead of ten, which is microseconds at the start
+            // of a kernel that only runs for tens of them.
+            int32_t l = 0, h = DB;
             while (h - l > 1) {
-                const int32_t mid = (l + h) >> 1;
-                if (static_cast<int64_t>(a.tile_prefix[mid]) * nvc <= lo) {
-                    l = mid;
-                } else {
-                    h = mid;
-                }
+                const int32_t step = (h - l + 31) >> 5;
+                const int32_t piv = l + (lane + 1) * step;
+                const bool le = piv < h && static_cast<int64_t>(a.tile_prefix[piv]) * nvc <= lo;  // true for a prefix of the lanes
+                const int32_t c = __popc(__ballot_sync(0xffffffffu, le));
+                l += c * step;
+                h = l + step < h ? l + step : h;
             }
             cc.b = l;
             load_seq(cc);
@@ -717,19 +720,24 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                         if (in1) s3 = fmaf(__half2float(mrow1[p1]), kLog2e, s3);
                     }
                     // +inf or NaN in a mask would poison the running maximum: such entries count as "masked out"
-                    s0 = s0 < 3.0e38f ? s0 : kNegBig;
-                    s1 = s1 < 3.0e38f ? s1 : kNegBig;
-                    s2 = s2 < 3.0e38f ? s2 : kNegBig;
-                    s3 = s3 < 3.0e38f ? s3 : kNegBig;
+                    s0 = s0 < 3.0e38f ? s0 : -INFINITY;
+                    s1 = s1 < 3.0e38f ? s1 : -INFINITY;
+                    s2 = s2 < 3.0e38f ? s2 : -INFINITY;
+                    s3 = s3 < 3.0e38f ? s3 : -INFINITY;
                 }
+                // Rows past the end of the sequence.  Without a mask a large negative finite score does: the tile's
+                // first row is a real token, so the reference maximum is a real score before these are
+                // exponentiated.  With a mask every real token of the tile may be removed; -inf then gives weight 0
+                // against the (always finite) reference maximum.
+                constexpr float kOut = MASK ? -INFINITY : kNegBig;
                 if (nvalid < kTileTok) {  // only the last tile of a sequence has rows past its end
                     if (g >= nvalid) {
-                        s0 = kNegBig;
-                        s1 = kNegBig;
+                        s0 = kOut;
+                        s1 = kOut;
                     }
                     if (g + 8 >= nvalid) {
-                        s2 = kNegBig;
-                        s3 = kNegBig;
+                        s2 = kOut;
+                        s3 = kOut;
                     }
                 }
                 {

@@ -40,12 +40,6 @@
 #ifndef PPLB200_PREFILL_WAIT
 #define PPLB200_PREFILL_WAIT mbar_test_wait
 #endif
-#ifndef PPLB200_PF_EXP16
-#define PPLB200_PF_EXP16 0
-#endif
-#ifndef PPLB200_PF_FMA2
-#define PPLB200_PF_FMA2 0
-#endif
 
 namespace pplb200 {
 
@@ -218,12 +212,6 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
-}
-// two exponentials in one special-function operation: fp16 arguments, fp16 results
-__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t x) {
-    uint32_t y;
-    asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-    return y;
 }
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
     float d;
@@ -764,6 +752,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 // row's horizon or past the end of the kv range need the mask (uniform for the CTA).  Unless the
                 // tile has rows that see nothing at all (handled below), column 0 of tile 0 is visible to every
                 // row, so m_ref is a real score from the first tile on.
+                // Score of a position the row may not see.  Without attn_mask a large negative FINITE number does:
+                // every row sees column 0 of its first tile, so its reference maximum is a real score before any
+                // such entry is exponentiated.  With a mask a row may see nothing at all; the entries are then
+                // -inf, which exponentiates to 0 against the (always finite) reference maximum.
+                constexpr float kOut = MASK ? -INFINITY : kNegBig;
                 if constexpr (MASK) {
                     // additive mask, one fp16 per (query row, kv position); entries that the mask tensor does not
                     // hold read as 0 and are reported; +inf / NaN entries count as masked out
@@ -780,7 +773,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         for (int e = 0; e < kBlockN; ++e) {
                             if (e < room && e < vis) {
                                 const float t = fmaf(__half2float(mrow[e]), a.mask_scale, sv[e]);
-                                sv[e] = t < 3.0e38f ? t : kNegBig;
+                                sv[e] = t < 3.0e38f ? t : kOut;
                             }
                         }
                     }
@@ -793,7 +786,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     const int limit = lim64 > kBlockN ? kBlockN : (lim64 < -1 ? -1 : static_cast<int>(lim64));
 #pragma unroll
                     for (int e = 0; e < kBlockN; ++e) {
-                        sv[e] = e <= limit ? sv[e] : kNegBig;
+                        sv[e] = e <= limit ? sv[e] : kOut;
                     }
                 }
                 float mx0 = fmax3(sv[0], sv[1], sv[2]), mx1 = fmax3(sv[3], sv[4], sv[5]);
@@ -840,19 +833,11 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     uint32_t pk[16];
 #pragma unroll
                     for (int e = 0; e < 16; ++e) {
-#if PPLB200_PF_FMA2
+                        // two scores per packed fp32 FMA (measured +1 %; exponentials of fp16 pairs in one
+                        // special-function operation were also tried: no gain, and fp16 arguments cost accuracy)
                         const float2 x = __ffma2_rn(make_float2(sv[32 * q + 2 * e], sv[32 * q + 2 * e + 1]),
                                                     make_float2(sc, sc), make_float2(neg_m, neg_m));
-                        const float x0 = x.x, x1 = x.y;
-#else
-                        const float x0 = fmaf(sv[32 * q + 2 * e], sc, neg_m);
-                        const float x1 = fmaf(sv[32 * q + 2 * e + 1], sc, neg_m);
-#endif
-#if PPLB200_PF_EXP16
-                        pk[e] = ex2_f16x2(h2_as_u32(__floats2half2_rn(x0, x1)));
-#else
-                        pk[e] = h2_as_u32(__floats2half2_rn(ex2_approx(x0), ex2_approx(x1)));
-#endif
+                        pk[e] = h2_as_u32(__floats2half2_rn(ex2_approx(x.x), ex2_approx(x.y)));
                         add_half2_to_float(l_sum, pk[e]);
                     }
                     tmem_st16(t_pb + 16 * q, pk);

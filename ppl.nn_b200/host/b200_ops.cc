@@ -467,10 +467,22 @@ RetCode DynamicBatchingRotaryPositionEmbeddingKernel::DoExecute(KernelExecContex
             return rc;
         }
     }
-    // The reference hands the input buffers over to the outputs when it is their last consumer
-    // (:55-75); here the outputs always get buffers of their own.
-    if ((rc = ReallocOn(rotated_query, GetCudaDevice())) != RC_SUCCESS) return rc;
-    if ((rc = ReallocOn(rotated_key, GetCudaDevice())) != RC_SUCCESS) return rc;
+    // The input buffers are handed over to the outputs when this kernel is their last consumer, as the
+    // reference does (:55-75); the kernels rotate in place then (the C ABI allows the aliasing).
+    const bool can_trans_query = ctx->IsLastConsumerOfInput(0) && query->GetType() == TENSORTYPE_NORMAL;
+    const bool can_trans_key = ctx->IsLastConsumerOfInput(1) && key->GetType() == TENSORTYPE_NORMAL;
+    void* query_data = query->GetBufferPtr();
+    void* key_data = key->GetBufferPtr();
+    if (can_trans_query) {
+        rotated_query->TransferBufferFrom(query);
+    } else if ((rc = ReallocOn(rotated_query, GetCudaDevice())) != RC_SUCCESS) {
+        return rc;
+    }
+    if (can_trans_key) {
+        rotated_key->TransferBufferFrom(key);
+    } else if ((rc = ReallocOn(rotated_key, GetCudaDevice())) != RC_SUCCESS) {
+        return rc;
+    }
 
     int64_t max_seqlen = 0;
     if ((rc = ReadScalar(in[4], &max_seqlen, "max_seqlen")) != RC_SUCCESS) return rc;
@@ -504,7 +516,7 @@ RetCode DynamicBatchingRotaryPositionEmbeddingKernel::DoExecute(KernelExecContex
         return rc;
     }
     Destructor tmp_guard([this, &tmp]() { GetCudaDevice()->FreeTmpBuffer(&tmp); });
-    return FromStatus(pplb200_rope_forward(&p, query->GetBufferPtr(), key->GetBufferPtr(), seqstarts->GetBufferPtr<int64_t>(),
+    return FromStatus(pplb200_rope_forward(&p, query_data, key_data, seqstarts->GetBufferPtr<int64_t>(),
                                            start_pos->GetBufferPtr<int64_t>(), tmp.addr, workspace_bytes,
                                            rotated_query->GetBufferPtr(), rotated_key->GetBufferPtr(), GetStream()));
 }

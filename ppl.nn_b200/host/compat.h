@@ -2,7 +2,7 @@
 // the operator and kernel classes in this directory can be written against the llm_cuda engine's
 // plug-in interface and built without a ppl.nn checkout.  Each type carries only the members this
 // path uses; names and meanings follow ppl.nn (citations are paths in its tree):
-//   RetCode / GetRetCodeStr        ppl.common (external); values used: see Appendix of the op contract
+//   RetCode / GetRetCodeStr        ppl.common (external); only the codes the llm_cuda engine returns on this path
 //   TensorShape                    include/ppl/nn/common/tensor_shape.h:21-25 (alias of ppl::common's)
 //   BufferDesc                     include/ppl/nn/common/buffer_desc.h:25-36
 //   Device                         include/ppl/nn/common/device.h:30-137
@@ -11,7 +11,8 @@
 //                                         src/ppl/nn/runtime/kernel_exec_context.h:28-48
 //   ir::Node, ir::Attr             src/ppl/nn/ir/node.h, src/ppl/nn/ir/attr.h
 //   KernelImpl                     src/ppl/nn/runtime/kernel_impl.h:65-71
-// When built inside ppl.nn, define PPLNN_B200_WITH_PPLNN and include the real headers instead.
+// Inside a ppl.nn build this header is not used at all: b200_ops.* and llm_cuda.* then include the real
+// headers these stand-ins are named after (see INTEGRATION.md for the file-by-file mapping).
 #pragma once
 
 #include <stdint.h>
@@ -179,6 +180,10 @@ public:
     virtual ppl::common::RetCode CopyFromHost(BufferDesc* dst, const void* src, uint64_t bytes) const = 0;
 };
 
+// include/ppl/nn/common/types.h: tensors the runtime may recycle are "normal"; inputs, outputs and constants
+// of the whole graph are reserved.  The harness only makes normal ones.
+enum tensortype_t : int { TENSORTYPE_NORMAL = 0, TENSORTYPE_RESERVED = 1 };
+
 // A tensor of the runtime: shape + a buffer on some device.  The buffer is either owned (allocated by
 // ReallocBuffer through the device) or borrowed (SetBufferPtr: user-owned memory such as the KV cache,
 // tools/benchmark_llama/text_generator.cc:223-224).
@@ -205,6 +210,25 @@ public:
         owner_ = false;
     }
     bool IsBufferOwner() const { return owner_; }
+    tensortype_t GetType() const { return TENSORTYPE_NORMAL; }
+
+    // Takes over `another`'s buffer together with its ownership; this tensor's old buffer is freed (or let
+    // go, if borrowed) and `another` is left without one (src/ppl/nn/runtime/tensor_impl.h:83-93).
+    void TransferBufferFrom(TensorImpl* another) {
+        FreeBuffer();
+        buffer_ = another->buffer_;
+        capacity_ = another->capacity_;
+        owner_ = another->owner_;
+        device_ = another->device_;
+        another->DetachBuffer();
+    }
+    BufferDesc DetachBuffer() {
+        const BufferDesc b = buffer_;
+        buffer_.addr = nullptr;
+        capacity_ = 0;
+        owner_ = false;
+        return b;
+    }
 
     // No-op when the tensor borrows a buffer that is already set (src/ppl/nn/runtime/tensor_impl.cc:25-32).
     ppl::common::RetCode ReallocBuffer() {
@@ -278,6 +302,13 @@ private:
 class KernelExecContext final : public InputOutputInfo {
 public:
     bool IsProfilingEnabled() const { return false; }
+    // Whether this kernel is the last one to read input `idx` (src/ppl/nn/runtime/kernel_exec_context.h:37-43
+    // derives it from the graph's edge-to-last-consumer list; the harness states it as a bit mask).
+    bool IsLastConsumerOfInput(uint32_t idx) const { return idx < 32 && ((last_consumer_mask_ >> idx) & 1u) != 0; }
+    void SetLastConsumerMask(uint32_t mask) { last_consumer_mask_ = mask; }
+
+private:
+    uint32_t last_consumer_mask_ = 0;
 };
 
 namespace ir {

@@ -23,6 +23,7 @@ struct Op {
     std::unique_ptr<LlmCudaOptKernel> opt;
     std::unique_ptr<KernelImpl> kernel;
     std::vector<std::unique_ptr<TensorImpl>> inputs, outputs;
+    uint32_t last_consumer_mask = 0;  // bit i: this op is the last consumer of its input i
 };
 
 datatype_t ToDataType(int32_t dt) {
@@ -232,6 +233,7 @@ int pplb200_host_op_run(void* opv, const pplb200_host_tensor* inputs, int num_in
     KernelExecContext ctx;
     ctx.SetInputs(in_raw);
     ctx.SetOutputs(out_raw);
+    ctx.SetLastConsumerMask(op->last_consumer_mask);
     const RetCode rc = op->kernel->Execute(&ctx);
     for (int i = 0; i < num_outputs; ++i) {
         if (!out_raw[i]) {
@@ -247,6 +249,12 @@ int pplb200_host_op_run(void* opv, const pplb200_host_tensor* inputs, int num_in
         outputs[i].on_host = 0;
     }
     return rc;
+}
+
+void pplb200_host_op_set_last_consumer(void* op, uint32_t input_mask) {
+    if (op) {
+        static_cast<Op*>(op)->last_consumer_mask = input_mask;
+    }
 }
 
 int pplb200_host_engine_synchronize(void* engine) {

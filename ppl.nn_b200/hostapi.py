@@ -15,7 +15,8 @@ HOST_EXPORTS = (
     "pplb200_host_engine_create", "pplb200_host_engine_destroy", "pplb200_host_engine_configure",
     "pplb200_host_engine_tmp_pool_bytes", "pplb200_host_register_ops", "pplb200_host_registry_has",
     "pplb200_host_registry_remove", "pplb200_host_registry_register_again", "pplb200_host_op_create",
-    "pplb200_host_op_destroy", "pplb200_host_op_run", "pplb200_host_engine_synchronize",
+    "pplb200_host_op_destroy", "pplb200_host_op_run", "pplb200_host_op_set_last_consumer",
+    "pplb200_host_engine_synchronize",
     "pplb200_host_retcode_str",
 )
 
@@ -63,6 +64,8 @@ def _dll():
     d.pplb200_host_op_run.restype = ctypes.c_int
     d.pplb200_host_op_run.argtypes = [vp, ctypes.POINTER(HostTensor), ctypes.c_int, ctypes.POINTER(HostTensor),
                                       ctypes.c_int]
+    d.pplb200_host_op_set_last_consumer.restype = None
+    d.pplb200_host_op_set_last_consumer.argtypes = [vp, ctypes.c_uint32]
     d.pplb200_host_engine_synchronize.restype = ctypes.c_int
     d.pplb200_host_engine_synchronize.argtypes = [vp]
     d.pplb200_host_retcode_str.restype = ctypes.c_char_p
@@ -167,6 +170,13 @@ class Op:
                                                     values, len(attrs), ctypes.byref(rc))
         if not self.handle:
             raise RetCodeError(f"create {domain}:{type_}:{version}", retcode_str(rc.value))
+
+    def set_last_consumer(self, *input_indices: int) -> None:
+        """Tell the op that it is the last consumer of these inputs (what the runtime derives from the graph)."""
+        mask = 0
+        for i in input_indices:
+            mask |= 1 << int(i)
+        self.d.pplb200_host_op_set_last_consumer(self.handle, mask)
 
     def run_raw(self, inputs: list, outputs: list) -> tuple[str, list[HostTensor]]:
         """inputs/outputs: HostTensor structs.  Returns (RetCode name, output structs after the run)."""

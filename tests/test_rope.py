@@ -217,3 +217,33 @@ def test_gpu_host_operator(orc, dev, pkg, host):
     _close(rk.cpu().numpy(), want_k)
     op.close()
     eng.close()
+
+
+@pytest.mark.gpu
+def test_host_operator_hands_input_buffers_over_when_it_is_their_last_consumer(orc, dev, pkg, host):
+    """rotary_position_embedding_kernel.cc:55-75: as the last consumer of query / key the kernel moves their
+    buffers to rotated_query / rotated_key (TransferBufferFrom) and rotates in place; otherwise the outputs get
+    buffers of their own."""
+    import torch
+    rng = np.random.default_rng(12)
+    q, k, ss, sp = _case(rng, [9, 1, 40], [0, 77, 3], 8, 2, 128)
+    want_q, want_k = orc.rope(q, k, ss, sp, theta=10000.0)
+    eng = host.Engine(0, torch.cuda.current_stream().cuda_stream)
+    op = host.Op(eng, "RotaryPositionEmbedding", dict(theta=_fbits(10000.0)))
+    t = lambda a: torch.from_numpy(a).to(dev)
+    dq, dk = t(q), t(k)
+    op.set_last_consumer(0)  # query only: rotated_query takes query's buffer, rotated_key is allocated
+    res = op.run([dq, dk, t(ss), t(sp), 40], [None, None])
+    eng.synchronize()
+    assert res[0].data == dq.data_ptr() and res[1].data not in (None, 0, dk.data_ptr())
+    _close(dq.cpu().numpy(), want_q)                      # rotated in place
+    assert np.array_equal(dk.cpu().numpy().view(np.uint16), k.view(np.uint16))  # key untouched
+    dq2, dk2 = t(q), t(k)
+    op.set_last_consumer(0, 1)
+    res = op.run([dq2, dk2, t(ss), t(sp), 40], [None, None])
+    eng.synchronize()
+    assert res[0].data == dq2.data_ptr() and res[1].data == dk2.data_ptr()
+    _close(dq2.cpu().numpy(), want_q)
+    _close(dk2.cpu().numpy(), want_k)
+    op.close()
+    eng.close()
