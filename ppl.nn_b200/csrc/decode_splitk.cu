@@ -218,7 +218,7 @@ constexpr int kPlanThreads = 512;
 __global__ void __launch_bounds__(kPlanThreads)
 decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
                    int32_t decoding_batches, int32_t class_heads, int64_t max_kvlen, int32_t split_k_mode,
-                   int32_t workers, int32_t max_ranges, PlanHeader* __restrict__ hdr,
+                   int32_t workers, int32_t max_ranges, int32_t static_ranges, PlanHeader* __restrict__ hdr,
                    int32_t* __restrict__ tile_prefix) {
     using Scan = cub::BlockScan<int32_t, kPlanThreads>;
     __shared__ typename Scan::TempStorage tmp;
@@ -230,7 +230,7 @@ decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restr
         carry = 0;
         longest = 1;
         hdr->status = 0;
-        hdr->counter = 0;
+        hdr->counter = static_ranges;  // the main kernel's CTAs take ranges [0, static_ranges) without asking
     }
     __syncthreads();
     for (int32_t base = 0; base < decoding_batches; base += kPlanThreads) {
@@ -444,6 +444,11 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
     const int head_lanes = a.head_lanes;
     const bool lockstep = a.lockstep != 0;
     const int layer = a.layer_idx;
+    const int32_t max_rows = static_cast<int32_t>(a.max_tokens);
+    const int64_t scale_tile_bytes = kTileTok * scale_row_bytes;
+    // paged mode: a tile starts a page when its token offset has no bits below the page size (page sizes that
+    // are not powers of two look the page up for every tile)
+    const uint32_t page_mask = page_shift >= 0 ? static_cast<uint32_t>(a.geom.page_size) - 1u : 0u;
 
     constexpr int32_t kBadRow = -(1 << 30);  // row_base of a sequence whose cachestarts entry is not a cache row
     auto load_seq = [&](Cursor& c) {  // per-sequence fields
@@ -471,14 +476,21 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
         }
     };
 
-    for (;;) {
-        __syncthreads();  // everyone has read the previous s_base
-        if (threadIdx.x == 0) {
-            s_base = atomicAdd(&a.hdr->counter, ranges_per_cta);
+    for (bool first_round = true;; first_round = false) {
+        // The first ranges are dealt statically, one batch per CTA (with one range per resident warp, the
+        // usual plan, that is all of them: no atomic and no barrier ahead of the first loads); the counter,
+        // which the planning kernel starts behind the static batches, hands out the rest.
+        int32_t base = static_cast<int32_t>(blockIdx.x) * ranges_per_cta;
+        if (!first_round) {
+            __syncthreads();  // everyone has read the previous s_base
+            if (threadIdx.x == 0) {
+                s_base = atomicAdd(&a.hdr->counter, ranges_per_cta);
+            }
+            __syncthreads();
+            base = s_base;
         }
-        __syncthreads();
-        const int32_t r = s_base + sub;
-        if (s_base >= num_ranges) {
+        const int32_t r = base + sub;
+        if (base >= num_ranges) {
             break;  // uniform for the CTA
         }
         if (r >= num_ranges) {
@@ -521,9 +533,14 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
         int32_t to_issue = static_cast<int32_t>(hi - lo);  // tiles of the range not yet issued
         int32_t to_consume = to_issue;
 
-        auto issue_one = [&]() {
+        // Position of the next tile to issue, kept incrementally: its first cache row (negative: not a cache
+        // row) and this lane's source address in the scale tensor.  Both are worked out in full where a new
+        // segment or, in paged mode, a new page begins; inside a run of consecutive rows a tile adds 16 rows.
+        int32_t i_row = 0;
+        const char* i_src = nullptr;
+        auto locate = [&]() {
             const int tok = ic.tile * kTileTok;
-            int row = ic.row_base + tok;
+            int32_t row = ic.row_base + tok;  // kBadRow + tok stays negative
             if (paged) {  // the page table row of the sequence gives the first cache row of every page
                 const uint32_t page = page_shift >= 0 ? static_cast<uint32_t>(tok) >> page_shift
                                                       : static_cast<uint32_t>(tok) / static_cast<uint32_t>(a.geom.page_size);
@@ -531,28 +548,30 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 if (page < static_cast<uint32_t>(a.geom.cachestart_stride_b)) {
                     const int64_t first = a.cachestarts[ic.b * a.geom.cachestart_stride_b + page];
                     if (first >= 0 && first < a.max_tokens) {
-                        row = static_cast<int>(first) + (tok - static_cast<int>(page) * a.geom.page_size);
+                        row = static_cast<int32_t>(first) + (tok - static_cast<int>(page) * a.geom.page_size);
                     }
                 }
             }
+            i_row = row;
+            i_src = scale_layer + (row >= 0 ? row : 0) * scale_row_bytes + ic.kvh * scale_head_bytes + scale_lane_off;
+        };
+        auto issue_one = [&]() {
             // A tile whose first row is not a cache row (a wrong index tensor) is flagged and read as zeros:
             // the scale copies read nothing and the bulk copies start past the last row, which zero-fills.
-            const bool row_ok = row >= 0 && row < a.max_tokens;
-            if (!row_ok) {
+            int32_t row = i_row;
+            if (row < 0 || row >= max_rows) {
                 if (lane == 0) {
                     atomicOr(&a.hdr->status, kDevRowOutOfRange);
                 }
-                row = static_cast<int>(a.max_tokens);
+                row = max_rows;
             }
             const uint32_t st = wsm + i_stage * T::kStageBytes;
             const uint32_t bar = wbar + i_stage * 8;
             {
                 // scales: every lane copies its half row of the K tile and of the V tile
-                const char* src = scale_layer + (row_ok ? row : 0) * scale_row_bytes + ic.kvh * scale_head_bytes +
-                                  scale_lane_off;
-                const uint32_t nbytes = (row + (lane >> 1)) < a.max_tokens ? kScaleCopy : 0;  // rows past the cache: zeros
-                cp_async<kScaleCopy>(st + scale_dst_off, src, nbytes);
-                cp_async<kScaleCopy>(st + scale_dst_off + T::kScaleBytes, src + scale_kv_bytes, nbytes);
+                const uint32_t nbytes = (row + (lane >> 1)) < max_rows ? kScaleCopy : 0;  // rows past the cache: zeros
+                cp_async<kScaleCopy>(st + scale_dst_off, i_src, nbytes);
+                cp_async<kScaleCopy>(st + scale_dst_off + T::kScaleBytes, i_src + scale_kv_bytes, nbytes);
                 cp_async_arrive(bar);
             }
             if (lane == 0) {
@@ -564,9 +583,22 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             }
             __syncwarp();
             i_stage = (i_stage + 1 == kStages) ? 0 : i_stage + 1;
-            advance(ic, 1);
             --to_issue;
+            // next tile: same segment and (paged) same page -> 16 rows on; otherwise locate it afresh
+            if (++ic.tile < ic.n && !(paged && (static_cast<uint32_t>(ic.tile * kTileTok) & page_mask) == 0u)) {
+                i_row += kTileTok;
+                i_src += scale_tile_bytes;
+            } else {
+                if (ic.tile >= ic.n) {
+                    ic.tile -= 1;
+                    advance(ic, 1);
+                }
+                if (ic.b < DB) {
+                    locate();
+                }
+            }
         };
+        locate();
         if (wait_dead) {
             to_issue = 0;  // a warp that has given up runs through its remaining ranges without copies
         }
@@ -1159,10 +1191,16 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
         return rc;
     }
 
+    // never more CTAs than there can be ranges
+    int64_t grid = plan.grid;
+    const int64_t per_cta = kWarps / plan.head_lanes;
+    if ((plan.max_ranges + per_cta - 1) / per_cta < grid) {
+        grid = (plan.max_ranges + per_cta - 1) / per_cta;
+    }
     launch_dependent(decode_plan_kernel, dim3(1), dim3(kPlanThreads), 0, stream, seqstarts, start_pos,
                      static_cast<int32_t>(p.decoding_batches), static_cast<int32_t>(plan.class_heads), p.max_kvlen,
-                     p.split_k_mode, static_cast<int32_t>(plan.workers), static_cast<int32_t>(plan.max_ranges), hdr,
-                     tile_prefix);
+                     p.split_k_mode, static_cast<int32_t>(plan.workers), static_cast<int32_t>(plan.max_ranges),
+                     static_cast<int32_t>(grid * per_cta), hdr, tile_prefix);
     rc = check_launch("decode_plan_kernel");
     if (rc != PPLB200_SUCCESS) {
         return rc;
@@ -1198,12 +1236,6 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.num_kv_heads = p.num_kv_heads;
     a.mask = mask;
 
-    // never more CTAs than there can be ranges
-    int64_t grid = plan.grid;
-    const int64_t per_cta = kWarps / plan.head_lanes;
-    if ((plan.max_ranges + per_cta - 1) / per_cta < grid) {
-        grid = (plan.max_ranges + per_cta - 1) / per_cta;
-    }
     if (a.mask.data != nullptr) {  // the mask path need not be the fastest: one instance, run-time coordinate order
         rc = launch_main<DH, kOrderGeneric, true>(tm_codes, a, grid, stream);
     } else {
