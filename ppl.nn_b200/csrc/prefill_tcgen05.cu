@@ -33,8 +33,11 @@
 #include <cuda.h>
 #include <stdio.h>
 
+#include <cub/block/block_scan.cuh>
+
 #include "common.cuh"
 #include "launch.h"
+#include "ragged.cuh"
 #include "tensor_map.h"
 
 #ifndef PPLB200_PREFILL_WAIT
@@ -896,25 +899,49 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
 }
 
-// Prefix sum of the (tile-padded) kv lengths of the prefill sequences: first staging row of each.
-__global__ void prefill_stage_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
-                                          int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen,
-                                          int64_t* __restrict__ stage_starts) {
-    if (blockIdx.x == 0 && threadIdx.x == 0) {
-        int64_t acc = 0;
-        for (int32_t i = 0; i < prefill_batches; ++i) {
+// Prefix sum of the (tile-padded) kv lengths of the prefill sequences: first staging row of each.  One CTA.
+constexpr int kStagePlanThreads = 256;
+__global__ void __launch_bounds__(kStagePlanThreads)
+prefill_stage_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
+                          int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen,
+                          int64_t* __restrict__ stage_starts) {
+    using Scan = cub::BlockScan<int64_t, kStagePlanThreads>;
+    __shared__ typename Scan::TempStorage tmp;
+    __shared__ int64_t carry;
+    if (threadIdx.x == 0) {
+        carry = 0;
+    }
+    __syncthreads();
+    for (int32_t base = 0; base < prefill_batches; base += kStagePlanThreads) {
+        const int32_t i = base + threadIdx.x;
+        int64_t rows = 0;
+        if (i < prefill_batches) {
             const int32_t b = decoding_batches + i;
             int64_t n = start_pos[b] + (seqstarts[b + 1] - seqstarts[b]);
-            n = n > max_kvlen ? max_kvlen : n;
-            stage_starts[i] = acc;
-            acc += (n + kBlockN - 1) / kBlockN * kBlockN;
+            n = n > max_kvlen ? max_kvlen : (n < 0 ? 0 : n);
+            rows = (n + kBlockN - 1) / kBlockN * kBlockN;
         }
-        stage_starts[prefill_batches] = acc;
+        int64_t excl, total;
+        Scan(tmp).ExclusiveSum(rows, excl, total);
+        const int64_t c = carry;
+        if (i < prefill_batches) {
+            stage_starts[i] = c + excl;
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            carry = c + total;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        stage_starts[prefill_batches] = carry;
     }
 }
 
-// Dequantise the cache rows of the prefill sequences (history and this call's tokens) into fp16
-// staging tensors [rows, Hkv, Dh]; pad rows up to the next multiple of the kv tile are zeroed.
+// Dequantise the cache rows of the prefill sequences (history and this call's tokens) into fp16 staging
+// tensors [rows, Hkv, Dh]; the pad rows up to the next multiple of the kv tile are zeroed.  Same streaming
+// shape as the KeyValueCache gather: a warp owns runs of 32 consecutive quantisation groups of one staging
+// row (8 code bytes in and 16 bytes out per lane, coalesced) and looks the owning sequence up once per run.
 __global__ void __launch_bounds__(256)
 prefill_stage_dequant_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ start_pos,
                              const int64_t* __restrict__ cachestarts, const int64_t* __restrict__ stage_starts,
@@ -922,54 +949,53 @@ prefill_stage_dequant_kernel(const int64_t* __restrict__ seqstarts, const int64_
                              __half* __restrict__ k_stage, __half* __restrict__ v_stage, CacheGeom geom,
                              int32_t decoding_batches, int32_t prefill_batches, int64_t max_kvlen, int64_t max_tokens,
                              uint32_t* __restrict__ status, int num_kv_heads, int head_dim) {
-    const int groups_per_head = head_dim >> 3;
-    const int64_t groups_per_tensor_row = static_cast<int64_t>(num_kv_heads) * groups_per_head;
-    const int64_t groups_per_token = 2 * groups_per_tensor_row;
+    const int lane = threadIdx.x & 31;
+    const int group_shift = head_dim == 128 ? 4 : 3;
+    const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
+    const int32_t groups_per_token = 2 * groups_per_tensor_row;
     const int64_t total_rows = stage_starts[prefill_batches];
-    const int64_t total = total_rows * groups_per_token;
-    for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
-         idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int64_t row = idx / groups_per_token;
-        const int64_t rr = idx - row * groups_per_token;
-        const int kv = rr >= groups_per_tensor_row ? 1 : 0;
-        const int64_t r2 = rr - kv * groups_per_tensor_row;
-        const int head = static_cast<int>(r2 / groups_per_head);
-        const int grp = static_cast<int>(r2 - static_cast<int64_t>(head) * groups_per_head);
-        // sequence that owns this staging row
-        int32_t lo = 0, hi = prefill_batches;
-        while (hi - lo > 1) {
-            const int32_t mid = (lo + hi) >> 1;
-            if (stage_starts[mid] <= row) {
-                lo = mid;
-            } else {
-                hi = mid;
-            }
-        }
-        const int32_t b = decoding_batches + lo;
-        const int64_t pos = row - stage_starts[lo];
+    for (WarpItems it(groups_per_token); it.tok < total_rows; it.next()) {
+        const int64_t row = it.tok;
+        const int32_t i = warp_find_segment(stage_starts, prefill_batches, row, lane);
+        const int32_t b = decoding_batches + i;
+        const int64_t pos = row - stage_starts[i];
         int64_t kvlen = start_pos[b] + (seqstarts[b + 1] - seqstarts[b]);
         kvlen = kvlen > max_kvlen ? max_kvlen : kvlen;
-        uint4 out = make_uint4(0u, 0u, 0u, 0u);
-        const int64_t crow = pos < kvlen ? cache_row(geom, cachestarts, b, pos) : 0;
-        if (pos < kvlen && !cache_row_ok(crow, max_tokens)) {  // a wrong index tensor: flagged, read as zeros
-            if (grp == 0) {
-                atomicOr(status, kDevRowOutOfRange);
-            }
-        } else if (pos < kvlen) {
-            const int64_t off = cache_offset(geom, crow, kv, head);
-            const uint2 codes = *reinterpret_cast<const uint2*>(cache + off + grp * 8);
-            const float s = __half2float(scale[(off >> 3) + grp]);
-            __half2* o2 = reinterpret_cast<__half2*>(&out);
-            const uint32_t w[2] = {codes.x, codes.y};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int c0 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1))) & 0xffu);
-                const int c1 = static_cast<int8_t>((w[i >> 1] >> (16 * (i & 1) + 8)) & 0xffu);
-                o2[i] = __floats2half2_rn(static_cast<float>(c0) * s, static_cast<float>(c1) * s);
+        int64_t crow = -1;
+        if (pos < kvlen) {
+            crow = cache_row(geom, cachestarts, b, pos);
+            if (!cache_row_ok(crow, max_tokens)) {  // a wrong index tensor: flagged, read as zeros
+                if (lane == 0) {
+                    atomicOr(status, kDevRowOutOfRange);
+                }
+                crow = -1;
             }
         }
-        __half* dst = (kv ? v_stage : k_stage) + (row * num_kv_heads + head) * head_dim + grp * 8;
-        *reinterpret_cast<uint4*>(dst) = out;
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+            if (g >= groups_per_token) {
+                continue;
+            }
+            int kv, head, grp;
+            split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
+            uint4 out = make_uint4(0u, 0u, 0u, 0u);
+            if (crow >= 0) {
+                const int64_t off = cache_offset(geom, crow, kv, head);
+                const uint2 codes = *reinterpret_cast<const uint2*>(cache + off + grp * 8);
+                const float sf = __half2float(scale[(off >> 3) + grp]);
+                __half2* o2 = reinterpret_cast<__half2*>(&out);
+                const uint32_t w[2] = {codes.x, codes.y};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int c0 = static_cast<int8_t>((w[e >> 1] >> (16 * (e & 1))) & 0xffu);
+                    const int c1 = static_cast<int8_t>((w[e >> 1] >> (16 * (e & 1) + 8)) & 0xffu);
+                    o2[e] = __floats2half2_rn(static_cast<float>(c0) * sf, static_cast<float>(c1) * sf);
+                }
+            }
+            __half* dst = (kv ? v_stage : k_stage) + (row * num_kv_heads + head) * head_dim + grp * 8;
+            *reinterpret_cast<uint4*>(dst) = out;
+        }
     }
 }
 
@@ -1098,14 +1124,16 @@ static int launch_prefill_dh(const pplb200_attn_params& p, const CacheGeom& geom
         const uint64_t one = align256(static_cast<uint64_t>(plan.kv_rows_bound) * p.num_kv_heads * p.head_dim * 2);
         __half* ks = reinterpret_cast<__half*>(base + plan.off_kv_stage);
         __half* vs = reinterpret_cast<__half*>(base + plan.off_kv_stage + one);
-        prefill_stage_plan_kernel<<<1, 32, 0, stream>>>(seqstarts, start_pos, static_cast<int32_t>(p.decoding_batches),
-                                                        static_cast<int32_t>(plan.prefill_batches), p.max_kvlen, ss);
+        prefill_stage_plan_kernel<<<1, kStagePlanThreads, 0, stream>>>(
+            seqstarts, start_pos, static_cast<int32_t>(p.decoding_batches), static_cast<int32_t>(plan.prefill_batches),
+            p.max_kvlen, ss);
         rc = check_launch("prefill_stage_plan_kernel");
         if (rc != PPLB200_SUCCESS) {
             return rc;
         }
-        const int64_t work = plan.kv_rows_bound * 2 * p.num_kv_heads * (p.head_dim / 8);
-        int64_t blocks = (work + 255) / 256;
+        // a warp per run of 32 * kChunks groups of a staging row; grid-stride beyond 16 CTAs per SM
+        const int64_t items_per_row = (2 * p.num_kv_heads * (p.head_dim / 8) + 32 * kChunks - 1) / (32 * kChunks);
+        int64_t blocks = (plan.kv_rows_bound * items_per_row * 32 + 255) / 256;
         blocks = blocks > 148 * 16 ? 148 * 16 : (blocks < 1 ? 1 : blocks);
         prefill_stage_dequant_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
             seqstarts, start_pos, cachestarts, ss, static_cast<const int8_t*>(cache), static_cast<const __half*>(scale),
