@@ -43,7 +43,7 @@ def _forward(op, dc, **kw):
                       dc.start_pos, idx.decoding_batches, idx.max_seqlen, idx.max_kvlen, dc.cache, dc.scale, **kw)
 
 
-def _check_sample(orc, dc, spec, out, seqs):
+def _check_sample(orc, dc, spec, out, seqs, cache_prefill=False):
     """Oracle on the sequences `seqs` only, over a compacted host copy of their cache rows (layout 0)."""
     from ppl_nn_b200 import workloads
     idx = dc.index
@@ -74,7 +74,7 @@ def _check_sample(orc, dc, spec, out, seqs):
     ck = dc.current_key[tok].cpu().numpy()
     cv = dc.current_value[tok].cpu().numpy()
     d = orc.desc(num_heads=Hq, num_kv_heads=Hkv, head_dim=Dh, batch=sub.batch, decoding_batches=n_dec,
-                 max_tokens=sub.max_tokens)
+                 max_tokens=sub.max_tokens, enable_cache_prefill=int(cache_prefill))
     want = orc.mhca(d, q, ck, cv, sub.seqstarts, sub.cachestarts, sub.start_pos, cache, scale)
     # the oracle re-appended this step's tokens into its copy: the GPU's rows must be identical
     for i, b in enumerate(seqs):
@@ -120,6 +120,30 @@ def test_full_size_sampled_sequences_match_the_oracle(orc, dev, pkg, name, k_dec
         diff = (other - ref).abs()
         assert float(diff.max()) <= MAX_ABS and float(diff.mean()) <= MEAN_ABS, (name, mode)
     del dc, out
+    torch.cuda.empty_cache()
+
+
+def test_cache_prefill_at_full_size(orc, dev, pkg):
+    """The mixed continuous-batching step with enable_cache_prefill: the 8 prompts (512..2048 tokens) read their
+    keys and values back from the INT8 cache.  The two shortest prompts and sampled decode sequences against the
+    oracle; every prompt's output must also stay within tolerance of the run that reads the fp16 inputs, from
+    which it differs only by the quantisation of K and V."""
+    import torch
+    from ppl_nn_b200 import workloads
+    spec = workloads.SPECS["cfg3_llama8b_mixed"]
+    dc = workloads.device_case(spec, dev)
+    idx = dc.index
+    op = _op(dc, spec, cache_prefill=True)
+    out = _forward(op, dc)
+    assert op.device_status() == 0
+    assert bool(torch.isfinite(out.float()).all())
+    _check_sample(orc, dc, spec, out, _sample(idx, np.random.default_rng(8), 2, 2), cache_prefill=True)
+    plain = _forward(_op(dc, spec), dc).float()
+    t0 = int(idx.seqstarts[idx.decoding_batches])
+    diff = (out.float()[t0:] - plain[t0:]).abs()
+    assert 0.0 < float(diff.max()) <= 0.25 and float(diff.mean()) <= 5e-3  # int8 K/V against fp16 K/V
+    assert bool((out[:t0].view(torch.int16) == plain.to(torch.float16)[:t0].view(torch.int16)).all())  # decode rows: same
+    del dc, out, plain
     torch.cuda.empty_cache()
 
 
