@@ -292,6 +292,18 @@ decode_plan_kernel(const int64_t* __restrict__ seqstarts, const int64_t* __restr
 // Main kernel
 // ------------------------------------------------------------------------------------------
 
+// lo += low half of ph, hi += high half of ph: the fp16 values widened exactly, one mixed-precision add each
+__device__ __forceinline__ void add_halves_to_floats(float& lo, float& hi, uint32_t ph) {
+    asm("{\n"
+        ".reg .b16 h0, h1;\n"
+        "mov.b32 {h0, h1}, %2;\n"
+        "add.rn.f32.f16 %0, h0, %0;\n"
+        "add.rn.f32.f16 %1, h1, %1;\n"
+        "}\n"
+        : "+f"(lo), "+f"(hi)
+        : "r"(ph));
+}
+
 // K codes word -> two half2 (channels 0,1 and 2,3 of the word), scaled: k = fp16(code * scale).  The product
 // of a 7-bit code and an 11-bit scale does not fit fp16; its rounding error, 2^-11 relative per element, is the
 // largest error of the whole kernel on keys with outlier channels (scores with a wide range: a pair of
@@ -427,7 +439,8 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
     uint32_t c_stage = 0, c_phase = 0;  // consume position in the stage ring
     uint32_t i_stage = 0;               // issue position in the stage ring
     bool wait_dead = false;             // set after the first timed-out wait: stop waiting and issuing, just finish
-    int32_t dead_inflight = 0;          // tiles issued but not yet seen complete when the warp gave up
+    int32_t dead_inflight = 0;          // tiles issued but not yet seen complete when the warp gave up ...
+    uint32_t dead_stage = 0, dead_phase = 0;  // ... and the ring position of the first of them
 
     const int nvc = a.class_heads;
     const int cls = warp % a.head_lanes;             // head class of this warp
@@ -652,6 +665,9 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
             }
             float m0 = kNegBig, m1 = kNegBig, l0 = 0.0f, l1 = 0.0f;
+            // growth thresholds of the lazy maximum in the units of the scores as they are compared (see below)
+            const float inv_sc = MASK ? 1.0f : 1.0f / a.scale_log2;
+            float thr0 = (kNegBig + kRescaleSlack) * inv_sc, thr1 = thr0;
             // attn_mask rows of this thread's two query heads (2t, 2t+1 of the octet): element [kv position]
             const __half* mrow0 = nullptr;
             const __half* mrow1 = nullptr;
@@ -673,12 +689,16 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             }
 
             for (int32_t tile = t_first; tile < t_end; ++tile) {
-                if (!wait_dead) {
+                // the common case is one try (it parks the warp until the tile has landed, up to the hint); a warp
+                // that has given up before falls through without waiting
+                if (!mbar_try_wait_hint(wbar + c_stage * 8, c_phase, PPLB200_WAIT_HINT_NS) && !wait_dead) {
                     if (!mbar_wait_bounded(reinterpret_cast<uint64_t*>(full_bar + warp * kStages + c_stage), c_phase)) {
                         // Give up: no further copies are issued and no further waits are made; the tiles already
                         // issued (this one included) are waited for once more, briefly, before the kernel returns.
                         wait_dead = true;
                         dead_inflight = (to_consume - (tile - t_first)) - to_issue;
+                        dead_stage = c_stage;
+                        dead_phase = c_phase;
                         to_issue = 0;
                         if (lane == 0) {
                             atomicOr(&a.hdr->status, kDevTmaTimeout);
@@ -735,12 +755,16 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 }
 
                 // ---------------- softmax (exp2 domain, lazy reference maximum) ----------------
-                float s0 = sacc[0] * a.scale_log2;  // token g,   head 2t
-                float s1 = sacc[1] * a.scale_log2;  // token g,   head 2t+1
-                float s2 = sacc[2] * a.scale_log2;  // token g+8, head 2t
-                float s3 = sacc[3] * a.scale_log2;  // token g+8, head 2t+1
+                // Raw scores: token g / g+8, heads 2t / 2t+1.  Without a mask they stay unscaled: the growth test
+                // compares them with thresholds kept in raw units (thr = (m + slack) / scale, updated only when the
+                // reference maximum moves), and scale and maximum enter the exponent through one FMA.
+                float s0 = sacc[0], s1 = sacc[1], s2 = sacc[2], s3 = sacc[3];
                 if constexpr (MASK) {  // additive mask on the scaled scores (exp2 domain: times log2 e)
                     constexpr float kLog2e = 1.4426950408889634f;
+                    s0 *= a.scale_log2;
+                    s1 *= a.scale_log2;
+                    s2 *= a.scale_log2;
+                    s3 *= a.scale_log2;
                     const int64_t p0 = static_cast<int64_t>(tile) * kTileTok + g, p1 = p0 + 8;
                     const bool in0 = p0 < kvlen && p0 < mask_room, in1 = p1 < kvlen && p1 < mask_room;
                     if (mrow0) {
@@ -757,11 +781,10 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                     s2 = s2 < 3.0e38f ? s2 : -INFINITY;
                     s3 = s3 < 3.0e38f ? s3 : -INFINITY;
                 }
-                // Rows past the end of the sequence.  Without a mask a large negative finite score does: the tile's
-                // first row is a real token, so the reference maximum is a real score before these are
-                // exponentiated.  With a mask every real token of the tile may be removed; -inf then gives weight 0
-                // against the (always finite) reference maximum.
-                constexpr float kOut = MASK ? -INFINITY : kNegBig;
+                // Rows past the end of the sequence score -inf: weight 0 against the (always finite) reference
+                // maximum, also where no row of the tile is left (an empty sequence, or a mask that removes every
+                // real token of the tile).
+                constexpr float kOut = -INFINITY;
                 if (nvalid < kTileTok) {  // only the last tile of a sequence has rows past its end
                     if (g >= nvalid) {
                         s0 = kOut;
@@ -772,19 +795,22 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                         s3 = kOut;
                     }
                 }
+                const float sc = MASK ? 1.0f : a.scale_log2;  // what is left to apply to s0..s3
                 {
                     float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
-                    const bool need = (lm0 > m0 + kRescaleSlack) || (lm1 > m1 + kRescaleSlack);
+                    const bool need = (lm0 > thr0) || (lm1 > thr1);
                     if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
                         for (int off = 4; off <= 16; off <<= 1) {
                             lm0 = fmaxf(lm0, __shfl_xor_sync(0xffffffffu, lm0, off));
                             lm1 = fmaxf(lm1, __shfl_xor_sync(0xffffffffu, lm1, off));
                         }
-                        const float n0 = fmaxf(m0, lm0), n1 = fmaxf(m1, lm1);
+                        const float n0 = fmaxf(m0, lm0 * sc), n1 = fmaxf(m1, lm1 * sc);
                         const float r0 = ex2_approx(m0 - n0), r1 = ex2_approx(m1 - n1);
                         m0 = n0;
                         m1 = n1;
+                        thr0 = (m0 + kRescaleSlack) * inv_sc;
+                        thr1 = (m1 + kRescaleSlack) * inv_sc;
                         l0 *= r0;
                         l1 *= r1;
 #pragma unroll
@@ -796,15 +822,14 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                         }
                     }
                 }
-                const float p0 = ex2_approx(s0 - m0), p1 = ex2_approx(s1 - m1);
-                const float p2 = ex2_approx(s2 - m0), p3 = ex2_approx(s3 - m1);
+                const float p0 = ex2_approx(fmaf(s0, sc, -m0)), p1 = ex2_approx(fmaf(s1, sc, -m1));
+                const float p2 = ex2_approx(fmaf(s2, sc, -m0)), p3 = ex2_approx(fmaf(s3, sc, -m1));
                 // The MMA consumes P rounded to fp16, so the normaliser sums the SAME rounded values: a
                 // rounding of p then cancels between numerator and denominator (exactly so when one token
                 // dominates), which keeps the output within one fp16 ulp of an fp32 evaluation.
                 const __half2 ph01 = __floats2half2_rn(p0, p1), ph23 = __floats2half2_rn(p2, p3);
-                const float2 pf01 = __half22float2(ph01), pf23 = __half22float2(ph23);
-                l0 += pf01.x + pf23.x;
-                l1 += pf01.y + pf23.y;
+                add_halves_to_floats(l0, l1, h2_as_u32(ph01));
+                add_halves_to_floats(l0, l1, h2_as_u32(ph23));
                 // P^T as the B operand of the second MMA: k = token, n = head
                 const uint32_t pb0 = movmatrix_trans(h2_as_u32(ph01));
                 const uint32_t pb1 = movmatrix_trans(h2_as_u32(ph23));
@@ -866,14 +891,12 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                     asm volatile("bar.sync %0, %1;" ::"r"(1 + sub), "r"(head_lanes * 32) : "memory");
                 }
                 __syncwarp();  // every lane has read this stage: it may be refilled
-                if (!wait_dead) {
-                    if (++c_stage == kStages) {
-                        c_stage = 0;
-                        c_phase ^= 1u;
-                    }
-                    if (to_issue > 0) {
-                        issue_one();
-                    }
+                if (++c_stage == kStages) {
+                    c_stage = 0;
+                    c_phase ^= 1u;
+                }
+                if (to_issue > 0) {  // never after the warp has given up
+                    issue_one();
                 }
             }
 
@@ -928,12 +951,12 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
     }
     if (wait_dead) {
         // Copies that were in flight when the warp gave up may still land in this CTA's shared memory: give
-        // each of them one more bounded wait (frozen consume position onwards) before the CTA may exit.
+        // each of them one more bounded wait (from the ring position recorded then) before the CTA may exit.
         for (int32_t i = 0; i < dead_inflight && i < kStages; ++i) {
-            mbar_wait_bounded(reinterpret_cast<uint64_t*>(full_bar + warp * kStages + c_stage), c_phase);
-            if (++c_stage == kStages) {
-                c_stage = 0;
-                c_phase ^= 1u;
+            mbar_wait_bounded(reinterpret_cast<uint64_t*>(full_bar + warp * kStages + dead_stage), dead_phase);
+            if (++dead_stage == kStages) {
+                dead_stage = 0;
+                dead_phase ^= 1u;
             }
         }
     }
