@@ -38,6 +38,7 @@ class Spec:
     outlier_k: bool = False
     peaked: bool = False
     is_causal: bool = True
+    pf_skip: int = 0  # decode lengths drawn and dropped before the prompts (the prompts of a mixed spec on their own)
 
 
 SPECS = {
@@ -49,7 +50,8 @@ SPECS = {
     "cfg3_llama8b_mixed": Spec("cfg3_llama8b_mixed", 32, 8, 128, 248, 256, 8192, n_prefill=8, pf_lo=512, pf_hi=2048,
                                seed=2),
     # the prefill half of the mixed step alone (for the tensor-core roofline of the prefill kernel)
-    "cfg3_prefill_only": Spec("cfg3_prefill_only", 32, 8, 128, 0, 1, 1, n_prefill=8, pf_lo=512, pf_hi=2048, seed=2),
+    "cfg3_prefill_only": Spec("cfg3_prefill_only", 32, 8, 128, 0, 256, 8192, n_prefill=8, pf_lo=512, pf_hi=2048, seed=2,
+                              pf_skip=248),
     # the same layer with 16 prompts of 4096 tokens: the steady state of the prefill kernel (not a BASELINE config)
     "prefill_16x4096": Spec("prefill_16x4096", 32, 8, 128, 0, 1, 1, n_prefill=16, pf_lo=4096, pf_hi=4096, seed=5),
     # LLaMA-2-70B attention layer, large-batch decode
@@ -106,6 +108,8 @@ def draw_lengths(spec: Spec):
         kv = np.clip(kv, spec.kv_lo, spec.kv_hi)
     else:
         kv = rng.integers(spec.kv_lo, spec.kv_hi + 1, spec.n_decode).astype(np.int64)
+        if spec.pf_skip:
+            rng.integers(spec.kv_lo, spec.kv_hi + 1, spec.pf_skip)
     pf = rng.integers(spec.pf_lo, spec.pf_hi + 1, spec.n_prefill).astype(np.int64) if spec.n_prefill else \
         np.zeros(0, dtype=np.int64)
     return kv, pf
