@@ -29,6 +29,8 @@ kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict
     const int32_t groups_per_tensor_row = num_kv_heads << group_shift;
     const int32_t groups_per_token = 2 * groups_per_tensor_row;
     const int32_t row_elems = num_kv_heads * head_dim;  // one token row of K (or V)
+    // a cache row that holds K and V of all heads back to back: the offset of a group is its index
+    const bool dense_row = geom.stride_h == head_dim && geom.stride_kv == row_elems;
     for (WarpItems it(groups_per_token); it.tok < total_tokens; it.next()) {
         // the payload loads go out before the lookups, which then overlap with them; the 64-bit part of every
         // address is formed once per token, the rest is 32-bit arithmetic on the group index
@@ -65,9 +67,12 @@ kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict
             __half s16;
             quant_group8(in[c], codes, s16);
             if (g < groups_per_token) {
-                int kv, head, grp;
-                split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
-                const int64_t off = kv * geom.stride_kv + head * geom.stride_h + grp * 8;
+                int64_t off = static_cast<int64_t>(g) * 8;  // K then V of all heads back to back (layout 0)
+                if (!dense_row) {
+                    int kv, head, grp;
+                    split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
+                    off = kv * geom.stride_kv + head * geom.stride_h + grp * 8;
+                }
                 *reinterpret_cast<uint2*>(c_row + off) = codes;
                 s_row[off >> 3] = s16;
             }
