@@ -299,6 +299,19 @@ def test_fast_quantiser_path_of_the_cuda_kernels_gives_the_exact_codes(oracle_mo
     assert total_fast > 1_000_000  # the fast path is the common case, so the check is not vacuous
 
 
+def test_scale_by_reciprocal_equals_the_division_for_every_half():
+    """The CUDA quantiser computes the group scale as fp16(a * fl(1/127)) instead of fp16(fl(a / 127)).  The
+    maximum a is itself an fp16 number, so the claim can be checked for every one of them: the two agree bit
+    for bit, also with the constant one ulp off either way (the margin the argument in common.cuh gives)."""
+    a = np.arange(0, 0x7C01, dtype=np.uint16).view(np.float16).astype(np.float32)  # every non-negative half, +inf
+    with np.errstate(over="ignore"):
+        ref = (a / np.float32(127.0)).astype(np.float32).astype(np.float16).view(np.uint16)
+        r = np.float32(1.0) / np.float32(127.0)
+        for c in (r, np.nextafter(r, np.float32(1)), np.nextafter(r, np.float32(0))):
+            got = (a * c).astype(np.float32).astype(np.float16).view(np.uint16)
+            np.testing.assert_array_equal(got, ref)
+
+
 @pytest.mark.parametrize("cache_prefill", [False, True])
 def test_cached_operator_mask_matches_numpy(pkg, orc, oracle_mod, cache_prefill):
     """attn_mask in orc_mhca against numpy over the dequantised rows: decode rows read the cache from position 0,
