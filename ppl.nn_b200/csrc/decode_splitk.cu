@@ -382,7 +382,14 @@ struct Cursor {
     int32_t kvh;
 };
 
-template <int DH, int ORDER, bool MASK>
+// KDOT (one query head per kv head, no mask): the scores come from integer dot products instead of the
+// tensor cores.  With a single query head the MMA's eight columns hold one useful number, while its A
+// operand still wants every key dequantised to fp16 (21 instructions per 8 codes with the remainder).  The
+// query row is instead quantised once per piece to int16 with one fp32 scale per 8-channel group
+// (|error| <= 2^-16 of the group's largest element), and a group's partial score is dp2a(codes, q) -- exact in
+// int32 -- times the key scale times the query scale: 8 instructions per 8 codes and keys that are exact by
+// construction.  V, the softmax bookkeeping and the output go through the MMA as before.
+template <int DH, int ORDER, bool MASK, bool KDOT>
 __global__ void __launch_bounds__(kThreads, kCtasPerSm)
 decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const DecodeArgs a) {
     using T = Traits<DH>;
@@ -637,9 +644,35 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             kvlen64 = kvlen64 > a.max_kvlen ? a.max_kvlen : kvlen64;
             const int32_t kvlen = static_cast<int32_t>(kvlen64);
 
+            // KDOT: this lane's quarter of the query row as int16 pairs, one scale per group of 8 channels
+            int32_t qi[KDOT ? DH / 8 : 1];
+            float qs[KDOT ? DH / 32 : 1];
+            if constexpr (KDOT) {
+                const __half* qp = a.q + (qtok * a.num_heads + kvh) * DH + t * (DH / 4);
+#pragma unroll
+                for (int gi = 0; gi < DH / 32; ++gi) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(qp + 8 * gi);
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&v);
+                    float2 f[4];
+                    float amax = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        f[i] = __half22float2(h2[i]);
+                        amax = max3_nan(amax, fabsf(f[i].x), fabsf(f[i].y));  // a NaN or infinite query element
+                        // must reach the scores (0 * inf below), as it does through the MMA
+                    }
+                    const float inv = amax > 0.0f ? 32767.0f / amax : 0.0f;
+                    qs[gi] = amax * (1.0f / 32767.0f);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int lo = __float2int_rn(f[i].x * inv), hi = __float2int_rn(f[i].y * inv);
+                        qi[4 * gi + i] = static_cast<int32_t>((static_cast<uint32_t>(lo) & 0xffffu) | (static_cast<uint32_t>(hi) << 16));
+                    }
+                }
+            }
             // Q fragments (B operand: k = channel, n = query head of the group)
             uint32_t qf[T::kKRegs][2];
-            {
+            if constexpr (!KDOT) {
                 const int hq_in_group = oct * 8 + g;
                 if (hq_in_group < a.group) {
                     const __half* qp = a.q + (qtok * a.num_heads + kvh * a.group + hq_in_group) * DH + t * (DH / 4);
@@ -738,6 +771,32 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                         sa[0] = lds32(st + ks_off);
                         sb[0] = lds32(st + ks_off + 128u);
                     }
+                    if constexpr (KDOT) {
+                        // rows g and g+8 against the one query head: per group an exact integer dot product,
+                        // scaled by key scale x query scale; the quad then adds up its four quarter rows
+                        float acc_a = 0.0f, acc_b = 0.0f;
+#pragma unroll
+                        for (int gi = 0; gi < DH / 32; ++gi) {
+                            int da = 0, db = 0;
+#pragma unroll
+                            for (int w = 0; w < 2; ++w) {
+                                const int rr = 2 * gi + w;
+                                da = __dp2a_lo(qi[2 * rr], static_cast<int>(wa[rr]), da);
+                                da = __dp2a_hi(qi[2 * rr + 1], static_cast<int>(wa[rr]), da);
+                                db = __dp2a_lo(qi[2 * rr], static_cast<int>(wb[rr]), db);
+                                db = __dp2a_hi(qi[2 * rr + 1], static_cast<int>(wb[rr]), db);
+                            }
+                            const float2 fa = __half22float2(u32_as_h2(sa[gi >> 1])), fb = __half22float2(u32_as_h2(sb[gi >> 1]));
+                            acc_a = fmaf(__int2float_rn(da), ((gi & 1) ? fa.y : fa.x) * qs[gi], acc_a);
+                            acc_b = fmaf(__int2float_rn(db), ((gi & 1) ? fb.y : fb.x) * qs[gi], acc_b);
+                        }
+                        acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
+                        acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
+                        acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 2);
+                        acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 2);
+                        sacc[0] = acc_a;  // token g
+                        sacc[2] = acc_b;  // token g + 8
+                    } else {
 #pragma unroll
                     for (int rr = 0; rr < T::kKRegs; ++rr) {
                         // word rr holds channels 4rr..4rr+3 of the slab: quantisation group rr/2 of the slab
@@ -752,87 +811,128 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                         mma_m16n8k16_f16f32(sacc, e0, e1, e2, e3, qf[rr][0], qf[rr][1]);
 #endif
                     }
+                    }
                 }
 
                 // ---------------- softmax (exp2 domain, lazy reference maximum) ----------------
                 // Raw scores: token g / g+8, heads 2t / 2t+1.  Without a mask they stay unscaled: the growth test
                 // compares them with thresholds kept in raw units (thr = (m + slack) / scale, updated only when the
                 // reference maximum moves), and scale and maximum enter the exponent through one FMA.
-                float s0 = sacc[0], s1 = sacc[1], s2 = sacc[2], s3 = sacc[3];
-                if constexpr (MASK) {  // additive mask on the scaled scores (exp2 domain: times log2 e)
-                    constexpr float kLog2e = 1.4426950408889634f;
-                    s0 *= a.scale_log2;
-                    s1 *= a.scale_log2;
-                    s2 *= a.scale_log2;
-                    s3 *= a.scale_log2;
-                    const int64_t p0 = static_cast<int64_t>(tile) * kTileTok + g, p1 = p0 + 8;
-                    const bool in0 = p0 < kvlen && p0 < mask_room, in1 = p1 < kvlen && p1 < mask_room;
-                    if (mrow0) {
-                        if (in0) s0 = fmaf(__half2float(mrow0[p0]), kLog2e, s0);
-                        if (in1) s2 = fmaf(__half2float(mrow0[p1]), kLog2e, s2);
+                uint32_t pb0, pb1;  // P^T as the B operand of the second MMA: k = token, n = head
+                if constexpr (KDOT) {
+                    // one head: every lane of quad g holds the raw scores of tokens g and g + 8
+                    float sa_ = sacc[0], sb_ = sacc[2];
+                    if (nvalid < kTileTok) {  // rows past the end of the sequence weigh nothing
+                        sa_ = g < nvalid ? sa_ : -INFINITY;
+                        sb_ = g + 8 < nvalid ? sb_ : -INFINITY;
                     }
-                    if (mrow1) {
-                        if (in0) s1 = fmaf(__half2float(mrow1[p0]), kLog2e, s1);
-                        if (in1) s3 = fmaf(__half2float(mrow1[p1]), kLog2e, s3);
-                    }
-                    // +inf or NaN in a mask would poison the running maximum: such entries count as "masked out"
-                    s0 = s0 < 3.0e38f ? s0 : -INFINITY;
-                    s1 = s1 < 3.0e38f ? s1 : -INFINITY;
-                    s2 = s2 < 3.0e38f ? s2 : -INFINITY;
-                    s3 = s3 < 3.0e38f ? s3 : -INFINITY;
-                }
-                // Rows past the end of the sequence score -inf: weight 0 against the (always finite) reference
-                // maximum, also where no row of the tile is left (an empty sequence, or a mask that removes every
-                // real token of the tile).
-                constexpr float kOut = -INFINITY;
-                if (nvalid < kTileTok) {  // only the last tile of a sequence has rows past its end
-                    if (g >= nvalid) {
-                        s0 = kOut;
-                        s1 = kOut;
-                    }
-                    if (g + 8 >= nvalid) {
-                        s2 = kOut;
-                        s3 = kOut;
-                    }
-                }
-                const float sc = MASK ? 1.0f : a.scale_log2;  // what is left to apply to s0..s3
-                {
-                    float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
-                    const bool need = (lm0 > thr0) || (lm1 > thr1);
-                    if (__any_sync(0xffffffffu, need)) {
+                    const float sc = a.scale_log2;
+                    float lm = fmaxf(sa_, sb_);
+                    if (__any_sync(0xffffffffu, lm > thr0)) {
 #pragma unroll
                         for (int off = 4; off <= 16; off <<= 1) {
-                            lm0 = fmaxf(lm0, __shfl_xor_sync(0xffffffffu, lm0, off));
-                            lm1 = fmaxf(lm1, __shfl_xor_sync(0xffffffffu, lm1, off));
+                            lm = fmaxf(lm, __shfl_xor_sync(0xffffffffu, lm, off));
                         }
-                        const float n0 = fmaxf(m0, lm0 * sc), n1 = fmaxf(m1, lm1 * sc);
-                        const float r0 = ex2_approx(m0 - n0), r1 = ex2_approx(m1 - n1);
+                        const float n0 = fmaxf(m0, lm * sc);
+                        const float r0 = ex2_approx(m0 - n0);
                         m0 = n0;
-                        m1 = n1;
                         thr0 = (m0 + kRescaleSlack) * inv_sc;
-                        thr1 = (m1 + kRescaleSlack) * inv_sc;
                         l0 *= r0;
-                        l1 *= r1;
 #pragma unroll
                         for (int i = 0; i < T::kMTiles; ++i) {
                             o[i][0] *= r0;
-                            o[i][1] *= r1;
+                            o[i][1] *= r0;
                             o[i][2] *= r0;
-                            o[i][3] *= r1;
+                            o[i][3] *= r0;
                         }
                     }
+                    // the normaliser sums the fp16-rounded weights, the very numbers the MMA consumes
+                    const uint32_t ph = h2_as_u32(__floats2half2_rn(ex2_approx(fmaf(sa_, sc, -m0)), ex2_approx(fmaf(sb_, sc, -m0))));
+                    float l_hi = 0.0f;
+                    add_halves_to_floats(l0, l_hi, ph);
+                    l0 += l_hi;
+                    // B fragment of lane (g', t'): tokens 2t', 2t'+1 and 2t'+8, 2t'+9 of head g' -- the one real head
+                    // is g' = 0; the other columns get the same weights and their outputs are never stored
+                    const uint32_t x = __shfl_sync(0xffffffffu, ph, 8 * t), y = __shfl_sync(0xffffffffu, ph, 8 * t + 4);
+                    pb0 = prmt(x, y, 0x5410u);
+                    pb1 = prmt(x, y, 0x7632u);
+                } else {
+                    float s0 = sacc[0], s1 = sacc[1], s2 = sacc[2], s3 = sacc[3];
+                    if constexpr (MASK) {  // additive mask on the scaled scores (exp2 domain: times log2 e)
+                        constexpr float kLog2e = 1.4426950408889634f;
+                        s0 *= a.scale_log2;
+                        s1 *= a.scale_log2;
+                        s2 *= a.scale_log2;
+                        s3 *= a.scale_log2;
+                        const int64_t p0 = static_cast<int64_t>(tile) * kTileTok + g, p1 = p0 + 8;
+                        const bool in0 = p0 < kvlen && p0 < mask_room, in1 = p1 < kvlen && p1 < mask_room;
+                        if (mrow0) {
+                            if (in0) s0 = fmaf(__half2float(mrow0[p0]), kLog2e, s0);
+                            if (in1) s2 = fmaf(__half2float(mrow0[p1]), kLog2e, s2);
+                        }
+                        if (mrow1) {
+                            if (in0) s1 = fmaf(__half2float(mrow1[p0]), kLog2e, s1);
+                            if (in1) s3 = fmaf(__half2float(mrow1[p1]), kLog2e, s3);
+                        }
+                        // +inf or NaN in a mask would poison the running maximum: such entries count as "masked out"
+                        s0 = s0 < 3.0e38f ? s0 : -INFINITY;
+                        s1 = s1 < 3.0e38f ? s1 : -INFINITY;
+                        s2 = s2 < 3.0e38f ? s2 : -INFINITY;
+                        s3 = s3 < 3.0e38f ? s3 : -INFINITY;
+                    }
+                    // Rows past the end of the sequence score -inf: weight 0 against the (always finite) reference
+                    // maximum, also where no row of the tile is left (an empty sequence, or a mask that removes every
+                    // real token of the tile).
+                    constexpr float kOut = -INFINITY;
+                    if (nvalid < kTileTok) {  // only the last tile of a sequence has rows past its end
+                        if (g >= nvalid) {
+                            s0 = kOut;
+                            s1 = kOut;
+                        }
+                        if (g + 8 >= nvalid) {
+                            s2 = kOut;
+                            s3 = kOut;
+                        }
+                    }
+                    const float sc = MASK ? 1.0f : a.scale_log2;  // what is left to apply to s0..s3
+                    {
+                        float lm0 = fmaxf(s0, s2), lm1 = fmaxf(s1, s3);
+                        const bool need = (lm0 > thr0) || (lm1 > thr1);
+                        if (__any_sync(0xffffffffu, need)) {
+    #pragma unroll
+                            for (int off = 4; off <= 16; off <<= 1) {
+                                lm0 = fmaxf(lm0, __shfl_xor_sync(0xffffffffu, lm0, off));
+                                lm1 = fmaxf(lm1, __shfl_xor_sync(0xffffffffu, lm1, off));
+                            }
+                            const float n0 = fmaxf(m0, lm0 * sc), n1 = fmaxf(m1, lm1 * sc);
+                            const float r0 = ex2_approx(m0 - n0), r1 = ex2_approx(m1 - n1);
+                            m0 = n0;
+                            m1 = n1;
+                            thr0 = (m0 + kRescaleSlack) * inv_sc;
+                            thr1 = (m1 + kRescaleSlack) * inv_sc;
+                            l0 *= r0;
+                            l1 *= r1;
+    #pragma unroll
+                            for (int i = 0; i < T::kMTiles; ++i) {
+                                o[i][0] *= r0;
+                                o[i][1] *= r1;
+                                o[i][2] *= r0;
+                                o[i][3] *= r1;
+                            }
+                        }
+                    }
+                    const float p0 = ex2_approx(fmaf(s0, sc, -m0)), p1 = ex2_approx(fmaf(s1, sc, -m1));
+                    const float p2 = ex2_approx(fmaf(s2, sc, -m0)), p3 = ex2_approx(fmaf(s3, sc, -m1));
+                    // The MMA consumes P rounded to fp16, so the normaliser sums the SAME rounded values: a
+                    // rounding of p then cancels between numerator and denominator (exactly so when one token
+                    // dominates), which keeps the output within one fp16 ulp of an fp32 evaluation.
+                    const __half2 ph01 = __floats2half2_rn(p0, p1), ph23 = __floats2half2_rn(p2, p3);
+                    add_halves_to_floats(l0, l1, h2_as_u32(ph01));
+                    add_halves_to_floats(l0, l1, h2_as_u32(ph23));
+                    // P^T as the B operand of the second MMA: k = token, n = head
+                    pb0 = movmatrix_trans(h2_as_u32(ph01));
+                    pb1 = movmatrix_trans(h2_as_u32(ph23));
                 }
-                const float p0 = ex2_approx(fmaf(s0, sc, -m0)), p1 = ex2_approx(fmaf(s1, sc, -m1));
-                const float p2 = ex2_approx(fmaf(s2, sc, -m0)), p3 = ex2_approx(fmaf(s3, sc, -m1));
-                // The MMA consumes P rounded to fp16, so the normaliser sums the SAME rounded values: a
-                // rounding of p then cancels between numerator and denominator (exactly so when one token
-                // dominates), which keeps the output within one fp16 ulp of an fp32 evaluation.
-                const __half2 ph01 = __floats2half2_rn(p0, p1), ph23 = __floats2half2_rn(p2, p3);
-                add_halves_to_floats(l0, l1, h2_as_u32(ph01));
-                add_halves_to_floats(l0, l1, h2_as_u32(ph23));
-                // P^T as the B operand of the second MMA: k = token, n = head
-                const uint32_t pb0 = movmatrix_trans(h2_as_u32(ph01));
-                const uint32_t pb1 = movmatrix_trans(h2_as_u32(ph23));
 
                 // ---------------- O^T += V^T * P^T ----------------
                 {
@@ -901,6 +1001,10 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
             }
 
             // ---------------- end of the piece: write fp16 output or an fp32 partial ----------------
+            if constexpr (KDOT) {  // columns 1.. of the fragments are copies of head 0's
+                m1 = m0;
+                l1 = l0;
+            }
 #pragma unroll
             for (int off = 4; off <= 16; off <<= 1) {
                 l0 += __shfl_xor_sync(0xffffffffu, l0, off);
@@ -1139,6 +1243,13 @@ int decode_oversubscription() {
     return (n >= 1 && n <= 16) ? n : PPLB200_DECODE_OVERSUB_DEFAULT;
 }
 
+// PPLB200_DECODE_KDOT=0 sends one-head-per-kv-head batches through the tensor-core scores as well (A/B
+// measurements only; read per call).
+static bool decode_kdot_enabled() {
+    const char* e = getenv("PPLB200_DECODE_KDOT");
+    return !(e && e[0] == '0');
+}
+
 static int map_order_kind(const CacheMapOrder& od) {
     if (od.pos_head == 1 && od.pos_kv == 2 && od.pos_layer == 3 && od.pos_row == 4) {
         return kOrderRowLast;
@@ -1149,7 +1260,7 @@ static int map_order_kind(const CacheMapOrder& od) {
     return kOrderGeneric;
 }
 
-template <int DH, int ORDER, bool MASK>
+template <int DH, int ORDER, bool MASK, bool KDOT>
 static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t grid, cudaStream_t stream) {
     using T = Traits<DH>;
     // the attribute belongs to the (kernel, device) pair: remembered per template instance and device
@@ -1160,7 +1271,7 @@ static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t
     }
     bool& attr_set = attr_set_on[dev_id];
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(decode_splitk_kernel<DH, ORDER, MASK>,
+        cudaError_t e = cudaFuncSetAttribute(decode_splitk_kernel<DH, ORDER, MASK, KDOT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
         if (e != cudaSuccess) {
             fprintf(stderr, "[ppl_nn_b200] cudaFuncSetAttribute(decode_splitk_kernel): %s\n", cudaGetErrorString(e));
@@ -1170,7 +1281,7 @@ static int launch_main(const CUtensorMap& tm_codes, const DecodeArgs& a, int64_t
     }
     {
         KernelTimer timer(PPLB200_KERNEL_DECODE, stream);
-        launch_dependent(decode_splitk_kernel<DH, ORDER, MASK>, dim3(static_cast<unsigned>(grid)), dim3(kThreads),
+        launch_dependent(decode_splitk_kernel<DH, ORDER, MASK, KDOT>, dim3(static_cast<unsigned>(grid)), dim3(kThreads),
                          T::kSmemBytes, stream, tm_codes, a);
     }
     return check_launch("decode_splitk_kernel");
@@ -1260,12 +1371,18 @@ static int launch_decode_dh(const pplb200_attn_params& p, const CacheGeom& geom,
     a.mask = mask;
 
     if (a.mask.data != nullptr) {  // the mask path need not be the fastest: one instance, run-time coordinate order
-        rc = launch_main<DH, kOrderGeneric, true>(tm_codes, a, grid, stream);
+        rc = launch_main<DH, kOrderGeneric, true, false>(tm_codes, a, grid, stream);
+    } else if (a.group == 1 && decode_kdot_enabled()) {  // one query head per kv head: integer-dot scores
+        switch (map_order_kind(order)) {
+            case kOrderRowLast: rc = launch_main<DH, kOrderRowLast, false, true>(tm_codes, a, grid, stream); break;
+            case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst, false, true>(tm_codes, a, grid, stream); break;
+            default: rc = launch_main<DH, kOrderGeneric, false, true>(tm_codes, a, grid, stream); break;
+        }
     } else {
         switch (map_order_kind(order)) {
-            case kOrderRowLast: rc = launch_main<DH, kOrderRowLast, false>(tm_codes, a, grid, stream); break;
-            case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst, false>(tm_codes, a, grid, stream); break;
-            default: rc = launch_main<DH, kOrderGeneric, false>(tm_codes, a, grid, stream); break;
+            case kOrderRowLast: rc = launch_main<DH, kOrderRowLast, false, false>(tm_codes, a, grid, stream); break;
+            case kOrderRowFirst: rc = launch_main<DH, kOrderRowFirst, false, false>(tm_codes, a, grid, stream); break;
+            default: rc = launch_main<DH, kOrderGeneric, false, false>(tm_codes, a, grid, stream); break;
         }
     }
     if (rc != PPLB200_SUCCESS) {

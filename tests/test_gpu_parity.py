@@ -113,6 +113,24 @@ def test_cfg2_mha_outlier_channels(orc, torch_dev, pkg, layout, num_layer, layer
     run_case(orc, torch_dev, workloads.host_case(spec), layout=layout, num_layer=num_layer, layer_idx=layer_idx)
 
 
+@pytest.mark.parametrize("dh", [128, 64])
+def test_one_head_per_kv_head_both_score_paths(orc, torch_dev, pkg, dh, monkeypatch):
+    """With one query head per kv head the decode kernel takes the scores from integer dot products
+    (codes x int16-quantised query) instead of the tensor cores; PPLB200_DECODE_KDOT=0 (read per call) sends
+    the same batch through the tensor-core scores.  Both must meet the tolerance, and they must agree with
+    one another far more closely than that (they differ only in how the keys are weighted, not in V)."""
+    from ppl_nn_b200 import workloads
+    spec = replace(workloads.scaled(workloads.SPECS["cfg2_llama7b_decode"], seqs=16 / 256, length=0.2), num_heads=8,
+                   num_kv_heads=8, head_dim=dh)
+    hc = workloads.host_case(spec)
+    outs = {}
+    for flag in ("1", "0"):
+        monkeypatch.setenv("PPLB200_DECODE_KDOT", flag)
+        run_case(orc, torch_dev, hc)
+        outs[flag] = run_case.last_output.copy()
+    assert np.abs(outs["1"] - outs["0"]).max() <= MAX_ABS
+
+
 @pytest.mark.parametrize("world", [1, 2, 8])
 def test_cfg4_gqa8_kv_head_shards(orc, torch_dev, pkg, world):
     """64 query / 8 kv heads, sharded by kv head: 8, 4 and 1 kv heads per rank exercise all three
