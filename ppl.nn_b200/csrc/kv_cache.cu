@@ -10,6 +10,11 @@
 
 namespace pplb200 {
 
+// FAST: every warp item lies wholly inside the K part or the V part of a token row (the row of one tensor is
+// a multiple of 32 * kChunks groups) and a cache row holds K and V of all heads back to back.  The source
+// and destination of an item are then one base address per warp plus the lane's offset: no bounds tests,
+// no per-lane choice between the two tensors, no group index arithmetic.
+template <bool FAST>
 __global__ void __launch_bounds__(256)
 kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict__ cur_v,
                       const int64_t* __restrict__ seqstarts, const int64_t* __restrict__ cachestarts,
@@ -31,50 +36,85 @@ kv_append_i8g8_kernel(const __half* __restrict__ cur_k, const __half* __restrict
     const int32_t row_elems = num_kv_heads * head_dim;  // one token row of K (or V)
     // a cache row that holds K and V of all heads back to back: the offset of a group is its index
     const bool dense_row = geom.stride_h == head_dim && geom.stride_kv == row_elems;
-    for (WarpItems it(groups_per_token); it.tok < total_tokens; it.next()) {
-        // the payload loads go out before the lookups, which then overlap with them; the 64-bit part of every
-        // address is formed once per token, the rest is 32-bit arithmetic on the group index
-        const __half* k_tok = cur_k + it.tok * row_elems;
-        const __half* v_tok = cur_v + it.tok * row_elems;
-        uint4 in[kChunks];
+    if constexpr (FAST) {
+        const int32_t items_per_tensor = groups_per_tensor_row / (32 * kChunks);
+        for (WarpItems it(groups_per_token); it.tok < total_tokens; it.next()) {
+            const bool is_v = it.chunk >= items_per_tensor;  // warp-uniform
+            const int32_t g0 = it.chunk * (32 * kChunks);    // first group of the item within the token row
+            const __half* src = (is_v ? cur_v : cur_k) + it.tok * row_elems +
+                                (g0 - (is_v ? groups_per_tensor_row : 0)) * 8 + lane * 8;
+            uint4 in[kChunks];
 #pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
-            in[c] = make_uint4(0u, 0u, 0u, 0u);
-            if (g < groups_per_token) {
-                // groups of a token row are laid out exactly like its channels: group r2 = channels 8 r2 ..
-                const bool is_v = g >= groups_per_tensor_row;
-                const int32_t r2 = g - (is_v ? groups_per_tensor_row : 0);
-                in[c] = *reinterpret_cast<const uint4*>((is_v ? v_tok : k_tok) + r2 * 8);
+            for (int c = 0; c < kChunks; ++c) {
+                in[c] = *reinterpret_cast<const uint4*>(src + c * 256);
             }
-        }
-        const int64_t tok = it.tok + tok_begin;
-        const int32_t b = warp_find_segment(seqstarts, batch, tok, lane);
-        const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (tok - seqstarts[b]));
-        if (!cache_row_ok(row, max_tokens)) {  // a wrong index tensor: flag it and leave the cache alone
-            if (lane == 0 && status != nullptr) {
-                atomicOr(status, kDevRowOutOfRange);
-            }
-            continue;
-        }
-        const int64_t row_off = row * geom.stride_s + geom.layer_idx * geom.stride_l;
-        int8_t* c_row = cache + row_off;
-        __half* s_row = scale + (row_off >> 3);
-#pragma unroll
-        for (int c = 0; c < kChunks; ++c) {
-            const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
-            uint2 codes;
-            __half s16;
-            quant_group8(in[c], codes, s16);
-            if (g < groups_per_token) {
-                int64_t off = static_cast<int64_t>(g) * 8;  // K then V of all heads back to back (layout 0)
-                if (!dense_row) {
-                    int kv, head, grp;
-                    split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
-                    off = kv * geom.stride_kv + head * geom.stride_h + grp * 8;
+            const int64_t tok = it.tok + tok_begin;
+            const int32_t b = warp_find_segment(seqstarts, batch, tok, lane);
+            const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (tok - seqstarts[b]));
+            if (!cache_row_ok(row, max_tokens)) {  // a wrong index tensor: flag it and leave the cache alone
+                if (lane == 0 && status != nullptr) {
+                    atomicOr(status, kDevRowOutOfRange);
                 }
-                *reinterpret_cast<uint2*>(c_row + off) = codes;
-                s_row[off >> 3] = s16;
+                continue;
+            }
+            const int64_t row_off = row * geom.stride_s + geom.layer_idx * geom.stride_l + static_cast<int64_t>(g0) * 8;
+            int8_t* c_dst = cache + row_off + lane * 8;
+            __half* s_dst = scale + (row_off >> 3) + lane;
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+                uint2 codes;
+                __half s16;
+                quant_group8(in[c], codes, s16);
+                *reinterpret_cast<uint2*>(c_dst + c * 256) = codes;
+                s_dst[c * 32] = s16;
+            }
+        }
+    } else {
+        for (WarpItems it(groups_per_token); it.tok < total_tokens; it.next()) {
+            // the payload loads go out before the lookups, which then overlap with them; the 64-bit part of every
+            // address is formed once per token, the rest is 32-bit arithmetic on the group index
+            const __half* k_tok = cur_k + it.tok * row_elems;
+            const __half* v_tok = cur_v + it.tok * row_elems;
+            uint4 in[kChunks];
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+                const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+                in[c] = make_uint4(0u, 0u, 0u, 0u);
+                if (g < groups_per_token) {
+                    // groups of a token row are laid out exactly like its channels: group r2 = channels 8 r2 ..
+                    const bool is_v = g >= groups_per_tensor_row;
+                    const int32_t r2 = g - (is_v ? groups_per_tensor_row : 0);
+                    in[c] = *reinterpret_cast<const uint4*>((is_v ? v_tok : k_tok) + r2 * 8);
+                }
+            }
+            const int64_t tok = it.tok + tok_begin;
+            const int32_t b = warp_find_segment(seqstarts, batch, tok, lane);
+            const int64_t row = cache_row(geom, cachestarts, b, start_pos[b] + (tok - seqstarts[b]));
+            if (!cache_row_ok(row, max_tokens)) {  // a wrong index tensor: flag it and leave the cache alone
+                if (lane == 0 && status != nullptr) {
+                    atomicOr(status, kDevRowOutOfRange);
+                }
+                continue;
+            }
+            const int64_t row_off = row * geom.stride_s + geom.layer_idx * geom.stride_l;
+            int8_t* c_row = cache + row_off;
+            __half* s_row = scale + (row_off >> 3);
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
+                const int32_t g = (it.chunk * kChunks + c) * 32 + lane;
+                uint2 codes;
+                __half s16;
+                quant_group8(in[c], codes, s16);
+                if (g < groups_per_token) {
+                    int64_t off = static_cast<int64_t>(g) * 8;  // K then V of all heads back to back (layout 0)
+                    if (!dense_row) {
+                        int kv, head, grp;
+                        split_group(g, groups_per_tensor_row, group_shift, kv, head, grp);
+                        off = kv * geom.stride_kv + head * geom.stride_h + grp * 8;
+                    }
+                    *reinterpret_cast<uint2*>(c_row + off) = codes;
+                    s_row[off >> 3] = s16;
+                }
             }
         }
     }
@@ -153,7 +193,11 @@ int launch_kv_append(const pplb200_attn_params& p, const CacheGeom& geom, const 
     const int64_t items_per_token = (2 * p.num_kv_heads * (p.head_dim / 8) + 32 * kChunks - 1) / (32 * kChunks);
     const int grid = grid_for(tokens * items_per_token * 32, 256, sm_count);  // a warp per item
     KernelTimer timer(PPLB200_KERNEL_APPEND, stream);
-    launch_dependent(kv_append_i8g8_kernel, dim3(grid), dim3(256), 0, stream, static_cast<const __half*>(cur_k),
+    const int64_t groups_per_tensor_row = static_cast<int64_t>(p.num_kv_heads) * (p.head_dim / 8);
+    const bool fast = groups_per_tensor_row % (32 * kChunks) == 0 && geom.stride_h == p.head_dim &&
+                      geom.stride_kv == static_cast<int64_t>(p.num_kv_heads) * p.head_dim;
+    auto kernel = fast ? kv_append_i8g8_kernel<true> : kv_append_i8g8_kernel<false>;
+    launch_dependent(kernel, dim3(grid), dim3(256), 0, stream, static_cast<const __half*>(cur_k),
                      static_cast<const __half*>(cur_v), seqstarts, cachestarts, start_pos, static_cast<int8_t*>(cache),
                      static_cast<__half*>(scale), geom, static_cast<int32_t>(p.batch), static_cast<int32_t>(first_seq),
                      p.total_tokens, p.max_tokens, status, p.num_kv_heads, p.head_dim);
