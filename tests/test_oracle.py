@@ -312,6 +312,35 @@ def test_scale_by_reciprocal_equals_the_division_for_every_half():
             np.testing.assert_array_equal(got, ref)
 
 
+def test_integer_dot_scores_of_the_decode_kernel(oracle_mod):
+    """With one query head per kv head the decode kernel quantises the query row to int16 with one fp32 scale
+    per 8-channel group and takes a group's partial score as the exact integer dot product of codes and
+    quantised query times key scale times query scale (csrc/decode_splitk.cu, KDOT).  Restated in numpy: the
+    score differs from the exactly dequantised one by at most 2^-16 of sum_g s_g * max|q_g| * sum|c|, and in
+    practice by a few 1e-6 relative to the score's own scale."""
+    rng = np.random.default_rng(23)
+    T, Dh = 512, 128
+    k = rng.standard_normal((T, Dh)).astype(np.float32)
+    k[:, ::16] *= 8.0  # outlier channels, as in the LLaMA-2-7B workload
+    codes, scales = oracle_mod.np_quant_groups(k.astype(np.float16).reshape(-1, 8))
+    c = codes.reshape(T, Dh // 8, 8).astype(np.int64)
+    s = scales.astype(np.float32).reshape(T, Dh // 8)
+    q = (rng.standard_normal(Dh) * rng.choice([0.01, 1.0, 30.0], Dh)).astype(np.float16).astype(np.float32)
+    qg = q.reshape(Dh // 8, 8)
+    amax = np.abs(qg).max(axis=1)
+    inv = np.where(amax > 0, np.float32(32767.0) / amax, 0).astype(np.float32)
+    qs = (amax * np.float32(1.0 / 32767.0)).astype(np.float32)
+    qi = np.rint((qg * inv[:, None]).astype(np.float32)).astype(np.int64)
+    assert np.abs(qi).max() <= 32767
+    idot = (c * qi[None]).sum(axis=2)                                  # exact in int32 on the device
+    assert np.abs(idot).max() < 2 ** 31
+    got = (idot.astype(np.float32) * (s * qs[None]).astype(np.float32)).astype(np.float64).sum(axis=1)
+    want = ((c * s[:, :, None].astype(np.float64)) * qg[None].astype(np.float64)).sum(axis=(1, 2))
+    bound = (s.astype(np.float64) * amax[None] * np.abs(c).sum(axis=2)).sum(axis=1) * 2.0 ** -16 + 1e-6 * np.abs(want).max()
+    assert (np.abs(got - want) <= bound).all()
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
+
+
 @pytest.mark.parametrize("cache_prefill", [False, True])
 def test_cached_operator_mask_matches_numpy(pkg, orc, oracle_mod, cache_prefill):
     """attn_mask in orc_mhca against numpy over the dequantised rows: decode rows read the cache from position 0,
