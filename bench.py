@@ -62,8 +62,8 @@ DTYPE = "fp16 in/out, int8 cache, fp32 accumulate"
 
 # DRAM bytes moved by decode_splitk_kernel per algorithmic byte, from an ncu capture of one launch on one
 # eighth of the headline workload (dram__bytes_read.sum + dram__bytes_write.sum over the algorithmic bytes
-# of the captured launch: 692.67 MB + 5.64 MB for 690.86 MB); traffic grows in proportion to cached tokens.
-DECODE_TRAFFIC_PER_ALGO_BYTE = 1.0108
+# of the captured launch: 693.08 MB + 4.61 MB for 690.86 MB); traffic grows in proportion to cached tokens.
+DECODE_TRAFFIC_PER_ALGO_BYTE = 1.0099
 
 PER_CONFIG = (  # (workload, enable_cache_prefill)
     ("cfg3_llama8b_mixed", False),
