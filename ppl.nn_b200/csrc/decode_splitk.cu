@@ -409,9 +409,11 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
         mbar_fence_init();
         tma_prefetch_desc(&tmap_codes);
     }
-    grid_launch_dependents();
     __syncthreads();
     grid_dependency_wait();  // from here on: the plan, and the cache rows the append kernel wrote
+    // The merge kernel may be scheduled from here on: the plan is complete and visible, so the merge kernel can
+    // read the plan and work out its segments ahead of its own wait for this grid.
+    grid_launch_dependents();
 
     // shared-space addresses of this warp's stage ring (1 KB aligned for the 128-byte swizzle) and barriers
     const uint32_t wsm = ((smem_u32(smem_raw) + 1023u) & ~1023u) + warp * T::kWarpBytes;
@@ -1077,14 +1079,12 @@ decode_reduce_kernel(const PlanHeader* __restrict__ hdr, const int32_t* __restri
                      const int64_t* __restrict__ seqstarts, __half* __restrict__ out, int32_t decoding_batches,
                      int32_t num_heads, int32_t group, int32_t octets, int32_t head_lanes, int32_t class_heads) {
     grid_launch_dependents();
-    grid_dependency_wait();
-    if (hdr->per_segment) {
-        return;  // split-k off: every segment was written whole
-    }
+    // The plan (header, tile prefix sums) was complete before the decode grid let this grid be scheduled, so
+    // the segment geometry is worked out first; only the partials need the decode grid to have finished.
     const int64_t wg = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
-    if (wg >= static_cast<int64_t>(decoding_batches) * num_heads) {
-        return;
+    if (hdr->per_segment || wg >= static_cast<int64_t>(decoding_batches) * num_heads) {
+        return;  // split-k off (every segment was written whole), or no such (sequence, head)
     }
     const int32_t b = static_cast<int32_t>(wg / num_heads);
     const int32_t qh = static_cast<int32_t>(wg - static_cast<int64_t>(b) * num_heads);
@@ -1103,6 +1103,7 @@ decode_reduce_kernel(const PlanHeader* __restrict__ hdr, const int32_t* __restri
     if (r_first == r_last) {
         return;  // the segment lies inside one range and was written whole
     }
+    grid_dependency_wait();  // the partials of the decode grid
     auto slot_of = [&](int64_t rr) -> int64_t {
         // the piece is the range's first piece unless the segment starts strictly inside the range
         const int64_t s = (rr == r_first && seg_lo > rr * R) ? 1 : 0;
