@@ -48,20 +48,12 @@ namespace pplb200 {
 
 namespace {
 
-// Two shapes of the kernel (compile time):
-//   narrow (PPLB200_PF_WIDE 0)  64-row kv blocks, one score buffer, two CTAs per SM (256 TMEM columns each)
-//   wide   (PPLB200_PF_WIDE 1)  128-row kv blocks, two score buffers, one CTA per SM (all 512 TMEM columns)
-#ifndef PPLB200_PF_WIDE
-#define PPLB200_PF_WIDE 0
-#endif
-constexpr bool kWide = PPLB200_PF_WIDE != 0;
-constexpr int kBlockM = 128;                // query rows per CTA
-constexpr int kBlockN = kWide ? 128 : 64;   // kv rows per tile
-constexpr int kThreads = 192;               // 6 warps
-constexpr int kKStages = kWide ? 2 : 3;
+constexpr int kBlockM = 128;    // query rows per CTA
+constexpr int kBlockN = 64;     // kv rows per block
+constexpr int kThreads = 192;   // 6 warps
+constexpr int kKStages = 3;
 constexpr int kVStages = 2;
-constexpr int kCtasPerSm = kWide ? 1 : 2;
-constexpr int kSBufs = kWide ? 2 : 1;       // score buffers in TMEM: Q K^T runs this many kv blocks ahead of the softmax
+constexpr int kCtasPerSm = 2;
 constexpr int kTileRing = 4;      // tile indices in flight between the producer and the other roles
 constexpr int kCounterWord = 16;  // the tile counter is this many 32-bit words after the status word
 constexpr float kNegBig = -1.0e30f;
@@ -79,9 +71,9 @@ struct PTraits {
     // and the two 256-column TMEM allocations always fit.
     static constexpr int kSmemBytes = 32768 + (kKStages + kVStages) * (kBlockN * 256) + kBarrierBytes;
     static constexpr uint32_t kPCols = kBlockN / 2;              // packed fp16: two kv columns per TMEM column
-    // TMEM columns: S (kSBufs x kBlockN) | P0 | P1 | O (128)
-    static constexpr uint32_t kColS = 0, kColP = kSBufs * kBlockN, kColO = kColP + 2 * kPCols;
-    static constexpr uint32_t kTmemCols = kWide ? 512 : 256;
+    // TMEM columns: S (64) | P0 | P1 | O (128)
+    static constexpr uint32_t kColS = 0, kColP = kBlockN, kColO = kColP + 2 * kPCols;
+    static constexpr uint32_t kTmemCols = 256;
 };
 
 struct PrefillArgs {
@@ -125,8 +117,8 @@ struct Barriers {
     uint64_t v_full[kVStages];
     uint64_t k_empty[kKStages];
     uint64_t v_empty[kVStages];
-    uint64_t s_full[kSBufs];
-    uint64_t s_free[kSBufs];
+    uint64_t s_full;
+    uint64_t s_free;
     uint64_t p_full[2];   // one per P buffer, so that a waiter can never be lapped
     uint64_t pv_done[2];  // P V of the tile that used P buffer 0 / 1 has completed
     uint64_t tile_full[kTileRing];  // the producer has published a tile index in tile_ring[e]
@@ -371,10 +363,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             mbar_init(&bars.v_full[s], 1);
             mbar_init(&bars.v_empty[s], 1);
         }
-        for (int i = 0; i < kSBufs; ++i) {
-            mbar_init(&bars.s_full[i], 1);
-            mbar_init(&bars.s_free[i], 128);
-        }
+        mbar_init(&bars.s_full, 1);
+        mbar_init(&bars.s_free, 128);
         mbar_init(&bars.o_free, 128);
         for (int e = 0; e < kTileRing; ++e) {
             mbar_init(&bars.tile_full[e], 1);
@@ -644,9 +634,8 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     // S = Q K(j)^T as soon as K(j) has landed and the softmax threads hold the previous scores in
                     // registers (the previous scores may be the last ones of the tile before)
                     const int s = kc % kKStages;
-                    const int sb = kc % kSBufs;  // score buffer of this block
                     ok = wait_or_abort(&bars.k_full[s], (kc / kKStages) & 1, abort_flag, a.status, kDevTmaTimeout) &&
-                         (kc < kSBufs || wait_or_abort(&bars.s_free[sb], ((kc / kSBufs) - 1) & 1, abort_flag, a.status,
+                         (kc == 0 || wait_or_abort(&bars.s_free, (kc - 1) & 1, abort_flag, a.status,
                                                        kDevMmaTimeout));
                     if (!ok) {
                         break;
@@ -658,12 +647,12 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         for (int cb = 0; cb < T::kColBlocks; ++cb) {
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {
-                                tc_mma_f16(d_s + sb * kBlockN, desc_join(q_lo + cb * (T::kQBlockBytes >> 4) + 2 * k, hi_sw128),
+                                tc_mma_f16(d_s, desc_join(q_lo + cb * (T::kQBlockBytes >> 4) + 2 * k, hi_sw128),
                                            desc_join(ks_lo + cb * (T::kKVBlockBytes >> 4) + 2 * k, hi_sw128), idesc_qk,
                                            (cb | k) ? 1u : 0u);
                             }
                         }
-                        tc_commit(&bars.s_full[sb]);
+                        tc_commit(&bars.s_full);
                         tc_commit(&bars.k_empty[s]);
                         if (j == ti.n_kv - 1) {
                             tc_commit(&bars.q_empty);  // the tile's last read of Q
@@ -744,8 +733,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                         break;
                     }
                 }
-                const int sb = pc % kSBufs;
-                ok = wait_or_abort(&bars.s_full[sb], (pc / kSBufs) & 1, abort_flag, a.status, kDevMmaTimeout);
+                ok = wait_or_abort(&bars.s_full, pc & 1, abort_flag, a.status, kDevMmaTimeout);
                 if (!ok) {
                     break;
                 }
@@ -755,7 +743,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                     uint32_t v[kBlockN / 32][32];
 #pragma unroll
                     for (int c = 0; c < kBlockN / 32; ++c) {
-                        tmem_ld32(t_s + sb * kBlockN + 32 * c, v[c]);
+                        tmem_ld32(t_s + 32 * c, v[c]);
                     }
                     tmem_wait_ld();
 #pragma unroll
@@ -768,7 +756,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
                 // S is in registers: the MMA warp may overwrite the buffer with a later block's scores
                 tc_fence_before();
-                mbar_arrive(&bars.s_free[sb]);
+                mbar_arrive(&bars.s_free);
                 // columns of this tile that row r may see: col <= limit.  Only tiles that reach past the first
                 // row's horizon or past the end of the kv range need the mask (uniform for the CTA).  Unless the
                 // tile has rows that see nothing at all (handled below), column 0 of tile 0 is visible to every
