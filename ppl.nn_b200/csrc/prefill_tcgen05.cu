@@ -94,6 +94,12 @@ struct PrefillArgs {
     int32_t group;
     int32_t kv_mode;    // 0: K/V are this call's rows (same indexing as Q); 1: staged cache rows; 2: own K/V tensor
     int32_t is_causal;  // query row i sees kv positions <= (kvlen - seqlen) + i; otherwise all of them
+    // head_rows > 0 (the un-cached operator on a batch of one-token sequences): a work unit is one
+    // (sequence, kv head), and the head_rows query heads of that kv group are the ROWS of its tile, so K and V
+    // of a sequence are read once per kv head instead of once per query head.  Unit pb = b * kv_heads + kvh;
+    // its query rows are rows pb * head_rows .. of the query tensor seen as [tokens * heads, 1, Dh].
+    int32_t head_rows;
+    int32_t kv_heads;
     int64_t max_kvlen;
     float scale_log2;
     MaskDev mask;      // the optional attn_mask input (kernel instances with MASK only)
@@ -413,9 +419,18 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             pb = rem / a.num_heads;
             ti.head = rem - pb * a.num_heads;
         }
-        const int b = a.decoding_batches + pb;
-        const int64_t seq0 = a.seqstarts[b];
-        int64_t seqlen = a.seqstarts[b + 1] - seq0;
+        int b = a.decoding_batches + pb;
+        int kvh_of_unit = -1;
+        int64_t seq0, seqlen;
+        if (a.head_rows > 0) {
+            b = pb / a.kv_heads;
+            kvh_of_unit = pb - b * a.kv_heads;
+            seq0 = static_cast<int64_t>(pb) * a.head_rows;
+            seqlen = a.head_rows;
+        } else {
+            seq0 = a.seqstarts[b];
+            seqlen = a.seqstarts[b + 1] - seq0;
+        }
         if (seqlen > a.max_seqlen) {
             seqlen = a.max_seqlen;
             if (lane == 0 && qt_rev == 0 && ti.head == 0) {  // only the producer warp decodes tiles
@@ -427,7 +442,7 @@ prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             return false;
         }
         const int qt = n_qt - 1 - qt_rev;  // longest (latest) query tiles first
-        ti.kvh = ti.head / a.group;
+        ti.kvh = kvh_of_unit >= 0 ? kvh_of_unit : ti.head / a.group;
         const int64_t i0 = static_cast<int64_t>(qt) * kBlockM;
         ti.rows_valid = (seqlen - i0) < kBlockM ? static_cast<int>(seqlen - i0) : kBlockM;
         // kv rows of the sequence, how many there are, and how many of them precede query row 0 (hist)
@@ -1065,7 +1080,7 @@ static int launch_attention_core(const void* query, const void* k_src, const voi
     // K and V of everything this call may read against half of a 126 MB L2
     a.seq_major = static_cast<uint64_t>(kv_rows) * num_kv_heads * DH * 4 > (64ull << 20) ? 1 : 0;
     a.num_heads = num_heads;
-    a.group = num_heads / num_kv_heads;
+    a.group = a.head_rows > 0 ? 1 : num_heads / num_kv_heads;
     a.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(DH));
 
     a.mask_scale = sqrtf(static_cast<float>(DH));
@@ -1195,13 +1210,29 @@ int launch_mha(int num_heads, int num_kv_heads, int head_dim, int is_causal, int
     a.kv_mode = 2;
     a.is_causal = is_causal ? 1 : 0;
     a.mask = mask;
-    const int64_t q_tiles = (max_seqlen + kBlockM - 1) / kBlockM;
+    int64_t q_tiles = (max_seqlen + kBlockM - 1) / kBlockM;
     const int64_t kv_rows = total_kv > 0 ? total_kv : 1;  // a tensor map needs a non-empty extent
+    int64_t q_rows = total_q;
+    int q_heads = num_heads;
+    const int group = num_heads / num_kv_heads;
+    if (max_seqlen == 1 && total_q == batch && group > 1 && group <= kBlockM && mask.data == nullptr &&
+        batch * num_kv_heads < (1 << 30)) {
+        // every sequence has exactly one query token: the heads of a kv group become the rows of a tile (a
+        // single row sees every kv position, causal or not)
+        a.head_rows = group;
+        a.kv_heads = num_kv_heads;
+        a.prefill_batches = static_cast<int32_t>(batch * num_kv_heads);
+        a.is_causal = 0;
+        a.max_seqlen = group;
+        q_tiles = 1;
+        q_rows = total_q * num_heads;
+        q_heads = 1;
+    }
     if (head_dim == 128) {
-        return launch_attention_core<128>(query, key, value, total_q, kv_rows, num_heads, num_kv_heads, q_tiles, a, stream);
+        return launch_attention_core<128>(query, key, value, q_rows, kv_rows, q_heads, num_kv_heads, q_tiles, a, stream);
     }
     if (head_dim == 64) {
-        return launch_attention_core<64>(query, key, value, total_q, kv_rows, num_heads, num_kv_heads, q_tiles, a, stream);
+        return launch_attention_core<64>(query, key, value, q_rows, kv_rows, q_heads, num_kv_heads, q_tiles, a, stream);
     }
     return PPLB200_UNSUPPORTED;
 }

@@ -142,6 +142,10 @@ CASES = [
     ([9, 4], [3, 0], 4, 2, 64),                           # fewer kv rows than query rows, and none at all
     ([300], [1000], 32, 8, 128),
     ([300] * 40, [10] * 40, 4, 2, 128),                   # runs of query tiles that see no kv row at all
+    # one-token sequences with several query heads per kv head: the heads of a group share one tile
+    ([1] * 5, [17, 64, 130, 1, 300], 32, 4, 128),
+    ([1, 1, 1], [70, 5, 129], 16, 8, 64),
+    ([1, 1], [0, 9], 8, 2, 64),                           # ... and a sequence without any kv row
 ]
 
 
