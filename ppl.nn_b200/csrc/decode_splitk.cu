@@ -823,13 +823,13 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                 uint32_t pb0, pb1;  // P^T as the B operand of the second MMA: k = token, n = head
                 if constexpr (KDOT) {
                     // one head: every lane of quad g holds the raw scores of tokens g and g + 8
-                    float sa_ = sacc[0], sb_ = sacc[2];
+                    float s_lo = sacc[0], s_hi = sacc[2];
                     if (nvalid < kTileTok) {  // rows past the end of the sequence weigh nothing
-                        sa_ = g < nvalid ? sa_ : -INFINITY;
-                        sb_ = g + 8 < nvalid ? sb_ : -INFINITY;
+                        s_lo = g < nvalid ? s_lo : -INFINITY;
+                        s_hi = g + 8 < nvalid ? s_hi : -INFINITY;
                     }
                     const float sc = a.scale_log2;
-                    float lm = fmaxf(sa_, sb_);
+                    float lm = fmaxf(s_lo, s_hi);
                     if (__any_sync(0xffffffffu, lm > thr0)) {
 #pragma unroll
                         for (int off = 4; off <= 16; off <<= 1) {
@@ -849,7 +849,7 @@ decode_splitk_kernel(const __grid_constant__ CUtensorMap tmap_codes, const Decod
                         }
                     }
                     // the normaliser sums the fp16-rounded weights, the very numbers the MMA consumes
-                    const uint32_t ph = h2_as_u32(__floats2half2_rn(ex2_approx(fmaf(sa_, sc, -m0)), ex2_approx(fmaf(sb_, sc, -m0))));
+                    const uint32_t ph = h2_as_u32(__floats2half2_rn(ex2_approx(fmaf(s_lo, sc, -m0)), ex2_approx(fmaf(s_hi, sc, -m0))));
                     float l_hi = 0.0f;
                     add_halves_to_floats(l0, l_hi, ph);
                     l0 += l_hi;
