@@ -65,6 +65,15 @@ DTYPE = "fp16 in/out, int8 cache, fp32 accumulate"
 # of the captured launch: 693.08 MB + 4.61 MB for 690.86 MB); traffic grows in proportion to cached tokens.
 DECODE_TRAFFIC_PER_ALGO_BYTE = 1.0099
 
+def decode_scores_form(spec) -> str:
+    """Which form of the decode kernel the library picks for a workload (csrc/decode_splitk.cu, launch_decode_dh)."""
+    if spec.n_decode == 0:
+        return "none (no decode sequences)"
+    if spec.num_heads == spec.num_kv_heads and os.environ.get("PPLB200_DECODE_KDOT", "1")[:1] != "0":
+        return "integer dot products (one query head per kv head)"
+    return "tensor cores (mma.m16n8k16 over the dequantised keys)"
+
+
 PER_CONFIG = (  # (workload, enable_cache_prefill)
     ("cfg3_llama8b_mixed", False),
     ("cfg3_llama8b_mixed", True),
@@ -440,6 +449,7 @@ def run_config(ctx: Ctx, name: str, cache_prefill: bool, steps: int, warmup: int
     ms = t["first_block_ms"] / steps
     roof = kernel_rooflines(ctx, dc, spec, idx, t)
     res = {"workload": name, "enable_cache_prefill": bool(cache_prefill), "n_gpus": ctx.world, "steps": steps,
+           "decode_scores": decode_scores_form(spec),
            "sharding": f"kv-heads/{ctx.world}", "ms_per_step": ms, "tokens_per_step": int(idx.total_tokens),
            "decode_tokens_per_s": nd / (ms * 1e-3), "tokens_per_s": idx.total_tokens / (ms * 1e-3),
            "decode_sequences": nd, "kv_tokens": int(idx.kvlens[:nd].sum()), "prefill_sequences": idx.batch - nd,
@@ -621,6 +631,7 @@ def main():
             "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
             "config": {"workload": spec.name, **config_bits,
                        "cache_layout": args.layout, "page_size": args.page_size, "sharding": f"kv-heads/{world}",
+                       "decode_scores": decode_scores_form(spec),
                        "l2": "no flush: the per-GPU cache working set is far larger than the 126 MB L2"
                              if algo_bytes > 4 * 126e6 else
                              "no flush: the step is compute-bound prefill" if nd == 0 else
