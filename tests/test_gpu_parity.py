@@ -168,10 +168,11 @@ def test_split_boundaries(orc, torch_dev, pkg):
         run_case(orc, torch_dev, workloads.host_case(spec), split_k=split_k)
 
 
-@pytest.mark.parametrize("page,layout", [(16, 0), (128, 0), (32, 3)])
-def test_paged_cache(orc, torch_dev, pkg, page, layout):
+@pytest.mark.parametrize("hq,hkv", [(8, 4), (4, 4)])  # tensor-core scores, and integer-dot scores (one head per kv head)
+@pytest.mark.parametrize("page,layout", [(16, 0), (128, 0), (32, 3), (48, 0)])
+def test_paged_cache(orc, torch_dev, pkg, page, layout, hq, hkv):
     from ppl_nn_b200 import workloads
-    spec = _spec(num_heads=8, num_kv_heads=4, head_dim=128, n_decode=12, kv_lo=1, kv_hi=700, seed=23)
+    spec = _spec(num_heads=hq, num_kv_heads=hkv, head_dim=128, n_decode=12, kv_lo=1, kv_hi=700, seed=23)
     run_case(orc, torch_dev, workloads.host_case(spec, page_size=page), layout=layout, split_k=2)
 
 
